@@ -1,0 +1,156 @@
+/*
+ * tensotron_gemm.h -- C ABI of libtensotron_gemm.so, the B200 (sm_100a) matmul
+ * engine that sits behind Tensotron's CUDA backend.
+ *
+ * Conventions (they follow the reference's existing native call sites, the cuBLAS
+ * P/Invoke at src/Tensotron/TensorRuntime.cs:1011-1081):
+ *   - cdecl, plain pointers and integers only; every entry returns an int status
+ *     (0 = success), the caller throws on non-zero like it does for cuBLAS.
+ *   - device pointers are raw addresses owned by the caller; the library never
+ *     frees or keeps them.  Element type is float32 everywhere; strides and
+ *     offsets are in ELEMENTS and fit int32 (src/Tensotron/TensorRuntime.cs:219).
+ *   - `stream` is a CUstream / cudaStream_t passed as void*; NULL is the default
+ *     stream.  Every call only enqueues stream-ordered work: no synchronisation,
+ *     no allocation, no host-visible side effect, so a call can be re-fired under
+ *     stream capture (src/Tensotron/TensorRuntime.cs:596-698).
+ *   - single caller thread per handle (README.md:168-170); no internal locking.
+ */
+#ifndef TENSOTRON_GEMM_H
+#define TENSOTRON_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported entry points (the library is built with hidden default visibility). */
+#if defined(_WIN32)
+#define TT_API __declspec(dllexport)
+#else
+#define TT_API __attribute__((visibility("default")))
+#endif
+
+typedef struct tt_handle_s* tt_handle_t;
+
+/* status codes */
+#define TT_OK 0
+#define TT_ERR_INVALID_ARG 1   /* null pointer, negative size, K mismatch, bad mode    */
+#define TT_ERR_CUDA 2          /* a CUDA runtime / driver call failed                   */
+#define TT_ERR_UNSUPPORTED 3   /* shape / stride combination outside the contract       */
+#define TT_ERR_WORKSPACE 4     /* handle workspace too small for the requested variant  */
+#define TT_ERR_DEVICE_WAIT 5   /* a bounded device-side wait ran out (see tt_check)     */
+
+/* math modes: 0 and 3 carry the meaning of SetCuBlasMathMode
+ * (src/Tensotron/TensorRuntime.cs:332-338: 0 = FP32, 3 = TF32); 4 is new. */
+#define TT_MATH_FP32 0    /* strict IEEE float32 FFMA, the default                      */
+#define TT_MATH_TF32 3    /* AllowTf32: tcgen05 kind::tf32, fp32 accumulate             */
+#define TT_MATH_3XTF32 4  /* three tf32 products per term, recovers ~fp32 accuracy      */
+
+/* activations fused into the Linear epilogue (src/Tensotron/Ops.Unary.cs:89-105) */
+#define TT_ACT_NONE 0
+#define TT_ACT_RELU 1
+#define TT_ACT_TANH 2
+
+TT_API const char* tt_version(void);
+
+/* Created once next to the cuBLAS handle (src/Tensotron/TensorRuntime.cs:509-510)
+ * and destroyed in Dispose (:1402-1415).  `workspace_bytes` sizes the split-K /
+ * backward scratch owned by the handle (0 picks a default).  Binds to `device`. */
+TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle);
+TT_API int tt_destroy(tt_handle_t h);
+
+/* Static, human-readable text for the last non-zero status on this handle. */
+TT_API const char* tt_last_error(tt_handle_t h);
+
+/* Replaces AllowTf32 / SetCuBlasMathMode (src/Tensotron/TensorRuntime.cs:158-159,
+ * :332-338). */
+TT_API int tt_set_math_mode(tt_handle_t h, int mode);
+TT_API int tt_get_math_mode(tt_handle_t h, int* mode);
+
+/* Replaces the body of IlgpuRuntime.LaunchMatMul
+ * (src/Tensotron/TensorRuntime.cs:242-243 contract, :959-988 implementation):
+ *   C[m,n] = sum_k A[m*aMs + k*aKs] * B[n*bNs + k*bKs],  C contiguous (M,N). */
+TT_API int tt_matmul(tt_handle_t h, void* stream, const float* a, const float* b, float* c,
+              int M, int N, int K, int aMs, int aKs, int bKs, int bNs);
+
+/* Replaces IlgpuRuntime.LaunchMatMulBatched
+ * (src/Tensotron/TensorRuntime.cs:252-254 contract, :1149-1211 implementation):
+ * the same product per batch entry; the batch index is decoded last-axis-fastest
+ * over batchDims and the operand offsets are sum(idx[ax] * stride[ax]) (stride 0 =
+ * broadcast).  C is contiguous (batch..., M, N).  The three int arrays are host
+ * memory, read during the call and not retained. */
+TT_API int tt_matmul_batched(tt_handle_t h, void* stream, const float* a, const float* b, float* c,
+                      int batchCount, int M, int N, int K, int aMs, int aKs, int bKs, int bNs,
+                      int batchRank, const int* batchDims, const int* aBatchStrides,
+                      const int* bBatchStrides);
+
+/* Linear.Forward (+ the Activation module that follows it) as one launch
+ * (src/Tensotron/Module.cs:100-105, src/Tensotron/TensorOps.LinearNT.cs:13-25):
+ *   y = act(x (M,K) . w (N,K)^T + bias (N)),  bias may be NULL. */
+TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* bias,
+                  float* y, int M, int N, int K, int act);
+
+/* Backward of the same (src/Tensotron/TensorOps.LinearNT.cs:27-48,
+ * src/Tensotron/TensorOps.cs:143-147, src/Tensotron/Ops.Unary.cs:89-105):
+ *   g  = dy * act'(y)            (ReLU: y>0 ? dy : 0;  Tanh: dy*(1-y*y))
+ *   dx = g . w        (M,K)  NN  -- skipped when dx is NULL
+ *   dw = g^T . x      (N,K)  TN
+ *   dbias[n] = sum_m g[m,n]  in a fixed order (no atomics) -- skipped when NULL
+ * Outputs are written, not accumulated (accumulation stays with Tensor.AddGrad).
+ * When act != TT_ACT_NONE the masked gradient g needs M*N floats of the handle
+ * workspace. */
+TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* y,
+                  const float* dy, float* dx, float* dw, float* dbias, int M, int N, int K, int act);
+
+/* CrossEntropy(mean-style) forward+backward in one launch
+ * (src/Tensotron/TensorOps.Losses.cs:97-108, src/Tensotron/TensorOps.Reduce.cs:122-141):
+ * labels are device int32; dlogits = (softmax - onehot) * scale; *loss (device
+ * float) = scale * sum_rows(-log softmax[label]); row sums are reduced in a fixed
+ * order.  `loss` and `dlogits` may each be NULL. */
+TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
+                             float* dlogits, float* loss, int rows, int classes, float scale);
+
+/* Fused Adam over one flat parameter span (src/Tensotron/Kernels.cs:126-157,
+ * src/Tensotron/Optimizers.cs:144-193).  adv = device [t, 1/(1-b1^t), 1/(1-b2^t)];
+ * when `advance` is non-zero the step counter is advanced on the device first, so a
+ * captured step keeps its bias correction moving across replays. */
+TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, float* m, float* v,
+                 float* adv, long long n, float beta1, float beta2, float lr, float eps,
+                 float coupled_wd, float decoupled_factor, int advance);
+
+/* target[i] += source[i]  (Kernels.AddInto, src/Tensotron/Kernels.cs:111-114). */
+TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* source, long long n);
+
+/* BroadcastBatch of TensorOps.MatMulND (src/Tensotron/TensorOps.MatMulND.cs:11-31):
+ * right-aligns the two batch shapes, returns the broadcast dims and per-operand
+ * element strides (0 on broadcast axes).  Pure host logic.  Returns
+ * TT_ERR_INVALID_ARG when the shapes do not broadcast.  *rank = max(ra, rb). */
+TT_API int tt_broadcast_batch(int ra, const int* a_dims, const int* a_strides, int rb, const int* b_dims,
+                       const int* b_strides, int* rank, int* dims, int* a_bs, int* b_bs);
+
+/* Counters in the spirit of TensorRuntime.Launches (src/Tensotron/TensorRuntime.cs:143-151). */
+typedef struct tt_stats {
+    long long launches;        /* kernels enqueued by this handle                        */
+    long long calls;           /* C-ABI compute calls                                     */
+    long long simt_tma;        /* calls served by the TMA-fed FP32 FFMA kernel            */
+    long long tcgen05;         /* calls served by the tcgen05 TF32 / 3xTF32 kernel        */
+    long long generic;         /* calls served by the any-stride kernel                   */
+    long long splitk;          /* calls that used the split-K workspace                   */
+    long long workspace_bytes; /* size of the handle workspace                            */
+} tt_stats;
+TT_API int tt_get_stats(tt_handle_t h, tt_stats* out);
+TT_API int tt_reset_stats(tt_handle_t h);
+
+/* Reads the device-side status word (bounded waits that gave up).  This call
+ * synchronises the stream; it is for tests and debugging, not the hot path. */
+TT_API int tt_check(tt_handle_t h, void* stream);
+
+/* Forces a kernel variant for A/B measurements: 0 auto, 1 generic, 2 SIMT-TMA. */
+TT_API int tt_set_variant(tt_handle_t h, int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENSOTRON_GEMM_H */

@@ -1,0 +1,613 @@
+// C ABI of libtensotron_gemm.so: argument checks, layout classification, variant
+// choice, TMA descriptor construction and kernel launches.  Nothing here allocates,
+// synchronises or copies from pageable memory after tt_create, so every compute call
+// can be recorded into a CUDA graph.
+#include "../../include/tensotron_gemm.h"
+
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "elementwise.cuh"
+#include "gemm_common.h"
+#include "gemm_generic.cuh"
+#include "sgemm_simt.cuh"
+#include "tensor_map.h"
+#include "tf32_launch.h"
+
+using namespace tt;
+
+struct tt_handle_s {
+    int device;
+    int num_sms;
+    int math_mode;
+    int variant;  // 0 auto, 1 generic, 2 simt-tma
+    uint8_t* workspace;
+    size_t workspace_bytes;
+    unsigned int* status;  // device status word
+    tt_stats stats;
+    char err[256];
+};
+
+namespace {
+
+constexpr size_t DEFAULT_WORKSPACE = 256ull << 20;
+constexpr long long TMA_MIN_FLOP_ELEMS = 1ll << 21;  // M*N*K below this -> any-stride kernel
+
+int fail(tt_handle_t h, int code, const char* fmt, const char* detail = "")
+{
+    if (h) snprintf(h->err, sizeof(h->err), fmt, detail);
+    return code;
+}
+
+int cuda_fail(tt_handle_t h, cudaError_t e, const char* what)
+{
+    if (h) snprintf(h->err, sizeof(h->err), "%s: %s", what, cudaGetErrorString(e));
+    return TT_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- batch handling -------------------------------------------------------------
+
+struct HostBatch {
+    int rank = 0;
+    int dims[MAX_BATCH_RANK];
+    int as[MAX_BATCH_RANK];
+    int bs[MAX_BATCH_RANK];
+};
+
+// Drops size-1 axes and merges adjacent axes that are jointly contiguous for both
+// operands (broadcast merges with broadcast).  Returns false when more than
+// MAX_BATCH_RANK axes remain.
+bool collapse_batch(int rank, const int* dims, const int* as, const int* bs, HostBatch& out)
+{
+    out.rank = 0;
+    for (int ax = 0; ax < rank; ax++) {
+        if (dims[ax] == 1) continue;
+        if (out.rank > 0) {
+            const int o = out.rank - 1;
+            // previous (outer) axis o, this (inner) axis ax: mergeable when
+            // stride_outer == dim_inner * stride_inner for both operands
+            if (static_cast<long long>(out.as[o]) == static_cast<long long>(dims[ax]) * as[ax] &&
+                static_cast<long long>(out.bs[o]) == static_cast<long long>(dims[ax]) * bs[ax]) {
+                out.dims[o] *= dims[ax];
+                out.as[o] = as[ax];
+                out.bs[o] = bs[ax];
+                continue;
+            }
+        }
+        if (out.rank == MAX_BATCH_RANK) return false;
+        out.dims[out.rank] = dims[ax];
+        out.as[out.rank] = as[ax];
+        out.bs[out.rank] = bs[ax];
+        out.rank++;
+    }
+    return true;
+}
+
+// Per-operand TMA batch dims: walks the axes innermost-first, skipping broadcast
+// axes, merging an axis into the open slot when it continues it contiguously.
+// Fills slot/mult for the kernel and appends (extent, stride) to the view.
+bool plan_tma_batch(const HostBatch& hb, const int* strides, signed char* slot, int* mult,
+                    OperandView& view)
+{
+    int nslots = 0;
+    long long cur_extent = 0, cur_stride = 0;
+    int slot_extent[3] = {1, 1, 1};
+    long long slot_stride[3] = {0, 0, 0};
+    for (int ax = hb.rank - 1; ax >= 0; ax--) {
+        if (strides[ax] == 0) { slot[ax] = -1; mult[ax] = 0; continue; }
+        if (nslots > 0 && static_cast<long long>(strides[ax]) == cur_extent * cur_stride) {
+            slot[ax] = static_cast<signed char>(nslots - 1);
+            mult[ax] = static_cast<int>(cur_extent);
+            cur_extent *= hb.dims[ax];
+            slot_extent[nslots - 1] = static_cast<int>(cur_extent);
+            continue;
+        }
+        if (nslots == 3) return false;
+        slot[ax] = static_cast<signed char>(nslots);
+        mult[ax] = 1;
+        cur_extent = hb.dims[ax];
+        cur_stride = strides[ax];
+        slot_extent[nslots] = hb.dims[ax];
+        slot_stride[nslots] = strides[ax];
+        nslots++;
+    }
+    for (int s = 0; s < nslots; s++) {
+        if (slot_stride[s] < 0) return false;
+        view.dim[view.rank] = static_cast<uint64_t>(slot_extent[s]);
+        view.stride_elems[view.rank] = static_cast<uint64_t>(slot_stride[s]);
+        view.rank++;
+    }
+    return true;
+}
+
+void fill_batch_desc(const HostBatch& hb, BatchDesc& bd)
+{
+    memset(&bd, 0, sizeof(bd));
+    bd.rank = hb.rank;
+    for (int i = 0; i < hb.rank; i++) {
+        bd.dims[i] = hb.dims[i];
+        bd.a_stride[i] = hb.as[i];
+        bd.b_stride[i] = hb.bs[i];
+        bd.a_slot[i] = bd.b_slot[i] = -1;
+    }
+}
+
+// ---- operand classification -----------------------------------------------------
+
+// Builds the 2-D part of a TMA view for one operand.  `rows` is the M (or N) extent,
+// row_stride / k_stride the element strides of that axis and of K.  Returns 1 for a
+// K-major view, 0 for an MN-major view, -1 when neither axis is contiguous.
+int operand_view(const float* base, int rows, int K, int row_stride, int k_stride,
+                 OperandView& v)
+{
+    v.base = base;
+    v.rank = 2;
+    v.stride_elems[0] = 1;
+    // A size-1 axis has no meaningful stride: give it the next legal one.
+    const auto legal = [](long long extent) {
+        return static_cast<uint64_t>(((extent + 3) / 4) * 4);
+    };
+    if (k_stride == 1 || K == 1) {
+        if (rows > 1 && row_stride <= 0) return -1;
+        v.dim[0] = K; v.dim[1] = rows;
+        v.stride_elems[1] = rows == 1 ? legal(K) : static_cast<uint64_t>(row_stride);
+        return 1;
+    }
+    if (row_stride == 1 || rows == 1) {
+        if (k_stride <= 0) return -1;
+        v.dim[0] = rows; v.dim[1] = K;
+        v.stride_elems[1] = static_cast<uint64_t>(k_stride);
+        return 0;
+    }
+    return -1;
+}
+
+struct GemmCall {
+    const float* a;
+    const float* b;
+    float* c;
+    int M, N, K, aMs, aKs, bKs, bNs;
+    HostBatch batch;
+    int batch_count;
+    Epilogue epi;
+};
+
+int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+{
+    generic::Params p;
+    p.a = g.a; p.b = g.b; p.c = g.c;
+    p.shape.M = g.M; p.shape.N = g.N; p.shape.K = g.K;
+    p.shape.tiles_m = (g.M + generic::BM - 1) / generic::BM;
+    p.shape.tiles_n = (g.N + generic::BN - 1) / generic::BN;
+    p.shape.batch = g.batch_count;
+    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    fill_batch_desc(g.batch, p.batch);
+    p.epi = g.epi;
+    p.aMs = g.aMs; p.aKs = g.aKs; p.bKs = g.bKs; p.bNs = g.bNs;
+    const long long max_grid = static_cast<long long>(h->num_sms) * 8;
+    const int grid = static_cast<int>(p.shape.work < max_grid ? p.shape.work : max_grid);
+    generic::gemm_generic_kernel<<<grid, generic::THREADS, 0, st>>>(p);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "generic gemm launch");
+    h->stats.launches++;
+    h->stats.generic++;
+    return TT_OK;
+}
+
+template <bool AK, bool BK_>
+int launch_simt_t(tt_handle_t h, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb,
+                  const simt::Params& p, int grid)
+{
+    auto kern = simt::sgemm_simt_kernel<AK, BK_>;
+    kern<<<grid, simt::THREADS, simt::SMEM_BYTES, st>>>(ma, mb, p);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "simt gemm launch");
+    return TT_OK;
+}
+
+// Returns TT_ERR_UNSUPPORTED (without touching h->err) when the operands cannot be
+// expressed as TMA descriptors; the caller then uses the any-stride kernel.
+int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+{
+    OperandView va, vb;
+    const int ak = operand_view(g.a, g.M, g.K, g.aMs, g.aKs, va);
+    const int bk = operand_view(g.b, g.N, g.K, g.bNs, g.bKs, vb);
+    if (ak < 0 || bk < 0) return TT_ERR_UNSUPPORTED;
+    simt::Params p;
+    memset(&p, 0, sizeof(p));
+    fill_batch_desc(g.batch, p.batch);
+    if (!plan_tma_batch(g.batch, g.batch.as, p.batch.a_slot, p.batch.a_mult, va)) return TT_ERR_UNSUPPORTED;
+    if (!plan_tma_batch(g.batch, g.batch.bs, p.batch.b_slot, p.batch.b_mult, vb)) return TT_ERR_UNSUPPORTED;
+    if (!tma_compatible(va) || !tma_compatible(vb)) return TT_ERR_UNSUPPORTED;
+
+    CUtensorMap ma, mb;
+    int r = ak ? encode_tensor_map(&ma, va, simt::BK, simt::BM, Swizzle::B128)
+               : encode_tensor_map(&ma, va, simt::BM, simt::BK, Swizzle::None);
+    if (r != 0) return TT_ERR_UNSUPPORTED;
+    r = bk ? encode_tensor_map(&mb, vb, simt::BK, simt::BN, Swizzle::B128)
+           : encode_tensor_map(&mb, vb, simt::BN, simt::BK, Swizzle::None);
+    if (r != 0) return TT_ERR_UNSUPPORTED;
+
+    p.shape.M = g.M; p.shape.N = g.N; p.shape.K = g.K;
+    p.shape.tiles_m = (g.M + simt::BM - 1) / simt::BM;
+    p.shape.tiles_n = (g.N + simt::BN - 1) / simt::BN;
+    p.shape.batch = g.batch_count;
+    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    p.epi = g.epi;
+    p.c = g.c;
+    p.status = h->status;
+    p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
+    const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
+    int rc;
+    if (ak && bk) rc = launch_simt_t<true, true>(h, st, ma, mb, p, grid);
+    else if (ak && !bk) rc = launch_simt_t<true, false>(h, st, ma, mb, p, grid);
+    else if (!ak && !bk) rc = launch_simt_t<false, false>(h, st, ma, mb, p, grid);
+    else rc = launch_simt_t<false, true>(h, st, ma, mb, p, grid);
+    if (rc != TT_OK) return rc;
+    h->stats.launches++;
+    h->stats.simt_tma++;
+    return TT_OK;
+}
+
+int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+{
+    if (g.M == 0 || g.N == 0 || g.batch_count == 0) return TT_OK;
+    if (g.K == 0 && !g.epi.bias && g.epi.act == TT_ACT_NONE) {
+        const cudaError_t e = cudaMemsetAsync(
+            g.c, 0, sizeof(float) * static_cast<size_t>(g.batch_count) * g.M * g.N, st);
+        if (e != cudaSuccess) return cuda_fail(h, e, "memset C");
+        return TT_OK;
+    }
+    const long long vol = static_cast<long long>(g.M) * g.N * (g.K > 0 ? g.K : 1);
+    if (g.K > 0 && h->variant != 1) {
+        if (h->math_mode != TT_MATH_FP32) {
+            const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
+                                            g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,
+                                            g.batch.dims, g.batch.as, g.batch.bs, g.epi, h->num_sms,
+                                            h->status);
+            if (rc == TT_OK) { h->stats.launches++; h->stats.tcgen05++; return TT_OK; }
+            if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
+        }
+        if (h->variant == 2 || vol >= TMA_MIN_FLOP_ELEMS) {
+            const int rc = try_launch_simt(h, st, g);
+            if (rc != TT_ERR_UNSUPPORTED) return rc;
+        }
+    }
+    return launch_generic(h, st, g);
+}
+
+// Per-device kernel attributes, set once at handle creation so that no compute call
+// does lazy set-up work (which could not be captured into a graph).
+cudaError_t init_kernels()
+{
+    cudaError_t e;
+    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
+}
+
+int check_common(tt_handle_t h, const void* a, const void* b, const void* c, int M, int N, int K)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (M < 0 || N < 0 || K < 0) return fail(h, TT_ERR_INVALID_ARG, "negative dimension");
+    if ((static_cast<long long>(M) * N > 0) && (!c || (K > 0 && (!a || !b))))
+        return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    return TT_OK;
+}
+
+int bind(tt_handle_t h)
+{
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur == h->device) return TT_OK;
+    const cudaError_t e = cudaSetDevice(h->device);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaSetDevice");
+    return TT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+TT_API const char* tt_version(void) { return "tensotron-gemm-b200 0.1 (sm_100a)"; }
+
+TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle)
+{
+    if (!out_handle) return TT_ERR_INVALID_ARG;
+    *out_handle = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return TT_ERR_CUDA;
+    if (cudaSetDevice(device) != cudaSuccess) return TT_ERR_CUDA;
+    tt_handle_s* h = new tt_handle_s();
+    memset(h, 0, sizeof(*h));
+    h->device = device;
+    h->math_mode = TT_MATH_FP32;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; return TT_ERR_CUDA; }
+    if (prop.major != 10) { delete h; return TT_ERR_UNSUPPORTED; }  // sm_100a code only
+    h->num_sms = prop.multiProcessorCount;
+    h->workspace_bytes = workspace_bytes ? workspace_bytes : DEFAULT_WORKSPACE;
+    if (cudaMalloc(&h->workspace, h->workspace_bytes) != cudaSuccess) { delete h; return TT_ERR_CUDA; }
+    if (cudaMalloc(&h->status, 256) != cudaSuccess) { cudaFree(h->workspace); delete h; return TT_ERR_CUDA; }
+    cudaMemset(h->status, 0, 256);
+    if (init_kernels() != cudaSuccess) { cudaFree(h->workspace); cudaFree(h->status); delete h; return TT_ERR_CUDA; }
+    h->stats.workspace_bytes = static_cast<long long>(h->workspace_bytes);
+    h->err[0] = 0;
+    *out_handle = h;
+    return TT_OK;
+}
+
+TT_API int tt_destroy(tt_handle_t h)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    cudaSetDevice(h->device);
+    cudaFree(h->workspace);
+    cudaFree(h->status);
+    delete h;
+    return TT_OK;
+}
+
+TT_API const char* tt_last_error(tt_handle_t h) { return h ? h->err : "null handle"; }
+
+TT_API int tt_set_math_mode(tt_handle_t h, int mode)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (mode != TT_MATH_FP32 && mode != TT_MATH_TF32 && mode != TT_MATH_3XTF32)
+        return fail(h, TT_ERR_INVALID_ARG, "unknown math mode");
+    h->math_mode = mode;
+    return TT_OK;
+}
+
+TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
+{
+    if (!h || !mode) return TT_ERR_INVALID_ARG;
+    *mode = h->math_mode;
+    return TT_OK;
+}
+
+TT_API int tt_set_variant(tt_handle_t h, int variant)
+{
+    if (!h || variant < 0 || variant > 2) return TT_ERR_INVALID_ARG;
+    h->variant = variant;
+    return TT_OK;
+}
+
+TT_API int tt_matmul(tt_handle_t h, void* stream, const float* a, const float* b, float* c, int M, int N,
+              int K, int aMs, int aKs, int bKs, int bNs)
+{
+    int rc = check_common(h, a, b, c, M, N, K);
+    if (rc) return rc;
+    if ((rc = bind(h))) return rc;
+    h->stats.calls++;
+    GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+TT_API int tt_matmul_batched(tt_handle_t h, void* stream, const float* a, const float* b, float* c,
+                      int batchCount, int M, int N, int K, int aMs, int aKs, int bKs, int bNs,
+                      int batchRank, const int* batchDims, const int* aBatchStrides,
+                      const int* bBatchStrides)
+{
+    int rc = check_common(h, a, b, c, M, N, K);
+    if (rc) return rc;
+    if (batchCount < 0 || batchRank < 0) return fail(h, TT_ERR_INVALID_ARG, "negative batch");
+    if (batchRank > 0 && (!batchDims || !aBatchStrides || !bBatchStrides))
+        return fail(h, TT_ERR_INVALID_ARG, "null batch arrays");
+    long long prod = 1;
+    for (int i = 0; i < batchRank; i++) {
+        if (batchDims[i] < 0) return fail(h, TT_ERR_INVALID_ARG, "negative batch dim");
+        prod *= batchDims[i];
+    }
+    if (prod != batchCount) return fail(h, TT_ERR_INVALID_ARG, "batchCount != product(batchDims)");
+    if ((rc = bind(h))) return rc;
+    h->stats.calls++;
+    GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, HostBatch(), batchCount,
+               Epilogue{nullptr, TT_ACT_NONE}};
+    if (batchCount == 0) return TT_OK;
+    if (!collapse_batch(batchRank, batchDims, aBatchStrides, bBatchStrides, g.batch))
+        return fail(h, TT_ERR_UNSUPPORTED, "more than 8 non-mergeable batch axes");
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* bias,
+                  float* y, int M, int N, int K, int act)
+{
+    int rc = check_common(h, x, w, y, M, N, K);
+    if (rc) return rc;
+    if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
+    if ((rc = bind(h))) return rc;
+    h->stats.calls++;
+    // y[m,n] = sum_k x[m*K + k] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:24)
+    GemmCall g{x, w, y, M, N, K, K, 1, 1, K, HostBatch(), 1, Epilogue{bias, act}};
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* y,
+                  const float* dy, float* dx, float* dw, float* dbias, int M, int N, int K, int act)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (M < 0 || N < 0 || K < 0) return fail(h, TT_ERR_INVALID_ARG, "negative dimension");
+    if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
+    if (!dy || !x || !w || !dw || (act != TT_ACT_NONE && !y))
+        return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const float* g = dy;
+    if (static_cast<long long>(M) * N > 0 && (act != TT_ACT_NONE || dbias)) {
+        const int chunks = ew::colsum_chunks(M);
+        const size_t g_bytes = act != TT_ACT_NONE ? sizeof(float) * static_cast<size_t>(M) * N : 0;
+        const size_t g_bytes_al = (g_bytes + 255) & ~static_cast<size_t>(255);
+        const size_t part_bytes = dbias ? sizeof(float) * static_cast<size_t>(chunks) * N : 0;
+        if (g_bytes_al + part_bytes > h->workspace_bytes)
+            return fail(h, TT_ERR_WORKSPACE, "workspace too small for linear backward");
+        float* gbuf = act != TT_ACT_NONE ? reinterpret_cast<float*>(h->workspace) : nullptr;
+        float* partial = dbias ? reinterpret_cast<float*>(h->workspace + g_bytes_al) : nullptr;
+        const bool vec = (N % 4 == 0) && aligned16(dy) && (!act || aligned16(y));
+        const dim3 grid((N + ew::COLSUM_COLS - 1) / ew::COLSUM_COLS, chunks);
+        if (vec) ew::act_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
+        else     ew::act_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
+        h->stats.launches++;
+        if (dbias) {
+            ew::colsum_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>(partial, dbias, N, chunks);
+            h->stats.launches++;
+        }
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "linear backward elementwise launch");
+        if (gbuf) g = gbuf;
+    } else if (dbias && N > 0) {
+        const cudaError_t e = cudaMemsetAsync(dbias, 0, sizeof(float) * N, st);
+        if (e != cudaSuccess) return cuda_fail(h, e, "memset dbias");
+    }
+    if (dx) {
+        // dx[m,k] = sum_n g[m*N + n] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:36)
+        GemmCall gx{g, w, dx, M, K, N, N, 1, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+        if ((rc = run_gemm(h, st, gx))) return rc;
+    }
+    // dw[n,k] = sum_m g[m*N + n] * x[m*K + k]       (src/Tensotron/TensorOps.LinearNT.cs:44)
+    GemmCall gw{g, x, dw, N, K, M, 1, N, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+    return run_gemm(h, st, gw);
+}
+
+TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
+                             float* dlogits, float* loss, int rows, int classes, float scale)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (rows < 0 || classes <= 0 || !logits || !labels) return fail(h, TT_ERR_INVALID_ARG, "bad cross-entropy arguments");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    if (rows == 0) return TT_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (sizeof(float) * static_cast<size_t>(rows) > h->workspace_bytes)
+        return fail(h, TT_ERR_WORKSPACE, "workspace too small for cross-entropy");
+    float* row_loss = loss ? reinterpret_cast<float*>(h->workspace) : nullptr;
+    const int warps_per_block = 8;
+    ew::softmax_ce_rows_kernel<<<(rows + warps_per_block - 1) / warps_per_block, 256, 0, st>>>(
+        logits, labels, dlogits, row_loss, rows, classes, scale);
+    h->stats.launches++;
+    if (loss) {
+        ew::sum_fixed_kernel<<<1, 1024, 0, st>>>(row_loss, loss, rows, scale);
+        h->stats.launches++;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "cross-entropy launch");
+    return TT_OK;
+}
+
+TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, float* m, float* v,
+                 float* adv, long long n, float beta1, float beta2, float lr, float eps,
+                 float coupled_wd, float decoupled_factor, int advance)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (n < 0 || !adv || (n > 0 && (!p || !g || !m || !v))) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (advance) {
+        ew::adam_advance_kernel<<<1, 1, 0, st>>>(adv, beta1, beta2);
+        h->stats.launches++;
+    }
+    if (n > 0) {
+        const bool vec = aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v);
+        const long long work = vec ? (n + 3) / 4 : n;
+        long long blocks = (work + 255) / 256;
+        const long long cap = static_cast<long long>(h->num_sms) * 16;
+        if (blocks > cap) blocks = cap;
+        if (vec) ew::adam_step_kernel<true><<<static_cast<int>(blocks), 256, 0, st>>>(p, g, m, v, adv, n, beta1, beta2, lr, eps, coupled_wd, decoupled_factor);
+        else     ew::adam_step_kernel<false><<<static_cast<int>(blocks), 256, 0, st>>>(p, g, m, v, adv, n, beta1, beta2, lr, eps, coupled_wd, decoupled_factor);
+        h->stats.launches++;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "Adam launch");
+    return TT_OK;
+}
+
+TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* source, long long n)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (n < 0 || (n > 0 && (!target || !source))) return fail(h, TT_ERR_INVALID_ARG, "bad AddInto arguments");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    if (n == 0) return TT_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = aligned16(target) && aligned16(source);
+    const long long work = vec ? (n + 3) / 4 : n;
+    long long blocks = (work + 255) / 256;
+    const long long cap = static_cast<long long>(h->num_sms) * 16;
+    if (blocks > cap) blocks = cap;
+    if (vec) ew::add_into_kernel<true><<<static_cast<int>(blocks), 256, 0, st>>>(target, source, n);
+    else     ew::add_into_kernel<false><<<static_cast<int>(blocks), 256, 0, st>>>(target, source, n);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "AddInto launch");
+    return TT_OK;
+}
+
+TT_API int tt_broadcast_batch(int ra, const int* a_dims, const int* a_strides, int rb, const int* b_dims,
+                       const int* b_strides, int* rank, int* dims, int* a_bs, int* b_bs)
+{
+    if (ra < 0 || rb < 0 || !rank) return TT_ERR_INVALID_ARG;
+    const int r = ra > rb ? ra : rb;
+    *rank = r;
+    for (int j = 0; j < r; j++) {
+        const int axa = j - (r - ra), axb = j - (r - rb);
+        const int da = axa >= 0 ? a_dims[axa] : 1;
+        const int db = axb >= 0 ? b_dims[axb] : 1;
+        if (da != db && da != 1 && db != 1) return TT_ERR_INVALID_ARG;
+        const int od = da > db ? da : db;
+        dims[j] = od;
+        a_bs[j] = (axa >= 0 && da == od) ? a_strides[axa] : 0;
+        b_bs[j] = (axb >= 0 && db == od) ? b_strides[axb] : 0;
+    }
+    return TT_OK;
+}
+
+TT_API int tt_get_stats(tt_handle_t h, tt_stats* out)
+{
+    if (!h || !out) return TT_ERR_INVALID_ARG;
+    *out = h->stats;
+    return TT_OK;
+}
+
+TT_API int tt_reset_stats(tt_handle_t h)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    const long long ws = h->stats.workspace_bytes;
+    memset(&h->stats, 0, sizeof(h->stats));
+    h->stats.workspace_bytes = ws;
+    return TT_OK;
+}
+
+TT_API int tt_check(tt_handle_t h, void* stream)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(h, e, "stream synchronize");
+    unsigned int word = 0;
+    e = cudaMemcpy(&word, h->status, sizeof(word), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(h, e, "status read");
+    if (word != 0) {
+        snprintf(h->err, sizeof(h->err), "device-side bounded wait gave up (code %u)", word);
+        cudaMemset(h->status, 0, sizeof(word));
+        return TT_ERR_DEVICE_WAIT;
+    }
+    return TT_OK;
+}
+
+}  // extern "C"

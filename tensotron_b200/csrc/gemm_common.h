@@ -1,0 +1,51 @@
+// Shared host/device parameter blocks for the GEMM kernels.
+#pragma once
+#include <stdint.h>
+
+namespace tt {
+
+constexpr int MAX_BATCH_RANK = 8;
+
+// Epilogue fused into the store path: C = act(acc + bias[n]).
+struct Epilogue {
+    const float* bias;  // per output column, may be null
+    int act;            // TT_ACT_*
+};
+
+// Batch structure after the host collapsed mergeable axes.  The linear batch index
+// is decoded last-axis-fastest over dims[0..rank).
+struct BatchDesc {
+    int rank;
+    int dims[MAX_BATCH_RANK];
+    // any-stride kernels: element offsets per axis
+    int a_stride[MAX_BATCH_RANK];
+    int b_stride[MAX_BATCH_RANK];
+    // TMA kernels: axis -> (coordinate slot 0..2 or -1 for broadcast, multiplier)
+    signed char a_slot[MAX_BATCH_RANK];
+    signed char b_slot[MAX_BATCH_RANK];
+    int a_mult[MAX_BATCH_RANK];
+    int b_mult[MAX_BATCH_RANK];
+};
+
+struct GemmShape {
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int batch;          // number of matrices
+    long long work;     // batch * tiles_m * tiles_n
+};
+
+// Grouped raster: consecutive work items walk GROUP tile-rows down before moving one
+// tile-column right, so the CTAs in flight at one time share A and B panels in L2.
+__host__ __device__ inline void raster_tile(int t, int tiles_m, int tiles_n, int group, int& tm,
+                                            int& tn)
+{
+    const int per_group = group * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * group;
+    const int gsize = (tiles_m - first_m) < group ? (tiles_m - first_m) : group;
+    const int r = t - g * per_group;
+    tm = first_m + r % gsize;
+    tn = r / gsize;
+}
+
+}  // namespace tt

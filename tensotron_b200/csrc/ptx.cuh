@@ -1,0 +1,127 @@
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (bulk tensor copies, always
+// CTA-local destinations), and a bounded wait that gives up instead of hanging.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tt {
+
+// Device-side status word values (written once, first error wins).
+enum : unsigned int {
+    DEV_OK = 0,
+    DEV_WAIT_FULL = 1,    // consumer gave up waiting for a TMA-filled stage
+    DEV_WAIT_EMPTY = 2,   // producer gave up waiting for a free stage
+    DEV_WAIT_MMA = 3,     // epilogue gave up waiting for tcgen05 completion
+    DEV_WAIT_TMEM = 4,    // MMA issuer gave up waiting for a drained accumulator
+};
+
+// Upper bound on one wait, in nanoseconds of %globaltimer.  The longest legitimate
+// wait is one output tile of the largest supported K (tens of milliseconds).
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05).
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for `parity` on `bar`.  Returns false (after recording `code` in *status and
+// raising the CTA-wide abort flag) when the wait exceeds WAIT_LIMIT_NS or another
+// role of this CTA already aborted; callers then leave their loops.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  volatile uint32_t* cta_abort,
+                                                  unsigned int* status, unsigned int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xFFu) == 0) {
+            if (*cta_abort) return false;
+            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                *cta_abort = 1u;
+                if (status) atomicCAS(status, 0u, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// 5-D tiled TMA load, global -> this CTA's shared memory, completion on `bar`.
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ float4 lds128(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr));
+    return v;
+}
+
+}  // namespace tt

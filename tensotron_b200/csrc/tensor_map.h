@@ -1,0 +1,30 @@
+// Host-side construction of TMA descriptors (CUtensorMap) for float32 operands.
+// The driver entry point is resolved at run time so the library does not link
+// libcuda directly.  Descriptors are built per call and passed to kernels as
+// __grid_constant__ parameters, so they are baked into captured graph nodes.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tt {
+
+enum class Swizzle { None, B128 };
+
+// Describes one operand as a tensor of up to 5 dims, innermost first.
+struct OperandView {
+    const float* base;
+    int rank;                 // number of real dims (2..5); the rest are padded with size 1
+    uint64_t dim[5];          // extent in elements, innermost first
+    uint64_t stride_elems[5]; // element stride of dim i (stride_elems[0] must be 1)
+};
+
+// Returns false when the view cannot be expressed as a TMA descriptor (alignment).
+bool tma_compatible(const OperandView& v);
+
+// box = extents of the copied tile for dims 0 and 1 (dims 2.. use 1).
+// Returns cudaSuccess-like 0 on success, non-zero CUresult otherwise.
+int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uint32_t box1,
+                      Swizzle swz);
+
+}  // namespace tt

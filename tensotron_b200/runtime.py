@@ -1,0 +1,210 @@
+"""ctypes binding of libtensotron_gemm.so and a mirror of the reference runtime
+surface for the matmul path (src/Tensotron/TensorRuntime.cs:242-254: LaunchMatMul,
+LaunchMatMulBatched; :158-159, :332-338: AllowTf32 / SetCuBlasMathMode).
+
+Buffers are torch CUDA tensors (device memory plumbing only) or raw integer device
+addresses.  Errors follow the reference: a non-zero native status raises
+(InvalidOperationException there, TensotronGemmError here).
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtensotron_gemm.so")
+
+TT_MATH_FP32, TT_MATH_TF32, TT_MATH_3XTF32 = 0, 3, 4
+TT_ACT_NONE, TT_ACT_RELU, TT_ACT_TANH = 0, 1, 2
+ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, 0: 0, 1: 1, 2: 2}
+
+EXPORTS = [
+    "tt_version", "tt_create", "tt_destroy", "tt_last_error", "tt_set_math_mode", "tt_get_math_mode",
+    "tt_matmul", "tt_matmul_batched", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
+    "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
+    "tt_set_variant",
+]
+
+
+class TensotronGemmError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("tensotron_gemm status %d: %s" % (status, message))
+        self.status = status
+
+
+class Stats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_longlong) for n in
+                ("launches", "calls", "simt_tma", "tcgen05", "generic", "splitk", "workspace_bytes")]
+
+
+_lib = None
+
+
+def load_library(path=None):
+    """Loads the CUDA library.  No fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    path = path or LIB_PATH
+    if not os.path.exists(path):
+        raise ImportError(
+            "%s is missing: build it with `python -m tensotron_b200.build` "
+            "(there is no CPU or cuBLAS fallback on this path)" % path)
+    L = ctypes.CDLL(path)
+    vp, i, f, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+    ip = ctypes.POINTER(ctypes.c_int)
+    L.tt_version.restype = ctypes.c_char_p
+    L.tt_last_error.restype = ctypes.c_char_p
+    L.tt_last_error.argtypes = [vp]
+    L.tt_create.argtypes = [i, ctypes.c_size_t, ctypes.POINTER(vp)]
+    L.tt_destroy.argtypes = [vp]
+    L.tt_set_math_mode.argtypes = [vp, i]
+    L.tt_get_math_mode.argtypes = [vp, ip]
+    L.tt_matmul.argtypes = [vp, vp, vp, vp, vp] + [i] * 7
+    L.tt_matmul_batched.argtypes = [vp, vp, vp, vp, vp] + [i] * 9 + [ip, ip, ip]
+    L.tt_linear_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i]
+    L.tt_linear_bwd.argtypes = [vp, vp] + [vp] * 7 + [i, i, i, i]
+    L.tt_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, vp, i, i, f]
+    L.tt_adam_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, i]
+    L.tt_add_into.argtypes = [vp, vp, vp, vp, ll]
+    L.tt_broadcast_batch.argtypes = [i, ip, ip, i, ip, ip, ip, ip, ip, ip]
+    L.tt_get_stats.argtypes = [vp, ctypes.POINTER(Stats)]
+    L.tt_reset_stats.argtypes = [vp]
+    L.tt_check.argtypes = [vp, vp]
+    L.tt_set_variant.argtypes = [vp, i]
+    for name in EXPORTS:
+        if getattr(L, name).restype is ctypes.c_int:
+            pass
+    if path == LIB_PATH:
+        _lib = L
+    return L
+
+
+def _ptr(x):
+    """Device address of a torch CUDA float32/int32 tensor, or a raw integer / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x)
+    if not x.is_cuda:
+        raise TypeError("expected a CUDA tensor")
+    return ctypes.c_void_p(x.data_ptr())
+
+
+def _iarr(v):
+    v = [int(t) for t in v]
+    return (ctypes.c_int * max(1, len(v)))(*v)
+
+
+def broadcast_batch(a_dims, a_strides, b_dims, b_strides):
+    """BroadcastBatch (src/Tensotron/TensorOps.MatMulND.cs:11-31) through the C ABI."""
+    L = load_library()
+    ra, rb = len(a_dims), len(b_dims)
+    r = max(ra, rb)
+    dims, a_bs, b_bs = _iarr([0] * r), _iarr([0] * r), _iarr([0] * r)
+    rank = ctypes.c_int(0)
+    rc = L.tt_broadcast_batch(ra, _iarr(a_dims), _iarr(a_strides), rb, _iarr(b_dims), _iarr(b_strides),
+                              ctypes.byref(rank), dims, a_bs, b_bs)
+    if rc:
+        raise TensotronGemmError(rc, "Cannot broadcast batch dims %s with %s" % (list(a_dims), list(b_dims)))
+    return list(dims)[:r], list(a_bs)[:r], list(b_bs)[:r]
+
+
+class TensorRuntime:
+    """The CUDA-backend runtime surface of the matmul path, one handle per device."""
+
+    def __init__(self, device=0, workspace_bytes=0):
+        self._L = load_library()
+        self._h = ctypes.c_void_p()
+        self.device = device
+        rc = self._L.tt_create(device, workspace_bytes, ctypes.byref(self._h))
+        if rc:
+            raise TensotronGemmError(rc, "tt_create failed (needs a sm_100 device)")
+        self._stream = None
+
+    # -- lifetime ---------------------------------------------------------------
+    def Dispose(self):
+        if self._h:
+            self._L.tt_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.Dispose()
+        except Exception:
+            pass
+
+    def _ck(self, rc):
+        if rc:
+            raise TensotronGemmError(rc, self._L.tt_last_error(self._h).decode())
+
+    def _st(self, stream):
+        """CUstream for the call: explicit, else torch's current stream on this device."""
+        if stream is not None:
+            return ctypes.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
+        import torch
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # -- math mode (src/Tensotron/TensorRuntime.cs:158-159, :332-338) --------------
+    @property
+    def AllowTf32(self):
+        return self.GetMathMode() == TT_MATH_TF32
+
+    @AllowTf32.setter
+    def AllowTf32(self, value):
+        self.SetCuBlasMathMode(TT_MATH_TF32 if value else TT_MATH_FP32)
+
+    def SetCuBlasMathMode(self, mode):
+        self._ck(self._L.tt_set_math_mode(self._h, int(mode)))
+
+    def GetMathMode(self):
+        m = ctypes.c_int(0)
+        self._ck(self._L.tt_get_math_mode(self._h, ctypes.byref(m)))
+        return m.value
+
+    def SetVariant(self, variant):
+        self._ck(self._L.tt_set_variant(self._h, int(variant)))
+
+    # -- launches ----------------------------------------------------------------
+    def LaunchMatMul(self, a, b, c, M, N, K, aMs, aKs, bKs, bNs, stream=None):
+        self._ck(self._L.tt_matmul(self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c),
+                                   M, N, K, aMs, aKs, bKs, bNs))
+
+    def LaunchMatMulBatched(self, a, b, c, batchCount, M, N, K, aMs, aKs, bKs, bNs,
+                            batchDims, aBatchStrides, bBatchStrides, stream=None):
+        self._ck(self._L.tt_matmul_batched(
+            self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c), batchCount, M, N, K,
+            aMs, aKs, bKs, bNs, len(batchDims), _iarr(batchDims), _iarr(aBatchStrides),
+            _iarr(bBatchStrides)))
+
+    def LaunchLinearForward(self, x, w, bias, y, M, N, K, act=0, stream=None):
+        self._ck(self._L.tt_linear_fwd(self._h, self._st(stream), _ptr(x), _ptr(w), _ptr(bias),
+                                       _ptr(y), M, N, K, ACT[act]))
+
+    def LaunchLinearBackward(self, x, w, y, dy, dx, dw, dbias, M, N, K, act=0, stream=None):
+        self._ck(self._L.tt_linear_bwd(self._h, self._st(stream), _ptr(x), _ptr(w), _ptr(y), _ptr(dy),
+                                       _ptr(dx), _ptr(dw), _ptr(dbias), M, N, K, ACT[act]))
+
+    def LaunchSoftmaxCrossEntropy(self, logits, labels, dlogits, loss, rows, classes, scale, stream=None):
+        self._ck(self._L.tt_softmax_cross_entropy(self._h, self._st(stream), _ptr(logits), _ptr(labels),
+                                                  _ptr(dlogits), _ptr(loss), rows, classes, scale))
+
+    def LaunchAdam(self, p, g, m, v, adv, n, b1=0.9, b2=0.999, lr=1e-3, eps=1e-8,
+                   coupledWd=0.0, decoupledFactor=1.0, advance=True, stream=None):
+        self._ck(self._L.tt_adam_step(self._h, self._st(stream), _ptr(p), _ptr(g), _ptr(m), _ptr(v),
+                                      _ptr(adv), n, b1, b2, lr, eps, coupledWd, decoupledFactor,
+                                      1 if advance else 0))
+
+    def LaunchAddInto(self, target, source, n, stream=None):
+        self._ck(self._L.tt_add_into(self._h, self._st(stream), _ptr(target), _ptr(source), n))
+
+    # -- counters / checks ---------------------------------------------------------
+    def Stats(self):
+        s = Stats()
+        self._ck(self._L.tt_get_stats(self._h, ctypes.byref(s)))
+        return {n: getattr(s, n) for n, _ in Stats._fields_}
+
+    def ResetCounters(self):
+        self._ck(self._L.tt_reset_stats(self._h))
+
+    def Check(self, stream=None):
+        """Synchronises and raises if a bounded device-side wait gave up."""
+        self._ck(self._L.tt_check(self._h, self._st(stream)))

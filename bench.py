@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Headline benchmark: strict-FP32 SGEMM TFLOP/s on the square 16384^3 problem, sharded
+along M over the GPUs of one box (one process per GPU, no data-path collective).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one C = A.B over this rank's M-shard (rows = 16384/N) through the C-ABI
+library.  `value` is whole-job TFLOP/s with operands resident in HBM; `e2e` is the same
+metric through the same call with pinned HOST operands (H2D of A-shard and B, D2H of the
+C-shard inside the timed region).  Rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_TOTAL = int(os.environ.get("TT_BENCH_N", "16384"))
+METRIC = "sgemm_fp32_tflops"
+UNIT = "TFLOP/s"
+
+# DRAM bytes per launch of sgemm_simt_kernel from an ncu capture (see profiles/); None until
+# a capture of this kernel exists.  Keyed by problem edge.
+NCU_TRAFFIC_BYTES = {}
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            # the upper half of the samples are the ones taken under load
+            sm_sorted = sorted(sm)
+            out["sm_mhz"] = statistics.median(sm_sorted[len(sm_sorted) // 2:])
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def cpu_reference_sample(steps, warmup, rows_hint=None):
+    """Times the CPU restatement of the reference's SIMD matmul (all host threads) on a
+    bounded row-slab of the same 16384^3 workload.  Returns (tflops, info dict)."""
+    import numpy as np
+
+    import oracle
+    threads = oracle.set_threads("auto")
+    n = N_TOTAL
+    rng = np.random.default_rng(0)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    rows = rows_hint or max(threads, 8)
+    # grow the slab until one step is at least ~1.5 s of work (bounded by 16 doublings)
+    a = rng.uniform(-1, 1, (rows, n)).astype(np.float32)
+    for _ in range(16):
+        t0 = time.perf_counter()
+        oracle.matmul2d(a, b, rows, n, n, n, 1, n, 1)
+        dt = time.perf_counter() - t0
+        if dt >= 1.5 or rows >= n:
+            break
+        rows = min(n, rows * 2)
+        a = rng.uniform(-1, 1, (rows, n)).astype(np.float32)
+    for _ in range(warmup):
+        oracle.matmul2d(a, b, rows, n, n, n, 1, n, 1)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.matmul2d(a, b, rows, n, n, n, 1, n, 1)
+    dt = (time.perf_counter() - t0) / steps
+    tflops = 2.0 * rows * n * n / dt / 1e12
+    info = {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": "rows %d of %d (x %d x %d), %d step(s) of %.2f s, C restatement of "
+                      "CpuKernels.MatMul2D Axpy path, row-parallel" % (rows, n, n, n, steps, dt)}
+    return tflops, dt, info
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    tflops, dt, info = cpu_reference_sample(steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "sgemm_fp32 %d^3 (C = A.B, row-major, uniform[-1,1))" % N_TOTAL,
+                   "note": "reference = CPU restatement of the C# SIMD backend (no .NET on this box); "
+                           "each step is a bounded row-slab of the workload"},
+        "cpu_baseline": info,
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    rank = env_int("RANK", 0)
+    world = env_int("WORLD_SIZE", 1)
+    local_rank = env_int("LOCAL_RANK", 0)
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from tensotron_b200.runtime import TT_MATH_FP32, TensorRuntime
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    rt = TensorRuntime(local_rank)          # raises if the CUDA library is missing: no fallback
+    rt.SetCuBlasMathMode(TT_MATH_FP32)
+    n = N_TOTAL
+    if n % world != 0:
+        raise SystemExit("world size must divide %d" % n)
+    rows = n // world
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    a = torch.rand((rows, n), generator=gen, device="cuda") * 2 - 1     # this rank's M-shard of A
+    gen.manual_seed(99)
+    b = torch.rand((n, n), generator=gen, device="cuda") * 2 - 1        # B replicated
+    c = torch.empty((rows, n), device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        rt.LaunchMatMul(a, b, c, rows, n, n, n, 1, n, 1)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    rt.ResetCounters()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = rt.Stats()["launches"]
+    clocks = sampler.stop() if rank == 0 else None
+    rt.Check()
+
+    # ---- end to end: pinned host operands, copies inside the timed region ----
+    ha = torch.empty((rows, n), pin_memory=True).copy_(a)
+    hb = torch.empty((n, n), pin_memory=True).copy_(b)
+    hc = torch.empty((rows, n), pin_memory=True)
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        a.copy_(ha, non_blocking=True)
+        b.copy_(hb, non_blocking=True)
+        rt.LaunchMatMul(a, b, c, rows, n, n, n, 1, n, 1)
+        hc.copy_(c, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        flop_total = 2.0 * n * n * n
+        ms_per_step = ms / args.steps
+        value = flop_total / (ms_per_step * 1e-3) / 1e12
+        e2e_value = flop_total / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        props = torch.cuda.get_device_properties(local_rank)
+        sms = props.multi_processor_count
+        max_mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
+        peak = sms * 128 * 2 * max_mhz * 1e6 / 1e12           # FP32 FFMA lanes x 2 flop x clock
+        per_gpu = value / world
+        roof = {
+            "bound": "fp32_ffma", "achieved": per_gpu, "peak": peak, "unit": UNIT,
+            "frac": per_gpu / peak, "traffic": NCU_TRAFFIC_BYTES.get(n),
+            "peak_source": "derived: %d SMs x 128 FP32 lanes x 2 x %.0f MHz (max SM clock); the "
+                           "measured-peaks file has no FP32 SIMT figure" % (sms, max_mhz),
+            "kernel": "sgemm_simt_kernel<K-major A, N-major B>",
+            "algorithmic_flops_per_launch": 2.0 * rows * n * n,
+        }
+        if clocks and clocks.get("sm_mhz"):
+            roof["frac_at_sampled_clock"] = per_gpu / (sms * 128 * 2 * clocks["sm_mhz"] * 1e6 / 1e12)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "sgemm_fp32 %d^3 (C = A.B, row-major, uniform[-1,1)), strict FP32, "
+                                   "sharded along M over %d GPU(s)" % (n, world),
+                       "rows_per_gpu": rows, "l2": "operands (%.0f MiB A-shard + %.0f MiB B) exceed the 126 MB L2"
+                       % (rows * n * 4 / 2 ** 20, n * n * 4 / 2 ** 20)},
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (rows * n + n * n) * 4,
+                    "d2h_bytes_per_step": rows * n * 4, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            _, _, info = cpu_reference_sample(1, 0)
+            line["cpu_baseline"] = info
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,7 +52,7 @@ __device__ __forceinline__ float apply_act(float v, int act)
 }
 
 template <bool A_KMAJ, bool B_KMAJ>
-__global__ void __maxnreg__(224)
+__global__ void __launch_bounds__(THREADS, 1)
 sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b, const Params p)
 {

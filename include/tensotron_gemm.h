@@ -147,7 +147,9 @@ TT_API int tt_reset_stats(tt_handle_t h);
  * synchronises the stream; it is for tests and debugging, not the hot path. */
 TT_API int tt_check(tt_handle_t h, void* stream);
 
-/* Forces a kernel variant for A/B measurements: 0 auto, 1 generic, 2 SIMT-TMA. */
+/* Forces a kernel variant for A/B measurements: 0 auto, 1 any-stride kernel,
+ * 2 TMA-fed FFMA kernel with 256x128 tiles, 3 the same with 128x128 tiles,
+ * 4 / 5 tcgen05 kernel (TF32 modes only) with 128- / 256-row tiles. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 #ifdef __cplusplus

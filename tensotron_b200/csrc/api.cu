@@ -21,7 +21,7 @@ struct tt_handle_s {
     int device;
     int num_sms;
     int math_mode;
-    int variant;  // 0 auto, 1 generic, 2 simt-tma
+    int variant;  // 0 auto, 1 generic, 2 simt-tma 256x128, 3 simt-tma 128x128, 4/5 tcgen05 tile height 128/256
     uint8_t* workspace;
     size_t workspace_bytes;
     unsigned int* status;  // device status word
@@ -197,21 +197,38 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     return TT_OK;
 }
 
-template <bool AK, bool BK_>
+template <int TM, bool AK, bool BK_>
 int launch_simt_t(tt_handle_t h, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb,
                   const simt::Params& p, int grid)
 {
-    auto kern = simt::sgemm_simt_kernel<AK, BK_>;
-    kern<<<grid, simt::THREADS, simt::SMEM_BYTES, st>>>(ma, mb, p);
+    auto kern = simt::sgemm_simt_kernel<TM, AK, BK_>;
+    kern<<<grid, simt::THREADS, simt::Cfg<TM, AK, BK_>::SMEM_BYTES, st>>>(ma, mb, p);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "simt gemm launch");
     return TT_OK;
 }
 
+// Tile choice for the FFMA kernel: 256x128 tiles (16x8 per thread) run ~1.5x the rate
+// of 128x128 tiles (8x8 per thread, shared-memory-return bound) but quantise worse on
+// small grids.  Estimated time = waves x per-tile cost; the cheaper one wins.  The
+// choice depends on the shape and the SM count only.
+int pick_tm(const tt_handle_t h, int M, int N, int batch)
+{
+    const auto waves = [&](int bm) {
+        const long long work = static_cast<long long>(batch) * ((M + bm - 1) / bm) * ((N + simt::BN - 1) / simt::BN);
+        return (work + h->num_sms - 1) / h->num_sms;
+    };
+    const double t16 = static_cast<double>(waves(256)) * 2.0 / 0.85;
+    const double t8 = static_cast<double>(waves(128)) * 1.0 / 0.55;
+    return t16 <= t8 ? 16 : 8;
+}
+
 // Returns TT_ERR_UNSUPPORTED (without touching h->err) when the operands cannot be
 // expressed as TMA descriptors; the caller then uses the any-stride kernel.
-int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+template <int TM>
+int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 {
+    constexpr int BM = 16 * TM;
     OperandView va, vb;
     const int ak = operand_view(g.a, g.M, g.K, g.aMs, g.aKs, va);
     const int bk = operand_view(g.b, g.N, g.K, g.bNs, g.bKs, vb);
@@ -224,15 +241,15 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     if (!tma_compatible(va) || !tma_compatible(vb)) return TT_ERR_UNSUPPORTED;
 
     CUtensorMap ma, mb;
-    int r = ak ? encode_tensor_map(&ma, va, simt::BK, simt::BM, Swizzle::B128)
-               : encode_tensor_map(&ma, va, simt::BM, simt::BK, Swizzle::None);
+    int r = ak ? encode_tensor_map(&ma, va, simt::BK, BM, Swizzle::B128)
+               : encode_tensor_map(&ma, va, BM, simt::BK, Swizzle::None);
     if (r != 0) return TT_ERR_UNSUPPORTED;
     r = bk ? encode_tensor_map(&mb, vb, simt::BK, simt::BN, Swizzle::B128)
            : encode_tensor_map(&mb, vb, simt::BN, simt::BK, Swizzle::None);
     if (r != 0) return TT_ERR_UNSUPPORTED;
 
     p.shape.M = g.M; p.shape.N = g.N; p.shape.K = g.K;
-    p.shape.tiles_m = (g.M + simt::BM - 1) / simt::BM;
+    p.shape.tiles_m = (g.M + BM - 1) / BM;
     p.shape.tiles_n = (g.N + simt::BN - 1) / simt::BN;
     p.shape.batch = g.batch_count;
     p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
@@ -242,14 +259,22 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
     const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
     int rc;
-    if (ak && bk) rc = launch_simt_t<true, true>(h, st, ma, mb, p, grid);
-    else if (ak && !bk) rc = launch_simt_t<true, false>(h, st, ma, mb, p, grid);
-    else if (!ak && !bk) rc = launch_simt_t<false, false>(h, st, ma, mb, p, grid);
-    else rc = launch_simt_t<false, true>(h, st, ma, mb, p, grid);
+    if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid);
+    else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid);
+    else if (!ak && !bk) rc = launch_simt_t<TM, false, false>(h, st, ma, mb, p, grid);
+    else rc = launch_simt_t<TM, false, true>(h, st, ma, mb, p, grid);
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
     return TT_OK;
+}
+
+int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+{
+    int tm = pick_tm(h, g.M, g.N, g.batch_count);
+    if (h->variant == 2) tm = 16;
+    if (h->variant == 3) tm = 8;
+    return tm == 16 ? try_launch_simt_tm<16>(h, st, g) : try_launch_simt_tm<8>(h, st, g);
 }
 
 int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
@@ -264,14 +289,16 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     const long long vol = static_cast<long long>(g.M) * g.N * (g.K > 0 ? g.K : 1);
     if (g.K > 0 && h->variant != 1) {
         if (h->math_mode != TT_MATH_FP32) {
+            int n_launch = 0;
             const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
                                             g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,
                                             g.batch.dims, g.batch.as, g.batch.bs, g.epi, h->num_sms,
-                                            h->status);
-            if (rc == TT_OK) { h->stats.launches++; h->stats.tcgen05++; return TT_OK; }
+                                            h->status, h->workspace, h->workspace_bytes, &n_launch,
+                                            h->variant == 4 ? 1 : h->variant == 5 ? 2 : 0);
+            if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
             if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
         }
-        if (h->variant == 2 || vol >= TMA_MIN_FLOP_ELEMS) {
+        if (h->variant == 2 || h->variant == 3 || vol >= TMA_MIN_FLOP_ELEMS) {
             const int rc = try_launch_simt(h, st, g);
             if (rc != TT_ERR_UNSUPPORTED) return rc;
         }
@@ -281,16 +308,29 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 
 // Per-device kernel attributes, set once at handle creation so that no compute call
 // does lazy set-up work (which could not be captured into a graph).
-cudaError_t init_kernels()
+template <int TM, bool AK, bool BK_>
+cudaError_t init_simt_one()
+{
+    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                simt::Cfg<TM, AK, BK_>::SMEM_BYTES);
+}
+
+template <int TM>
+cudaError_t init_simt_tm()
 {
     cudaError_t e;
-    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    if ((e = init_simt_one<TM, true, true>()) != cudaSuccess) return e;
+    if ((e = init_simt_one<TM, true, false>()) != cudaSuccess) return e;
+    if ((e = init_simt_one<TM, false, true>()) != cudaSuccess) return e;
+    return init_simt_one<TM, false, false>();
+}
+
+cudaError_t init_kernels()
+{
+    cudaError_t e = init_simt_tm<8>();
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, simt::SMEM_BYTES);
+    e = init_simt_tm<16>();
     if (e != cudaSuccess) return e;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
@@ -375,7 +415,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 2) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 5) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }

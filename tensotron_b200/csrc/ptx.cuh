@@ -83,12 +83,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
                                                   unsigned int* status, unsigned int code)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    // The timer is only consulted once a wait has been spinning for a while: reading
+    // %globaltimer is slow and most waits end within a few polls.
+    unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFFu) == 0) {
+        if ((++spins & 0x3FFu) == 0) {
             if (*cta_abort) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > WAIT_LIMIT_NS) {
                 *cta_abort = 1u;
                 if (status) atomicCAS(status, 0u, code);
                 return false;

@@ -1,23 +1,35 @@
-// Strict-FP32 SGEMM for sm_100a: SIMT FFMA tiles fed by TMA.
+// Strict-FP32 SGEMM for sm_100a: SIMT FMA tiles fed by TMA.
 //
-// One persistent CTA per SM walks a grouped raster of 128x128 output tiles.  A
-// dedicated producer warp streams 128x32 (A) and 32x128 (B) float tiles into a
-// shared-memory ring with TMA; eight consumer warps (8x8 accumulators per thread)
-// read them with 128-bit shared loads and issue FFMAs only.  Stages are handed over
-// with mbarriers (full: TMA transaction bytes; empty: one arrival per consumer
-// warp), so the main loop has no CTA-wide barrier and the ring keeps filling across
-// tile boundaries while the previous tile's epilogue stores.
+// One persistent CTA per SM (8 warps) walks a grouped raster of (16*TM)x128 output
+// tiles, TM = 16 (256x128 tile, 16x8 accumulators per thread) or TM = 8 (128x128, 8x8).
+// Thread 0 streams (16*TM)x32 (A) and 32x128 (B) float tiles into a shared-memory ring
+// with TMA, a few k-steps ahead of the consumers; all warps read the tiles with 128-bit
+// shared loads and issue packed two-wide FP32 FMAs (fma.rn.f32x2).  Stages are handed
+// over with mbarriers (full: TMA transaction bytes; empty: one arrival per warp), and
+// the ring keeps filling across tile boundaries while the previous tile's epilogue
+// stores.
 //
-// Operand layouts.  Each operand is either contiguous along K ("K-major") or along
-// its M/N axis ("MN-major"); TMA copies tiles in their native order:
-//   K-major : smem [128 rows][32 k], 128-byte rows, hardware 128B swizzle.  A thread
-//             reads float4 = 4 consecutive k of one row; the 16-byte chunk index is
-//             XORed with (row & 7), and thread->row assignment is interleaved so the
-//             rows one warp instruction touches all differ in (row & 7): conflict-free.
-//   MN-major: smem [32 k][128 cols], no swizzle.  A thread reads float4 = 4 adjacent
-//             rows/cols of one k.
-// Summation order over K is fixed (ascending k, one accumulator per output), so the
-// result does not depend on the grid size or on which SM ran a tile.
+// Why 16x8 per thread and packed FMAs: on this SM the FP32 pipe retires 128 FMAs per
+// clock, one warp instruction per scheduler per clock, and shared memory returns
+// 128 B/clk.  With scalar FFMA every non-FMA instruction steals an FMA issue slot and an
+// 8x8 register tile needs the whole shared-memory return bandwidth.  A 16x8 tile needs
+// 75 % of it, and the two-wide FMA halves the FMA issue slots, leaving room for the
+// loads.  128 accumulators plus fragments need > 170 registers, hence exactly 8 warps
+// (2 per scheduler partition) and no separate producer warp.
+//
+// Operand layouts.  The main loop wants both operands "MN-major" in shared memory:
+// [32 k][rows] with the M (or N) index contiguous, so that a float4 holds 4 adjacent
+// rows/columns of one k and adjacent register pairs feed the packed FMA directly.
+//   MN-major operand in global memory (A of a TN product, B of NN/TN): TMA lands the
+//       tile in exactly that order; the main loop reads the TMA stage itself.
+//   K-major operand (A of NN/NT, B of NT): TMA lands [rows][32 k] (128-byte rows,
+//       hardware 128B swizzle).  While the FMAs of k-tile i run, the warps transpose
+//       k-tile i+1 through registers (4 LDS.128 + 4 STS.128 per 4x4 block) into one of
+//       two MN-major buffers whose rows are padded by 16 bytes; one CTA barrier per
+//       k-tile (every 8192 FMA cycles) separates writers from readers.
+// Summation order over K is fixed (ascending k, one accumulator per output, fused
+// multiply-add), so the result does not depend on the tile shape, the grid size or the
+// SM that ran a tile.
 #pragma once
 #include "gemm_common.h"
 #include "ptx.cuh"
@@ -25,15 +37,38 @@
 namespace tt {
 namespace simt {
 
-constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 4;
-constexpr int A_TILE_BYTES = BM * BK * 4;  // 16 KiB
-constexpr int B_TILE_BYTES = BN * BK * 4;  // 16 KiB
-constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int CONSUMER_WARPS = 8;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int BN = 128, BK = 32;
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
 constexpr int RASTER_GROUP = 8;
+constexpr int G_UNROLL = 2;  // k groups (of 4) unrolled in the main loop; bounds code size
+
+template <int TM, bool A_KMAJ, bool B_KMAJ>
+struct Cfg {
+    static constexpr int BM = 16 * TM;
+    static constexpr int RAW_A = BM * BK * 4;
+    static constexpr int RAW_B = BN * BK * 4;
+    static constexpr int STAGE_BYTES = RAW_A + RAW_B;
+    // Row pitch (bytes) of the MN-major tile the main loop reads: the TMA stage itself,
+    // or the padded transposed copy of a K-major tile.
+    static constexpr int ROWB_A = A_KMAJ ? BM * 4 + 16 : BM * 4;
+    static constexpr int ROWB_B = B_KMAJ ? BN * 4 + 16 : BN * 4;
+    static constexpr int TA_BYTES = A_KMAJ ? BK * ROWB_A : 0;
+    static constexpr int TB_BYTES = B_KMAJ ? BK * ROWB_B : 0;
+    static constexpr bool HAS_T = A_KMAJ || B_KMAJ;
+    static constexpr bool ALL_T = A_KMAJ && B_KMAJ;
+    static constexpr int BUDGET = 227 * 1024 - 1024 /*align slack*/ - 512 /*barriers, cursor*/;
+    static constexpr int FIT = (BUDGET - 2 * (TA_BYTES + TB_BYTES)) / STAGE_BYTES;
+    static constexpr int STAGES = FIT > 4 ? 4 : FIT;
+    // How many k-tiles ahead of the consumers the producer runs.  A stage whose tiles
+    // are all transposed is released one k-tile earlier than one the main loop reads.
+    static constexpr int DIST = ALL_T ? STAGES : STAGES - 1;
+    static constexpr int OFF_TA = STAGES * STAGE_BYTES;
+    static constexpr int OFF_TB = OFF_TA + 2 * TA_BYTES;
+    static constexpr int OFF_BAR = (OFF_TB + 2 * TB_BYTES + 127) & ~127;
+    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+    static_assert(STAGES >= 2, "shared-memory budget");
+};
 
 struct Params {
     GemmShape shape;
@@ -51,225 +86,303 @@ __device__ __forceinline__ float apply_act(float v, int act)
     return v;
 }
 
-template <bool A_KMAJ, bool B_KMAJ>
+// Cursor over this CTA's (tile, k-tile) sequence; used by the producer thread, which
+// runs DIST steps ahead of the consumers.  Lives in shared memory.
+struct LoadCursor {
+    long long w;
+    int kt;
+    int m0, n0;
+    int ca0, ca1, ca2, cb0, cb1, cb2;
+    uint32_t stage, use;  // stage to fill next; how many times the ring has wrapped
+    int ok;
+};
+
+template <int BM>
+__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat)
+{
+    const int bidx = static_cast<int>(cur.w / tiles_per_mat);
+    const int t = static_cast<int>(cur.w - static_cast<long long>(bidx) * tiles_per_mat);
+    int tm, tn;
+    raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
+    cur.m0 = tm * BM;
+    cur.n0 = tn * BN;
+    cur.ca0 = cur.ca1 = cur.ca2 = 0;
+    cur.cb0 = cur.cb1 = cur.cb2 = 0;
+    int br = bidx;
+    for (int ax = p.batch.rank - 1; ax >= 0; ax--) {
+        const int d = p.batch.dims[ax];
+        const int bi = br % d;
+        br /= d;
+        const int sa = p.batch.a_slot[ax], sb = p.batch.b_slot[ax];
+        if (sa == 0) cur.ca0 += bi * p.batch.a_mult[ax];
+        else if (sa == 1) cur.ca1 += bi * p.batch.a_mult[ax];
+        else if (sa == 2) cur.ca2 += bi * p.batch.a_mult[ax];
+        if (sb == 0) cur.cb0 += bi * p.batch.b_mult[ax];
+        else if (sb == 1) cur.cb1 += bi * p.batch.b_mult[ax];
+        else if (sb == 2) cur.cb2 += bi * p.batch.b_mult[ax];
+    }
+}
+
+// Transposes one K-major TMA tile ([ROWS][32 k], 128B-swizzled) into an MN-major tile
+// ([32 k][ROWS], row pitch ROWB bytes).  Each thread moves 4x4 blocks: block (R, c) =
+// rows 4R..4R+3, k 4c..4c+3.  A quarter warp covers 4 chunks x 2 row groups, which
+// makes the swizzled reads conflict-free and the padded writes 2-way.
+template <int ROWS, int ROWB>
+__device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst, int warp, int lane)
+{
+    constexpr int ITER = ROWS / 128;  // blocks per thread
+#pragma unroll
+    for (int u = 0; u < ITER; u++) {
+        const int R = (ROWS == 256 ? warp * 8 : (warp & 3) * 8) + (lane >> 2);
+        const int c = (ROWS == 256 ? u * 4 : (warp >> 2) * 4) + (lane & 3);
+        const int rsw = (R & 1) << 2;  // (4R + i) & 7 == rsw + i
+        float4 r[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            r[i] = *reinterpret_cast<const float4*>(raw + (4 * R + i) * 128 + ((c ^ (rsw + i)) << 4));
+        uint8_t* out = dst + (4 * c) * ROWB + R * 16;
+        *reinterpret_cast<float4*>(out) = make_float4(r[0].x, r[1].x, r[2].x, r[3].x);
+        *reinterpret_cast<float4*>(out + ROWB) = make_float4(r[0].y, r[1].y, r[2].y, r[3].y);
+        *reinterpret_cast<float4*>(out + 2 * ROWB) = make_float4(r[0].z, r[1].z, r[2].z, r[3].z);
+        *reinterpret_cast<float4*>(out + 3 * ROWB) = make_float4(r[0].w, r[1].w, r[2].w, r[3].w);
+    }
+}
+
+template <int TM, bool A_KMAJ, bool B_KMAJ>
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b, const Params p)
 {
+    using C = Cfg<TM, A_KMAJ, B_KMAJ>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int HALVES = TM / 8;  // 8-row halves of the thread tile
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
     uint64_t* empty_bar = full_bar + STAGES;
     volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
+    LoadCursor& cur = *reinterpret_cast<LoadCursor*>(smem + C::OFF_BAR + 128);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], CONSUMER_WARPS);
-        }
-        *cta_abort = 0u;
-        fence_mbar_init();
-    }
-    __syncthreads();
-
     const int k_tiles = (p.shape.K + BK - 1) / BK;
     const int tiles_per_mat = p.shape.tiles_m * p.shape.tiles_n;
 
-    if (warp == CONSUMER_WARPS) {
-        // ------------------------------ producer ------------------------------
-        if (lane == 0) {
-            prefetch_tensormap(&map_a);
-            prefetch_tensormap(&map_b);
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            for (long long w = blockIdx.x; ok && w < p.shape.work; w += gridDim.x) {
-                const int bidx = static_cast<int>(w / tiles_per_mat);
-                const int t = static_cast<int>(w - static_cast<long long>(bidx) * tiles_per_mat);
-                int tm, tn;
-                raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
-                int ca[3] = {0, 0, 0}, cb[3] = {0, 0, 0};
-                int br = bidx;
-                for (int ax = p.batch.rank - 1; ax >= 0; ax--) {
-                    const int d = p.batch.dims[ax];
-                    const int bi = br % d;
-                    br /= d;
-                    if (p.batch.a_slot[ax] >= 0) ca[p.batch.a_slot[ax]] += bi * p.batch.a_mult[ax];
-                    if (p.batch.b_slot[ax] >= 0) cb[p.batch.b_slot[ax]] += bi * p.batch.b_mult[ax];
-                }
-                const int m0 = tm * BM, n0 = tn * BN;
-                for (int kt = 0; kt < k_tiles; kt++) {
-                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, cta_abort, p.status,
-                                           DEV_WAIT_EMPTY)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* sa = smem + stage * STAGE_BYTES;
-                    uint8_t* sb = sa + A_TILE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-                    const int k0 = kt * BK;
-                    if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[stage], k0, m0, ca[0], ca[1], ca[2]);
-                    else        tma_load_5d(sa, &map_a, &full_bar[stage], m0, k0, ca[0], ca[1], ca[2]);
-                    if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[stage], k0, n0, cb[0], cb[1], cb[2]);
-                    else        tma_load_5d(sb, &map_b, &full_bar[stage], n0, k0, cb[0], cb[1], cb[2]);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                }
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], WARPS);
+        }
+        *cta_abort = 0u;
+        fence_mbar_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        cur.w = blockIdx.x;
+        cur.kt = 0;
+        cur.stage = 0;
+        cur.use = 0;
+        cur.ok = 1;
+    }
+    __syncthreads();
+
+    // Issues the TMA loads of the cursor's (tile, k-tile) into cur.stage and advances
+    // (thread 0 only; its state lives in shared memory so it costs no registers).
+    auto produce_one = [&]() {
+        if (cur.w >= p.shape.work || !cur.ok) return;
+        if (cur.kt == 0) cursor_set_tile<C::BM>(cur, p, tiles_per_mat);
+        const uint32_t ps = cur.stage;
+        if (cur.use > 0) {
+            // the stage was used before: wait until all warps released that use
+            if (!mbar_wait_bounded(&empty_bar[ps], (cur.use - 1) & 1u, cta_abort, p.status,
+                                   DEV_WAIT_EMPTY)) {
+                cur.ok = 0;
+                return;
             }
         }
-        return;
+        uint8_t* sa = smem + ps * C::STAGE_BYTES;
+        uint8_t* sb = sa + C::RAW_A;
+        mbar_arrive_expect_tx(&full_bar[ps], C::STAGE_BYTES);
+        const int k0 = cur.kt * BK;
+        if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[ps], k0, cur.m0, cur.ca0, cur.ca1, cur.ca2);
+        else        tma_load_5d(sa, &map_a, &full_bar[ps], cur.m0, k0, cur.ca0, cur.ca1, cur.ca2);
+        if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, cur.n0, cur.cb0, cur.cb1, cur.cb2);
+        else        tma_load_5d(sb, &map_b, &full_bar[ps], cur.n0, k0, cur.cb0, cur.cb1, cur.cb2);
+        if (ps + 1 == STAGES) { cur.stage = 0; cur.use++; } else { cur.stage = ps + 1; }
+        if (++cur.kt == k_tiles) { cur.kt = 0; cur.w += gridDim.x; }
+    };
+
+    if (tid == 0) {
+#pragma unroll 1
+        for (int i = 0; i < C::DIST; i++) produce_one();
     }
 
-    // -------------------------------- consumers --------------------------------
-    const int wm = warp >> 1;  // 0..3 -> 32 rows each
-    const int wn = warp & 1;   // 0..1 -> 64 cols each
-    const int ty = lane >> 3;  // 0..3
-    const int tx = lane & 7;   // 0..7
+    // Transposes the K-major tiles of TMA stage `s` into transposed buffer `tb`.
+    auto transpose_stage = [&](uint32_t s, uint32_t tb) {
+        const uint8_t* raw = smem + s * C::STAGE_BYTES;
+        if (A_KMAJ)
+            transpose_tile<C::BM, C::ROWB_A>(raw, smem + C::OFF_TA + tb * C::TA_BYTES, warp, lane);
+        if (B_KMAJ)
+            transpose_tile<BN, C::ROWB_B>(raw + C::RAW_A, smem + C::OFF_TB + tb * C::TB_BYTES, warp, lane);
+    };
 
-    // Per-thread byte offsets inside a stage (see the layout notes at the top).
-    int off_a[4];  // K-major A: index q = low two bits of the (compile-time part of the) chunk
-    int off_b[8];  // K-major B: index = k chunk
-    int off_am = 0, off_bm = 0;
-    if (A_KMAJ) {
-#pragma unroll
-        for (int q = 0; q < 4; q++) off_a[q] = (wm * 32 + ty) * 128 + ((q ^ ty) << 4);
-    } else {
-        off_am = (wm * 32 + ty * 4) * 4;
-    }
-    if (B_KMAJ) {
-#pragma unroll
-        for (int c = 0; c < 8; c++) off_b[c] = A_TILE_BYTES + (wn * 64 + tx) * 128 + ((c ^ tx) << 4);
-    } else {
-        off_bm = A_TILE_BYTES + (wn * 64 + tx * 4) * 4;
+    uint32_t stage = 0, phase = 0, tb = 0;
+    if (C::HAS_T) {
+        // prologue: k-tile 0 of the first tile
+        if (mbar_wait_bounded(&full_bar[0], 0u, cta_abort, p.status, DEV_WAIT_FULL)) {
+            transpose_stage(0, 0);
+            if (C::ALL_T) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[0]);
+            }
+        }
+        __syncthreads();
+        if (*cta_abort) return;
     }
 
-    uint32_t stage = 0, phase = 0;
-    bool ok = true;
-    for (long long w = blockIdx.x; ok && w < p.shape.work; w += gridDim.x) {
+    // ---- consumer mapping: warp grid 4 (m) x 2 (n), lane grid 4 (ty) x 8 (tx) ----
+    const int wm = warp >> 1;
+    const int wn = warp & 1;
+    const int ty = lane >> 3;
+    const int tx = lane & 7;
+    constexpr int WROWS = C::BM / 4;  // rows per warp: 32 (TM=8) or 64 (TM=16)
+    const int off_am = (wm * WROWS + ty * 4) * 4;
+    const int off_bm = (wn * 64 + tx * 4) * 4;
+
+    for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
         const int bidx = static_cast<int>(w / tiles_per_mat);
         const int t = static_cast<int>(w - static_cast<long long>(bidx) * tiles_per_mat);
         int tm, tn;
         raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
+        const bool last_tile = w + gridDim.x >= p.shape.work;
 
-        float acc[8][8];
+        // Accumulators are packed float2 for the two-wide FP32 FMA.  For a row pair
+        // (i, i+1) and a column pair (j, j+1):
+        //   d0 = (C[i][j],   C[i+1][j+1]) += (a_i, a_i+1) * (b_j,   b_j+1)
+        //   d1 = (C[i][j+1], C[i+1][j])   += (a_i, a_i+1) * (b_j+1, b_j)
+        // so neither operand has to be broadcast into both halves of a register pair;
+        // only the swapped column pair is built.  Each lane is an independent IEEE fma
+        // in ascending k, so the bits equal the scalar-FMA formulation.
+        float2 d0[TM / 2][4], d1[TM / 2][4];
 #pragma unroll
-        for (int i = 0; i < 8; i++)
+        for (int i = 0; i < TM / 2; i++)
 #pragma unroll
-            for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+            for (int j = 0; j < 4; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
 
+#pragma unroll 1
         for (int kt = 0; kt < k_tiles; kt++) {
-            if (!mbar_wait_bounded(&full_bar[stage], phase, cta_abort, p.status, DEV_WAIT_FULL)) {
-                ok = false;
-                break;
-            }
-            const uint8_t* st = smem + stage * STAGE_BYTES;
+            if (tid == 0) produce_one();
+            bool ok = true;
+            if (!C::HAS_T)
+                ok = mbar_wait_bounded(&full_bar[stage], phase, cta_abort, p.status, DEV_WAIT_FULL);
+            if (!C::HAS_T && !ok) return;  // no CTA barriers on this path: leaving is safe
 
-#pragma unroll
+            const uint8_t* st = smem + stage * C::STAGE_BYTES;
+            const uint8_t* sa = (A_KMAJ ? smem + C::OFF_TA + tb * C::TA_BYTES : st) + off_am;
+            const uint8_t* sb = (B_KMAJ ? smem + C::OFF_TB + tb * C::TB_BYTES : st + C::RAW_A) + off_bm;
+
+#pragma unroll G_UNROLL
             for (int g = 0; g < BK / 4; g++) {  // 8 groups of 4 k
-                float4 av[8], bv[8];            // K-major: [row] = 4 consecutive k
-                float4 am[4][2], bm[4][2];      // MN-major: [k][half] = 4 adjacent rows/cols
-                if (A_KMAJ) {
+                const uint8_t* sag = sa + g * 4 * C::ROWB_A;
+                const uint8_t* sbg = sb + g * 4 * C::ROWB_B;
+                float4 bm[4][2];  // [k][half] = 4 adjacent cols
 #pragma unroll
-                    for (int ib = 0; ib < 2; ib++)
+                for (int kk = 0; kk < 4; kk++)
 #pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const int cc = g ^ ((i & 1) << 2);  // compile-time part of the chunk
-                            av[ib * 4 + i] = *reinterpret_cast<const float4*>(
-                                st + off_a[cc & 3] + (ib * 16 + i * 4) * 128 + (cc & 4) * 16);
-                        }
-                } else {
+                    for (int jb = 0; jb < 2; jb++)
+                        bm[kk][jb] = *reinterpret_cast<const float4*>(sbg + kk * C::ROWB_B + jb * 128);
+#pragma unroll
+                for (int h = 0; h < HALVES; h++) {
+                    float4 am[4][2];  // [k][ib] = 4 adjacent rows
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++)
 #pragma unroll
                         for (int ib = 0; ib < 2; ib++)
                             am[kk][ib] = *reinterpret_cast<const float4*>(
-                                st + off_am + (g * 4 + kk) * (BM * 4) + ib * 64);
-                }
-                if (B_KMAJ) {
+                                sag + kk * C::ROWB_A + (h * 32 + ib * 16) * 4);
 #pragma unroll
-                    for (int jb = 0; jb < 2; jb++)
+                    for (int kk = 0; kk < 4; kk++) {
+                        float2 a2[4], b2[4], b2s[4];
 #pragma unroll
-                        for (int j = 0; j < 4; j++)
-                            bv[jb * 4 + j] = *reinterpret_cast<const float4*>(
-                                st + off_b[g] + (jb * 32 + j * 8) * 128);
-                } else {
-#pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
-#pragma unroll
-                        for (int jb = 0; jb < 2; jb++)
-                            bm[kk][jb] = *reinterpret_cast<const float4*>(
-                                st + off_bm + (g * 4 + kk) * (BN * 4) + jb * 128);
-                }
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    float a[8], b[8];
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        if (A_KMAJ) {
-                            const float4 v = av[i];
-                            a[i] = kk == 0 ? v.x : kk == 1 ? v.y : kk == 2 ? v.z : v.w;
-                        } else {
-                            const float4 v = am[kk][i >> 2];
-                            a[i] = (i & 3) == 0 ? v.x : (i & 3) == 1 ? v.y : (i & 3) == 2 ? v.z : v.w;
+                        for (int pr = 0; pr < 4; pr++) {  // row pairs of this half
+                            const float4 v = am[kk][pr >> 1];
+                            a2[pr] = (pr & 1) ? make_float2(v.z, v.w) : make_float2(v.x, v.y);
                         }
-                    }
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        if (B_KMAJ) {
-                            const float4 v = bv[j];
-                            b[j] = kk == 0 ? v.x : kk == 1 ? v.y : kk == 2 ? v.z : v.w;
-                        } else {
-                            const float4 v = bm[kk][j >> 2];
-                            b[j] = (j & 3) == 0 ? v.x : (j & 3) == 1 ? v.y : (j & 3) == 2 ? v.z : v.w;
+                        for (int q = 0; q < 4; q++) {  // column pairs
+                            const float4 v = bm[kk][q >> 1];
+                            b2[q] = (q & 1) ? make_float2(v.z, v.w) : make_float2(v.x, v.y);
+                            b2s[q] = make_float2(b2[q].y, b2[q].x);
                         }
+#pragma unroll
+                        for (int pr = 0; pr < 4; pr++)
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                d0[h * 4 + pr][q] = __ffma2_rn(a2[pr], b2[q], d0[h * 4 + pr][q]);
+                                d1[h * 4 + pr][q] = __ffma2_rn(a2[pr], b2s[q], d1[h * 4 + pr][q]);
+                            }
                     }
-#pragma unroll
-                    for (int i = 0; i < 8; i++)
-#pragma unroll
-                        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+
+            // advance to the next k-tile's stage
+            uint32_t nstage = stage + 1, nphase = phase;
+            if (nstage == STAGES) { nstage = 0; nphase ^= 1u; }
+            if (!C::ALL_T) {
+                // this k-tile's TMA stage was read by the main loop: release it
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            }
+            if (C::HAS_T) {
+                if (!(last_tile && kt == k_tiles - 1)) {  // a next k-tile exists
+                    if (mbar_wait_bounded(&full_bar[nstage], nphase, cta_abort, p.status, DEV_WAIT_FULL)) {
+                        transpose_stage(nstage, tb ^ 1u);
+                        if (C::ALL_T) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&empty_bar[nstage]);
+                        }
+                    }
+                }
+                // writers of buffer tb^1 | readers of buffer tb: one barrier orders both
+                __syncthreads();
+                if (*cta_abort) return;  // uniform: every thread sees the flag after the barrier
+                tb ^= 1u;
+            }
+            stage = nstage;
+            phase = nphase;
         }
-        if (!ok) break;
 
         // ------------------------------ epilogue ------------------------------
+        // Unpacked view of the accumulators: element (r, c) of the thread tile.
+        const auto acc_at = [&](int r, int c) -> float {
+            const float2 v = ((r & 1) == (c & 1)) ? d0[r >> 1][c >> 1] : d1[r >> 1][c >> 1];
+            return (r & 1) ? v.y : v.x;
+        };
         float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
-        const int row_base = tm * BM + wm * 32;
+        const int row_base = tm * C::BM + wm * WROWS;
         const int col_base = tn * BN + wn * 64;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
 #pragma unroll
-        for (int ib = 0; ib < 2; ib++)
+        for (int h = 0; h < HALVES; h++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int r = row_base + ib * 16 + (A_KMAJ ? (i * 4 + ty) : (ty * 4 + i));
-                if (r >= p.shape.M) continue;
-                float* crow = cmat + static_cast<long long>(r) * p.shape.N;
+            for (int ib = 0; ib < 2; ib++)
 #pragma unroll
-                for (int jb = 0; jb < 2; jb++) {
-                    if (B_KMAJ) {
+                for (int i = 0; i < 4; i++) {
+                    const int r = row_base + h * 32 + ib * 16 + ty * 4 + i;
+                    if (r >= p.shape.M) continue;
+                    float* crow = cmat + static_cast<long long>(r) * p.shape.N;
+                    const int ai = h * 8 + ib * 4 + i;
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const int cidx = col_base + jb * 32 + j * 8 + tx;
-                            if (cidx < p.shape.N) {
-                                float v = acc[ib * 4 + i][jb * 4 + j];
-                                if (bias) v += __ldg(bias + cidx);
-                                crow[cidx] = apply_act(v, act);
-                            }
-                        }
-                    } else {
+                    for (int jb = 0; jb < 2; jb++) {
                         const int cidx = col_base + jb * 32 + tx * 4;
                         float v[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            v[j] = acc[ib * 4 + i][jb * 4 + j];
+                            v[j] = acc_at(ai, jb * 4 + j);
                             if (bias && cidx + j < p.shape.N) v[j] += __ldg(bias + cidx + j);
                             v[j] = apply_act(v[j], act);
                         }
@@ -282,7 +395,6 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                         }
                     }
                 }
-            }
     }
 }
 

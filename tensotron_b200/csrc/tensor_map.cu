@@ -61,8 +61,9 @@ int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uin
     }
     const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(v.base),
                            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           swz == Swizzle::B128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                                : CU_TENSOR_MAP_SWIZZLE_NONE,
+                           swz == Swizzle::B128       ? CU_TENSOR_MAP_SWIZZLE_128B
+                           : swz == Swizzle::B128_A32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                      : CU_TENSOR_MAP_SWIZZLE_NONE,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return static_cast<int>(r);
 }

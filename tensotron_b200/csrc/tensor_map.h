@@ -9,7 +9,9 @@
 
 namespace tt {
 
-enum class Swizzle { None, B128 };
+// B128: 16-byte chunks swizzled within 128-byte rows.  B128_A32: 32-byte chunks swizzled
+// within 128-byte rows (the only layout tcgen05 accepts for MN-major 32-bit operands).
+enum class Swizzle { None, B128, B128_A32 };
 
 // Describes one operand as a tensor of up to 5 dims, innermost first.
 struct OperandView {

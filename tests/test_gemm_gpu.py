@@ -83,7 +83,7 @@ SHAPES = [(256, 256, 512),   # benchmark config 1
           (1, 512, 512), (512, 1, 512), (512, 512, 4), (8, 64, 64), (1, 1, 1), (5, 3, 7), (2, 4, 3)]
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN", "TT"])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_matmul_matches_oracle(rt, shape, layout, variant):
@@ -104,7 +104,7 @@ def test_config1_uniform_seed0(rt):
     a = rng.uniform(-1, 1, (256, 512)).astype(np.float32)
     b = rng.uniform(-1, 1, (512, 256)).astype(np.float32)
     exp = oracle.matmul2d(a, b, 256, 256, 512, 512, 1, 256, 1)
-    for variant in (0, 1, 2):
+    for variant in (0, 1, 2, 3):
         got = run_matmul(rt, a, b, 256, 256, 512, (512, 1, 256, 1), variant)
         assert np.abs(got - exp).max() <= fp32_bound(512, a, b)
 
@@ -129,15 +129,16 @@ def test_bitwise_repeatable_and_grid_independent(rt):
     r1 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 2)
     r2 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 2)
     assert np.array_equal(r1, r2)
-    r3 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 1)
-    assert np.array_equal(r1, r3)  # both kernels: one accumulator per output, ascending k, fmaf
+    for other in (1, 3):   # any-stride kernel, 128x128-tile kernel
+        r3 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), other)
+        assert np.array_equal(r1, r3)  # all kernels: one accumulator per output, ascending k, fmaf
 
 
 def test_nan_propagates_like_reference(rt):
     a = np.zeros((128, 64), dtype=np.float32)
     b = np.ones((64, 128), dtype=np.float32)
     b[5, 7] = np.nan
-    for variant in (1, 2):
+    for variant in (1, 2, 3):
         c = run_matmul(rt, a, b, 128, 128, 64, (64, 1, 128, 1), variant)
         assert np.isnan(c[:, 7]).all() and not np.isnan(c[:, 0]).any()
 
@@ -191,7 +192,7 @@ BATCH_CASES = [
 ]
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("case", BATCH_CASES)
 def test_batched_matches_scalar_oracle(rt, case, variant):
     a_shape, b_shape, bt = case

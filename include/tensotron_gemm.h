@@ -41,6 +41,7 @@ typedef struct tt_handle_s* tt_handle_t;
 #define TT_ERR_UNSUPPORTED 3   /* shape / stride combination outside the contract       */
 #define TT_ERR_WORKSPACE 4     /* handle workspace too small for the requested variant  */
 #define TT_ERR_DEVICE_WAIT 5   /* a bounded device-side wait ran out (see tt_check)     */
+#define TT_ERR_STATIC_LIMIT 6  /* size beyond what a *_static entry's built-in scratch holds */
 
 /* math modes: 0 and 3 carry the meaning of SetCuBlasMathMode
  * (src/Tensotron/TensorRuntime.cs:332-338: 0 = FP32, 3 = TF32); 4 is new. */
@@ -111,6 +112,18 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
  * order.  `loss` and `dlogits` may each be NULL. */
 TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
                              float* dlogits, float* loss, int rows, int classes, float scale);
+
+/* Same result as tt_softmax_cross_entropy, for callers that may not allocate device
+ * memory.  No counterpart in the reference: there the per-row losses live in tensors from
+ * its own allocator.  It takes no handle (tt_create allocates) and keeps the per-row losses
+ * in an array built into the library image, which every GPU that loads the library holds
+ * until exit (TT_STATIC_CE_MAX_ROWS floats).  rows above that limit are refused with
+ * TT_ERR_STATIC_LIMIT.  The call runs on the current device; its first call on a device
+ * looks the array's address up, so make that call before any stream capture.  All calls
+ * share the array: calls that overlap on the GPU race on it. */
+#define TT_STATIC_CE_MAX_ROWS 65536
+TT_API int tt_softmax_cross_entropy_static(void* stream, const float* logits, const int* labels,
+                                    float* dlogits, float* loss, int rows, int classes, float scale);
 
 /* Fused Adam over one flat parameter span (src/Tensotron/Kernels.cs:126-157,
  * src/Tensotron/Optimizers.cs:144-193).  adv = device [t, 1/(1-b1^t), 1/(1-b2^t)];

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtensotron_gemm.so")
-SOURCES = ["api.cu", "tensor_map.cu", "tf32_gemm.cu"]
+SOURCES = ["api.cu", "tensor_map.cu", "tf32_gemm.cu", "static_scratch.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

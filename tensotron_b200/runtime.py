@@ -20,7 +20,7 @@ EXPORTS = [
     "tt_version", "tt_create", "tt_destroy", "tt_last_error", "tt_set_math_mode", "tt_get_math_mode",
     "tt_matmul", "tt_matmul_batched", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
-    "tt_set_variant",
+    "tt_set_variant", "tt_softmax_cross_entropy_static",
 ]
 
 
@@ -63,6 +63,7 @@ def load_library(path=None):
     L.tt_linear_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i]
     L.tt_linear_bwd.argtypes = [vp, vp] + [vp] * 7 + [i, i, i, i]
     L.tt_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, vp, i, i, f]
+    L.tt_softmax_cross_entropy_static.argtypes = [vp, vp, vp, vp, vp, i, i, f]
     L.tt_adam_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, i]
     L.tt_add_into.argtypes = [vp, vp, vp, vp, ll]
     L.tt_broadcast_batch.argtypes = [i, ip, ip, i, ip, ip, ip, ip, ip, ip]
@@ -92,6 +93,24 @@ def _ptr(x):
 def _iarr(v):
     v = [int(t) for t in v]
     return (ctypes.c_int * max(1, len(v)))(*v)
+
+
+STATIC_CE_MAX_ROWS = 65536
+
+
+def softmax_cross_entropy_static(logits, labels, dlogits, loss, rows, classes, scale, stream=None):
+    """tt_softmax_cross_entropy_static: cross-entropy for callers that may not allocate device
+    memory (no handle, scratch built into the library).  Runs on torch's current device."""
+    import torch
+    L = load_library()
+    st = ctypes.c_void_p(stream if isinstance(stream, int) else
+                         (stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream))
+    rc = L.tt_softmax_cross_entropy_static(st, _ptr(logits), _ptr(labels), _ptr(dlogits), _ptr(loss),
+                                           rows, classes, scale)
+    if rc == 6:
+        raise TensotronGemmError(rc, "rows %d exceed the built-in scratch (%d rows)" % (rows, STATIC_CE_MAX_ROWS))
+    if rc:
+        raise TensotronGemmError(rc, "tt_softmax_cross_entropy_static failed")
 
 
 def broadcast_batch(a_dims, a_strides, b_dims, b_strides):

@@ -158,8 +158,9 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr int HALVES = TM / 8;  // 8-row halves of the thread tile
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment.
-    uint8_t* smem = reinterpret_cast<uint8_t*>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
+    // (pointer arithmetic on the shared array itself, so the compiler keeps emitting
+    // shared-space loads rather than generic ones)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
     uint64_t* empty_bar = full_bar + STAGES;
     volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);

@@ -130,6 +130,98 @@ def cpu_reference_sample(steps, warmup, rows_hint=None):
     return tflops, dt, info
 
 
+def time_calls(fn, iters, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def sgemm_modes_8192(rt, sms, max_mhz):
+    """North-star sizes: 8192^3 in strict FP32, TF32 and 3xTF32 (single GPU)."""
+    import torch
+
+    from tensotron_b200.runtime import TT_MATH_3XTF32, TT_MATH_FP32, TT_MATH_TF32
+    n = 8192
+    a = torch.rand((n, n), device="cuda") * 2 - 1
+    b = torch.rand((n, n), device="cuda") * 2 - 1
+    c = torch.empty((n, n), device="cuda")
+    flop = 2.0 * n ** 3
+    fp32_peak = sms * 128 * 2 * max_mhz * 1e6 / 1e12
+    tf32_peak = None
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        tf32_peak = peaks["bf16_tflops"] / 2.0
+        src = "derived: half of the measured BF16 burst peak (MEASURED_PEAKS.json)"
+    except (OSError, KeyError, ValueError):
+        tf32_peak = 1590.0 / 2.0
+        src = "derived: half of the fallback BF16 peak (1.59 PFLOP/s)"
+    out = {}
+    for name, mode, iters in (("fp32", TT_MATH_FP32, 5), ("tf32", TT_MATH_TF32, 20), ("3xtf32", TT_MATH_3XTF32, 10)):
+        rt.SetCuBlasMathMode(mode)
+        ms = time_calls(lambda: rt.LaunchMatMul(a, b, c, n, n, n, n, 1, n, 1), iters)
+        tf = flop / ms / 1e9
+        if name == "fp32":
+            out[name] = {"tflops": tf, "ms": ms, "frac_of_fp32_ffma_peak": tf / fp32_peak}
+        else:
+            pipe = tf * (3 if name == "3xtf32" else 1)
+            out[name] = {"tflops": tf, "ms": ms, "tensor_pipe_tflops": pipe,
+                         "frac_of_tf32_peak": pipe / tf32_peak}
+    rt.SetCuBlasMathMode(TT_MATH_FP32)
+    out["tf32_peak_tflops"] = tf32_peak
+    out["tf32_peak_source"] = src
+    return out
+
+
+def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
+    """Config 4: 784-4096-4096-4096-10 MLP, global batch 8192 split over the ranks,
+    cross-entropy on random labels, Adam lr 1e-3; gradient all-reduce over NCCL."""
+    import torch
+    import torch.distributed as dist
+
+    from tensotron_b200.mlp import MlpTrainer, shard_rows
+    from tensotron_b200.runtime import TT_MATH_FP32, TT_MATH_TF32
+    gb = 8192
+    s, e = shard_rows(gb, world, rank)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((gb, 784), generator=gen, device="cuda")[s:e].contiguous()
+    gen.manual_seed(1)
+    y = torch.randint(0, 10, (gb,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
+    res = {}
+    for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32)):
+        tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
+                        process_group=pg, math_mode=mode)
+        for _ in range(warmup):
+            tr.step(x, y, global_batch=gb)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            loss = tr.step(x, y, global_batch=gb)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        lt = loss.double().clone()
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(lt)
+        ms = t.item() / steps
+        res[name] = {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "loss": lt.item(),
+                     "tflops": 1756.5 / ms}      # 1756.5 GFLOP of GEMM work per step
+        del tr
+    rt.SetCuBlasMathMode(TT_MATH_FP32)
+    return res
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
     if rank != 0:
@@ -179,7 +271,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    rt = TensorRuntime(local_rank)          # raises if the CUDA library is missing: no fallback
+    # raises if the CUDA library is missing: no fallback.  2.5 GiB workspace: 3xTF32 keeps
+    # hi/lo copies of both 8192^2 operands there.
+    rt = TensorRuntime(local_rank, 2560 << 20)
     rt.SetCuBlasMathMode(TT_MATH_FP32)
     n = N_TOTAL
     if n % world != 0:
@@ -242,6 +336,18 @@ def main():
     barrier()
     e2e_ms = e0.elapsed_time(e1)
 
+    del ha, hb, hc
+    extras = {}
+    if not args.no_extras:
+        pg = dist.group.WORLD if world > 1 else None
+        del a, b, c
+        torch.cuda.empty_cache()
+        extras["mlp_784_4096x3_10_batch8192"] = mlp_steps_per_s(rt, rank, world, local_rank, pg)
+        if world == 1:
+            props0 = torch.cuda.get_device_properties(local_rank)
+            extras["sgemm_8192"] = sgemm_modes_8192(rt, props0.multi_processor_count,
+                                                    (clocks or {}).get("sm_max_mhz") or 1965.0)
+
     t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -281,6 +387,8 @@ def main():
             "gpu_launches": launches,
             "roofline": roof,
         }
+        if extras:
+            line["extras"] = extras
         if world == 1 and not args.no_cpu_baseline:
             _, _, info = cpu_reference_sample(1, 0)
             line["cpu_baseline"] = info

@@ -37,12 +37,17 @@ def _newest_dep():
     return t
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, defines=(), out=None):
+    """defines / out: build an experimental variant (extra -D flags) to another file."""
+    global LIB, OBJ
+    if out:
+        LIB = out
+        OBJ = out + ".build"
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
-    extra = ["-Xptxas", "-v"] if verbose else []
+    extra = (["-Xptxas", "-v"] if verbose else []) + ["-D" + d for d in defines]
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

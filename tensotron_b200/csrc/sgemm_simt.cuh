@@ -41,7 +41,10 @@ constexpr int BN = 128, BK = 32;
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int RASTER_GROUP = 8;
-constexpr int G_UNROLL = 2;  // k groups (of 4) unrolled in the main loop; bounds code size
+#ifndef TT_G_UNROLL
+#define TT_G_UNROLL 4
+#endif
+constexpr int G_UNROLL = TT_G_UNROLL;  // k groups (of 4) unrolled in the main loop; bounds code size
 
 template <int TM, bool A_KMAJ, bool B_KMAJ>
 struct Cfg {

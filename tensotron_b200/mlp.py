@@ -1,0 +1,135 @@
+"""Data-parallel MLP training step on the GEMM engine.
+
+The step is the reference's `Sequential(Linear, ReLU, ..., Linear)` + `CrossEntropy` +
+`Adam` loop (examples/Tensotron.Examples/BenchExample.cs:630-699 shape of the loop;
+src/Tensotron/Module.cs:82-112, src/Tensotron/TensorOps.Losses.cs:97-108,
+src/Tensotron/Optimizers.cs:144-193), with every product going through the C-ABI library:
+
+  forward   one fused launch per layer (GEMM + bias + ReLU)             tt_linear_fwd
+  loss      softmax cross-entropy forward+backward, device labels       tt_softmax_cross_entropy
+  backward  per layer: activation backward + fixed-order bias gradient,
+            dX (NN GEMM), dW (TN GEMM)                                  tt_linear_bwd
+  exchange  one NCCL all-reduce (sum) per layer's gradient slice, issued as soon as the
+            slice is final so it overlaps the rest of the backward pass
+  update    one fused Adam over the flat parameter buffer                tt_adam_step
+
+Parameters, gradients and Adam moments live in flat buffers laid out layer by layer
+(W_i then b_i), so a layer's gradients are one contiguous slice and Adam is one launch.
+Data parallelism: each rank holds `global_batch / world` rows; the loss and its gradient are
+scaled by 1/global_batch, so the summed gradients equal the single-GPU gradients up to
+summation order.  torch.distributed is plumbing (process group, NCCL stream handling).
+"""
+import math
+
+import torch
+
+from .runtime import TT_MATH_FP32, TensorRuntime
+
+
+def shard_rows(total, world, rank):
+    """Contiguous row block [start, end) of `total` rows owned by `rank` (same split as the
+    reference's ParallelRows: ceil-sized blocks, src/Tensotron/CpuKernels.cs:461-472)."""
+    per = (total + world - 1) // world
+    start = min(total, rank * per)
+    return start, min(total, start + per)
+
+
+def layer_layout(dims):
+    """Offsets (in floats) of W_i and b_i inside the flat buffers; W_i is (out, in)."""
+    offs, cur = [], 0
+    for i in range(len(dims) - 1):
+        w = cur
+        cur += dims[i + 1] * dims[i]
+        b = cur
+        cur += dims[i + 1]
+        cur = (cur + 3) & ~3  # keep every layer 16-byte aligned for TMA / 128-bit accesses
+        offs.append((w, b))
+    return offs, cur
+
+
+class MlpTrainer:
+    def __init__(self, dims, rt=None, device=0, lr=1e-3, seed=2, process_group=None, math_mode=TT_MATH_FP32):
+        self.dims = list(dims)
+        self.L = len(dims) - 1
+        self.device = device
+        self.rt = rt or TensorRuntime(device)
+        self.lr = lr
+        self.pg = process_group
+        self.math_mode = math_mode
+        self.offs, total = layer_layout(self.dims)
+        dev = torch.device("cuda", device)
+        self.params = torch.zeros(total, device=dev)
+        self.grads = torch.zeros(total, device=dev)
+        self.m = torch.zeros(total, device=dev)
+        self.v = torch.zeros(total, device=dev)
+        self.adv = torch.zeros(3, device=dev)
+        self.loss = torch.zeros(1, device=dev)
+        self.n_params = total
+        gen = torch.Generator().manual_seed(seed)   # same weights on every rank
+        for i, (wo, bo) in enumerate(self.offs):
+            fan_in, fan_out = self.dims[i], self.dims[i + 1]
+            bound = 1.0 / math.sqrt(fan_in)           # Kaiming-uniform a=sqrt(5) (src/Tensotron/Init.cs:54-58)
+            w = (torch.rand(fan_out * fan_in, generator=gen) * 2 - 1) * bound
+            b = (torch.rand(fan_out, generator=gen) * 2 - 1) * bound
+            self.params[wo:wo + fan_out * fan_in].copy_(w)
+            self.params[bo:bo + fan_out].copy_(b)
+        self._acts = None
+        self._batch = 0
+
+    # ---- views ----
+    def weight(self, i, buf=None):
+        buf = self.params if buf is None else buf
+        wo, _ = self.offs[i]
+        return buf[wo:wo + self.dims[i + 1] * self.dims[i]].view(self.dims[i + 1], self.dims[i])
+
+    def bias(self, i, buf=None):
+        buf = self.params if buf is None else buf
+        _, bo = self.offs[i]
+        return buf[bo:bo + self.dims[i + 1]]
+
+    def layer_slice(self, i, buf):
+        wo, bo = self.offs[i]
+        return buf[wo:bo + self.dims[i + 1]]
+
+    def _ensure_buffers(self, batch):
+        if self._batch == batch:
+            return
+        dev = self.params.device
+        self._acts = [torch.empty((batch, d), device=dev) for d in self.dims[1:]]
+        self._dacts = [torch.empty((batch, d), device=dev) for d in self.dims[1:]]
+        self._batch = batch
+
+    # ---- one training step ----
+    def step(self, x, labels, global_batch=None, apply_update=True):
+        """x: (rows, dims[0]) float32 CUDA, labels: (rows,) int32 CUDA.  Returns the device
+        scalar holding this rank's share of the mean loss (sum over ranks = global mean)."""
+        rt = self.rt
+        rt.SetCuBlasMathMode(self.math_mode)
+        rows = x.shape[0]
+        gb = global_batch or rows
+        self._ensure_buffers(rows)
+        L = self.L
+        inp = x
+        for i in range(L):
+            act = 1 if i < L - 1 else 0
+            rt.LaunchLinearForward(inp, self.weight(i), self.bias(i), self._acts[i], rows,
+                                   self.dims[i + 1], self.dims[i], act)
+            inp = self._acts[i]
+        rt.LaunchSoftmaxCrossEntropy(self._acts[L - 1], labels, self._dacts[L - 1], self.loss, rows,
+                                     self.dims[L], 1.0 / gb)
+        handles = []
+        for i in reversed(range(L)):
+            act = 1 if i < L - 1 else 0
+            layer_in = x if i == 0 else self._acts[i - 1]
+            dx = self._dacts[i - 1] if i > 0 else None
+            rt.LaunchLinearBackward(layer_in, self.weight(i), self._acts[i], self._dacts[i], dx,
+                                    self.weight(i, self.grads), self.bias(i, self.grads), rows,
+                                    self.dims[i + 1], self.dims[i], act)
+            if self.pg is not None:
+                import torch.distributed as dist
+                handles.append(dist.all_reduce(self.layer_slice(i, self.grads), group=self.pg, async_op=True))
+        for h in handles:
+            h.wait()
+        if apply_update:
+            rt.LaunchAdam(self.params, self.grads, self.m, self.v, self.adv, self.n_params, lr=self.lr)
+        return self.loss

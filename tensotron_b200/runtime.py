@@ -10,7 +10,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtensotron_gemm.so")
+LIB_PATH = os.environ.get("TENSOTRON_GEMM_LIB", os.path.join(_HERE, "libtensotron_gemm.so"))
 
 TT_MATH_FP32, TT_MATH_TF32, TT_MATH_3XTF32 = 0, 3, 4
 TT_ACT_NONE, TT_ACT_RELU, TT_ACT_TANH = 0, 1, 2

@@ -27,9 +27,10 @@ N_TOTAL = int(os.environ.get("TT_BENCH_N", "16384"))
 METRIC = "sgemm_fp32_tflops"
 UNIT = "TFLOP/s"
 
-# DRAM bytes per launch of sgemm_simt_kernel from an ncu capture (see profiles/); None until
-# a capture of this kernel exists.  Keyed by problem edge.
-NCU_TRAFFIC_BYTES = {}
+# DRAM bytes (read + write) per launch of sgemm_simt_kernel from ncu, keyed by problem edge.
+# 8192 is captured (profiles/sgemm_simt_kernel_nn_8192_dram_traffic.md); 16384 is that capture
+# scaled (reads x 8, writes x 4), because a 3 GB / 157 ms launch is too large to capture.
+NCU_TRAFFIC_BYTES = {8192: 2242259712 + 256432640, 16384: 8 * 2242259712 + 4 * 256432640}
 
 
 def env_int(name, default):
@@ -365,7 +366,8 @@ def main():
         per_gpu = value / world
         roof = {
             "bound": "fp32_ffma", "achieved": per_gpu, "peak": peak, "unit": UNIT,
-            "frac": per_gpu / peak, "traffic": NCU_TRAFFIC_BYTES.get(n),
+            "frac": per_gpu / peak, "traffic": NCU_TRAFFIC_BYTES.get(n) if world == 1 else None,
+            "traffic_note": "ncu DRAM bytes per launch; 16384 is the 8192^3 capture scaled (reads x 8, writes x 4)",
             "peak_source": "derived: %d SMs x 128 FP32 lanes x 2 x %.0f MHz (max SM clock); the "
                            "measured-peaks file has no FP32 SIMT figure" % (sms, max_mhz),
             "kernel": "sgemm_simt_kernel<K-major A, N-major B>",

@@ -181,6 +181,33 @@ def sgemm_modes_8192(rt, sms, max_mhz):
     return out
 
 
+def bmm_config3(rt):
+    """Config 3: A [32,1,384,256] x B [1,16,256,192] -> [32,16,384,192], one launch through
+    LaunchMatMulBatched (the reference issues 512 cuBLAS calls); FP32 and TF32.  In TF32 the
+    151 MB output write makes it HBM-bound, so achieved GB/s is reported too."""
+    import torch
+
+    from tensotron_b200 import runtime
+    from tensotron_b200.runtime import TT_MATH_FP32, TT_MATH_TF32
+    a = torch.rand((32, 1, 384, 256), device="cuda") * 2 - 1
+    b = torch.rand((1, 16, 256, 192), device="cuda") * 2 - 1
+    c = torch.empty((32, 16, 384, 192), device="cuda")
+    dims, aBs, bBs = runtime.broadcast_batch([32, 1], [98304, 98304], [1, 16], [786432, 49152])
+    flop = 512 * 2.0 * 384 * 192 * 256
+    nbytes = 4.0 * (a.numel() + b.numel() + c.numel())
+    out = {"algorithmic_bytes": nbytes, "flop": flop}
+    for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32)):
+        rt.SetCuBlasMathMode(mode)
+        ms = time_calls(lambda: rt.LaunchMatMulBatched(a, b, c, 512, 384, 192, 256, 256, 1, 192, 1, dims, aBs, bBs), 20)
+        out[name] = {"ms": ms, "tflops": flop / ms / 1e9, "hbm_gbs": nbytes / ms / 1e6}
+    rt.SetCuBlasMathMode(TT_MATH_FP32)
+    try:
+        out["hbm_peak_gbs"] = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]
+    except (OSError, KeyError, ValueError):
+        out["hbm_peak_gbs"] = 6650.0
+    return out
+
+
 def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
     """Config 4: 784-4096-4096-4096-10 MLP, global batch 8192 split over the ranks,
     cross-entropy on random labels, Adam lr 1e-3; gradient all-reduce over NCCL."""
@@ -346,6 +373,7 @@ def main():
         extras["mlp_784_4096x3_10_batch8192"] = mlp_steps_per_s(rt, rank, world, local_rank, pg)
         if world == 1:
             props0 = torch.cuda.get_device_properties(local_rank)
+            extras["bmm_32x16_384x256x192"] = bmm_config3(rt)
             extras["sgemm_8192"] = sgemm_modes_8192(rt, props0.multi_processor_count,
                                                     (clocks or {}).get("sm_max_mhz") or 1965.0)
 

@@ -173,6 +173,7 @@ struct GemmCall {
     HostBatch batch;
     int batch_count;
     Epilogue epi;
+    size_t ws_off = 0;  // first free byte of the handle workspace for this call
 };
 
 int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
@@ -201,32 +202,61 @@ template <int TM, bool AK, bool BK_>
 int launch_simt_t(tt_handle_t h, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb,
                   const simt::Params& p, int grid)
 {
-    auto kern = simt::sgemm_simt_kernel<TM, AK, BK_>;
-    kern<<<grid, simt::THREADS, simt::Cfg<TM, AK, BK_>::SMEM_BYTES, st>>>(ma, mb, p);
+    constexpr int smem = simt::Cfg<TM, AK, BK_>::SMEM_BYTES;
+    // split-K exists for the 128x128 tile only (small problems)
+    if (TM == 8 && p.splits > 1) simt::sgemm_simt_kernel<8, AK, BK_, true><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+    else simt::sgemm_simt_kernel<TM, AK, BK_, false><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "simt gemm launch");
     return TT_OK;
 }
 
-// Tile choice for the FFMA kernel: 256x128 tiles (16x8 per thread) run ~1.5x the rate
-// of 128x128 tiles (8x8 per thread, shared-memory-return bound) but quantise worse on
-// small grids.  Estimated time = waves x per-tile cost; the cheaper one wins.  The
+// Tile and split-K choice for the FMA kernel.  256x128 tiles (16x8 per thread) run at
+// about 76 % of the FMA peak, 128x128 tiles (8x8 per thread) at about 70 %, but small
+// grids quantise badly on 148 SMs; cutting K into `splits` ranges (partials reduced in a
+// fixed order by the last CTA of each tile) fills the machine for small M x N.  The model
+// is time ~ waves x (k-tiles per split + fixed per-item overhead) x per-tile cost, and the
 // choice depends on the shape and the SM count only.
-int pick_tm(const tt_handle_t h, int M, int N, int batch)
+struct SimtPlan {
+    int tm;
+    int splits;
+    int kps;
+};
+
+SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail)
 {
-    const auto waves = [&](int bm) {
-        const long long work = static_cast<long long>(batch) * ((M + bm - 1) / bm) * ((N + simt::BN - 1) / simt::BN);
-        return (work + h->num_sms - 1) / h->num_sms;
-    };
-    const double t16 = static_cast<double>(waves(256)) * 2.0 / 0.85;
-    const double t8 = static_cast<double>(waves(128)) * 1.0 / 0.55;
-    return t16 <= t8 ? 16 : 8;
+    const int k_tiles = (K + simt::BK - 1) / simt::BK;
+    SimtPlan best{16, 1, k_tiles};
+    double best_t = 1e300;
+    for (int tm : {16, 8}) {
+        const int bm = 16 * tm;
+        const long long tiles = static_cast<long long>(batch) * ((M + bm - 1) / bm) * ((N + simt::BN - 1) / simt::BN);
+        const double tile_cost = tm == 16 ? 2.0 / 0.76 : 1.0 / 0.70;
+        for (int splits = 1; splits <= 32; splits++) {
+            const int kps = (k_tiles + splits - 1) / splits;
+            const int real = (k_tiles + kps - 1) / kps;
+            if (real != splits) continue;              // skip counts that leave empty ranges
+            if (splits > 1) {
+                if (tm != 8) break;                    // split-K exists for the 128x128 tile only
+                if (kps < 1) break;
+                const size_t need = static_cast<size_t>(tiles) * splits * bm * simt::BN * sizeof(float);
+                if (need > ws_avail) break;
+            }
+            const long long work = tiles * splits;
+            const long long waves = (work + h->num_sms - 1) / h->num_sms;
+            // per work item: kps k-tiles + ~2 k-tiles worth of pipeline fill / epilogue; the
+            // reduction kernel costs about as much as two more k-tiles of a 128x128 tile
+            const double t = static_cast<double>(waves) * (kps + 2.0) * tile_cost + (splits > 1 ? 2.0 / 0.70 : 0.0);
+            if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps}; }
+        }
+    }
+    return best;
 }
 
 // Returns TT_ERR_UNSUPPORTED (without touching h->err) when the operands cannot be
 // expressed as TMA descriptors; the caller then uses the any-stride kernel.
 template <int TM>
-int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const SimtPlan& plan)
 {
     constexpr int BM = 16 * TM;
     OperandView va, vb;
@@ -252,12 +282,16 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     p.shape.tiles_m = (g.M + BM - 1) / BM;
     p.shape.tiles_n = (g.N + simt::BN - 1) / simt::BN;
     p.shape.batch = g.batch_count;
-    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    p.splits = plan.splits;
+    p.kps = plan.kps;
+    p.partial = reinterpret_cast<float*>(h->workspace + g.ws_off);
+    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * plan.splits;
     p.epi = g.epi;
     p.c = g.c;
     p.status = h->status;
     p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
     const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
+    if (plan.splits > 1) h->stats.splitk++;
     int rc;
     if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid);
     else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid);
@@ -266,15 +300,28 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
+    if (plan.splits > 1) {
+        const long long threads = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * (BM * simt::BN / 4);
+        simt::splitk_reduce_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
+            p.partial, g.c, p.shape, g.epi, plan.splits, p.c_vec_ok);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "split-K reduce launch");
+        h->stats.launches++;
+    }
     return TT_OK;
 }
 
 int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 {
-    int tm = pick_tm(h, g.M, g.N, g.batch_count);
-    if (h->variant == 2) tm = 16;
-    if (h->variant == 3) tm = 8;
-    return tm == 16 ? try_launch_simt_tm<16>(h, st, g) : try_launch_simt_tm<8>(h, st, g);
+    const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
+    SimtPlan plan = plan_simt(h, g.M, g.N, g.K, g.batch_count, ws_avail);
+    if (h->variant == 2 || h->variant == 3) {
+        // pinned tile height (A/B measurements and tests): no split-K
+        plan.tm = h->variant == 2 ? 16 : 8;
+        plan.splits = 1;
+        plan.kps = (g.K + simt::BK - 1) / simt::BK;
+    }
+    return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
 
 int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
@@ -293,7 +340,8 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
                                             g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,
                                             g.batch.dims, g.batch.as, g.batch.bs, g.epi, h->num_sms,
-                                            h->status, h->workspace, h->workspace_bytes, &n_launch,
+                                            h->status, h->workspace + g.ws_off,
+                                            h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0, &n_launch,
                                             h->variant == 4 ? 1 : h->variant == 5 ? 2 : 0);
             if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
             if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
@@ -311,9 +359,13 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 template <int TM, bool AK, bool BK_>
 cudaError_t init_simt_one()
 {
-    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_>,
+    cudaError_t e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         simt::Cfg<TM, AK, BK_>::SMEM_BYTES);
+    if (e != cudaSuccess || TM != 8) return e;
+    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<8, AK, BK_, true>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                simt::Cfg<TM, AK, BK_>::SMEM_BYTES);
+                                simt::Cfg<8, AK, BK_>::SMEM_BYTES);
 }
 
 template <int TM>
@@ -484,6 +536,7 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     const float* g = dy;
+    size_t ws_used = 0;  // the masked gradient and the column-sum partials stay live during the GEMMs
     if (static_cast<long long>(M) * N > 0 && (act != TT_ACT_NONE || dbias)) {
         const int chunks = ew::colsum_chunks(M);
         const size_t g_bytes = act != TT_ACT_NONE ? sizeof(float) * static_cast<size_t>(M) * N : 0;
@@ -505,6 +558,7 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(h, e, "linear backward elementwise launch");
         if (gbuf) g = gbuf;
+        ws_used = (g_bytes_al + part_bytes + 255) & ~static_cast<size_t>(255);
     } else if (dbias && N > 0) {
         const cudaError_t e = cudaMemsetAsync(dbias, 0, sizeof(float) * N, st);
         if (e != cudaSuccess) return cuda_fail(h, e, "memset dbias");
@@ -512,10 +566,12 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
     if (dx) {
         // dx[m,k] = sum_n g[m*N + n] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:36)
         GemmCall gx{g, w, dx, M, K, N, N, 1, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+        gx.ws_off = ws_used;
         if ((rc = run_gemm(h, st, gx))) return rc;
     }
     // dw[n,k] = sum_m g[m*N + n] * x[m*K + k]       (src/Tensotron/TensorOps.LinearNT.cs:44)
     GemmCall gw{g, x, dw, N, K, M, 1, N, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+    gw.ws_off = ws_used;
     return run_gemm(h, st, gw);
 }
 

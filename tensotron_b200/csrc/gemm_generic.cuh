@@ -64,17 +64,19 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
 
-        for (int k0 = 0; k0 < p.shape.K; k0 += BK) {
+        // Global loads of k-tile i+1 are issued into registers before the FMAs of k-tile i,
+        // so the global-memory latency overlaps the arithmetic.
+        float ra[(BM * BK) / THREADS], rb[(BN * BK) / THREADS];
+        const auto fetch = [&](int k0) {
 #pragma unroll
             for (int e = 0; e < (BM * BK) / THREADS; e++) {
                 const int idx = tid + e * THREADS;
                 const int kk = a_kmaj ? (idx % BK) : (idx / BM);
                 const int mm = a_kmaj ? (idx / BK) : (idx % BM);
                 const int gm = m0 + mm, gk = k0 + kk;
-                float v = 0.f;
-                if (gm < p.shape.M && gk < p.shape.K)
-                    v = __ldg(A + static_cast<long long>(gm) * p.aMs + static_cast<long long>(gk) * p.aKs);
-                As[kk][mm] = v;
+                ra[e] = (gm < p.shape.M && gk < p.shape.K)
+                            ? __ldg(A + static_cast<long long>(gm) * p.aMs + static_cast<long long>(gk) * p.aKs)
+                            : 0.f;
             }
 #pragma unroll
             for (int e = 0; e < (BN * BK) / THREADS; e++) {
@@ -82,12 +84,25 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
                 const int kk = b_kmaj ? (idx % BK) : (idx / BN);
                 const int nn = b_kmaj ? (idx / BK) : (idx % BN);
                 const int gn = n0 + nn, gk = k0 + kk;
-                float v = 0.f;
-                if (gn < p.shape.N && gk < p.shape.K)
-                    v = __ldg(B + static_cast<long long>(gn) * p.bNs + static_cast<long long>(gk) * p.bKs);
-                Bs[kk][nn] = v;
+                rb[e] = (gn < p.shape.N && gk < p.shape.K)
+                            ? __ldg(B + static_cast<long long>(gn) * p.bNs + static_cast<long long>(gk) * p.bKs)
+                            : 0.f;
+            }
+        };
+        if (p.shape.K > 0) fetch(0);
+        for (int k0 = 0; k0 < p.shape.K; k0 += BK) {
+#pragma unroll
+            for (int e = 0; e < (BM * BK) / THREADS; e++) {
+                const int idx = tid + e * THREADS;
+                As[a_kmaj ? (idx % BK) : (idx / BM)][a_kmaj ? (idx / BK) : (idx % BM)] = ra[e];
+            }
+#pragma unroll
+            for (int e = 0; e < (BN * BK) / THREADS; e++) {
+                const int idx = tid + e * THREADS;
+                Bs[b_kmaj ? (idx % BK) : (idx / BN)][b_kmaj ? (idx / BK) : (idx % BN)] = rb[e];
             }
             __syncthreads();
+            if (k0 + BK < p.shape.K) fetch(k0 + BK);
 #pragma unroll
             for (int kk = 0; kk < BK; kk++) {
                 const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);

@@ -69,7 +69,7 @@ struct Cfg {
     static constexpr int OFF_TA = STAGES * STAGE_BYTES;
     static constexpr int OFF_TB = OFF_TA + 2 * TA_BYTES;
     static constexpr int OFF_BAR = (OFF_TB + 2 * TB_BYTES + 127) & ~127;
-    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // barriers @0, cursor @128, split-K flag @256
     static_assert(STAGES >= 2, "shared-memory budget");
 };
 
@@ -80,6 +80,11 @@ struct Params {
     float* c;
     unsigned int* status;  // device status word (bounded waits)
     int c_vec_ok;          // C base 16-byte aligned and N % 4 == 0
+    // split-K: every output tile is cut into `splits` k-ranges of `kps` k-tiles; work item
+    // w = tile * splits + split.  Partial tiles go to `partial` ([tile][split][BM][BN]);
+    // splitk_reduce_kernel adds them in split order and runs the epilogue.
+    int splits, kps;
+    float* partial;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act)
@@ -93,7 +98,8 @@ __device__ __forceinline__ float apply_act(float v, int act)
 // runs DIST steps ahead of the consumers.  Lives in shared memory.
 struct LoadCursor {
     long long w;
-    int kt;
+    int kt, ke;   // next k-tile to load, end of this work item's k range
+    int fresh;    // 1: the next load starts a new work item
     int m0, n0;
     int ca0, ca1, ca2, cb0, cb1, cb2;
     uint32_t stage, use;  // stage to fill next; how many times the ring has wrapped
@@ -101,10 +107,15 @@ struct LoadCursor {
 };
 
 template <int BM>
-__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat)
+__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat, int k_tiles)
 {
-    const int bidx = static_cast<int>(cur.w / tiles_per_mat);
-    const int t = static_cast<int>(cur.w - static_cast<long long>(bidx) * tiles_per_mat);
+    const long long unit = cur.w / p.splits;
+    const int split = static_cast<int>(cur.w - unit * p.splits);
+    cur.kt = split * p.kps;
+    cur.ke = min(k_tiles, cur.kt + p.kps);
+    cur.fresh = 0;
+    const int bidx = static_cast<int>(unit / tiles_per_mat);
+    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
     int tm, tn;
     raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
     cur.m0 = tm * BM;
@@ -151,7 +162,9 @@ __device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst,
     }
 }
 
-template <int TM, bool A_KMAJ, bool B_KMAJ>
+// SPLITK is a compile-time switch because the mere presence of a second epilogue changes
+// the register allocation of the main loop (measured: 56 -> 48 TFLOP/s at 8192^3).
+template <int TM, bool A_KMAJ, bool B_KMAJ, bool SPLITK>
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b, const Params p)
@@ -187,6 +200,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         prefetch_tensormap(&map_b);
         cur.w = blockIdx.x;
         cur.kt = 0;
+        cur.ke = 0;
+        cur.fresh = 1;
         cur.stage = 0;
         cur.use = 0;
         cur.ok = 1;
@@ -197,7 +212,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     // (thread 0 only; its state lives in shared memory so it costs no registers).
     auto produce_one = [&]() {
         if (cur.w >= p.shape.work || !cur.ok) return;
-        if (cur.kt == 0) cursor_set_tile<C::BM>(cur, p, tiles_per_mat);
+        if (cur.fresh) cursor_set_tile<C::BM>(cur, p, tiles_per_mat, k_tiles);
         const uint32_t ps = cur.stage;
         if (cur.use > 0) {
             // the stage was used before: wait until all warps released that use
@@ -216,7 +231,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, cur.n0, cur.cb0, cur.cb1, cur.cb2);
         else        tma_load_5d(sb, &map_b, &full_bar[ps], cur.n0, k0, cur.cb0, cur.cb1, cur.cb2);
         if (ps + 1 == STAGES) { cur.stage = 0; cur.use++; } else { cur.stage = ps + 1; }
-        if (++cur.kt == k_tiles) { cur.kt = 0; cur.w += gridDim.x; }
+        if (++cur.kt == cur.ke) { cur.fresh = 1; cur.w += gridDim.x; }
     };
 
     if (tid == 0) {
@@ -257,8 +272,12 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const int off_bm = (wn * 64 + tx * 4) * 4;
 
     for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
-        const int bidx = static_cast<int>(w / tiles_per_mat);
-        const int t = static_cast<int>(w - static_cast<long long>(bidx) * tiles_per_mat);
+        const long long unit = w / p.splits;
+        const int split = static_cast<int>(w - unit * p.splits);
+        const int kb = split * p.kps;
+        const int ke = min(k_tiles, kb + p.kps);
+        const int bidx = static_cast<int>(unit / tiles_per_mat);
+        const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
         int tm, tn;
         raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
         const bool last_tile = w + gridDim.x >= p.shape.work;
@@ -277,7 +296,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int j = 0; j < 4; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
 
 #pragma unroll 1
-        for (int kt = 0; kt < k_tiles; kt++) {
+        for (int kt = kb; kt < ke; kt++) {
             if (tid == 0) produce_one();
             bool ok = true;
             if (!C::HAS_T)
@@ -341,7 +360,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (lane == 0) mbar_arrive(&empty_bar[stage]);
             }
             if (C::HAS_T) {
-                if (!(last_tile && kt == k_tiles - 1)) {  // a next k-tile exists
+                if (!(last_tile && kt == ke - 1)) {  // a next k-tile exists
                     if (mbar_wait_bounded(&full_bar[nstage], nphase, cta_abort, p.status, DEV_WAIT_FULL)) {
                         transpose_stage(nstage, tb ^ 1u);
                         if (C::ALL_T) {
@@ -366,39 +385,108 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             return (r & 1) ? v.y : v.x;
         };
         float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
-        const int row_base = tm * C::BM + wm * WROWS;
-        const int col_base = tn * BN + wn * 64;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
+
+        if (SPLITK && p.splits > 1) {
+            // park this split's partial tile ([BM][BN] floats, dense) in the workspace; a
+            // separate kernel adds the partials of a tile in split order and runs the epilogue
+            float* mine = p.partial + w * (C::BM * BN);
 #pragma unroll
-        for (int h = 0; h < HALVES; h++)
+            for (int h = 0; h < HALVES; h++)
 #pragma unroll
-            for (int ib = 0; ib < 2; ib++)
+                for (int ib = 0; ib < 2; ib++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int r = row_base + h * 32 + ib * 16 + ty * 4 + i;
-                    if (r >= p.shape.M) continue;
-                    float* crow = cmat + static_cast<long long>(r) * p.shape.N;
-                    const int ai = h * 8 + ib * 4 + i;
+                    for (int i = 0; i < 4; i++) {
+                        const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
+                        const int ai = h * 8 + ib * 4 + i;
 #pragma unroll
-                    for (int jb = 0; jb < 2; jb++) {
-                        const int cidx = col_base + jb * 32 + tx * 4;
-                        float v[4];
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            v[j] = acc_at(ai, jb * 4 + j);
-                            if (bias && cidx + j < p.shape.N) v[j] += __ldg(bias + cidx + j);
-                            v[j] = apply_act(v[j], act);
-                        }
-                        if (p.c_vec_ok && cidx + 3 < p.shape.N) {
-                            *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 4; j++)
-                                if (cidx + j < p.shape.N) crow[cidx + j] = v[j];
+                        for (int jb = 0; jb < 2; jb++) {
+                            const int lc = wn * 64 + jb * 32 + tx * 4;
+                            *reinterpret_cast<float4*>(mine + lr * BN + lc) =
+                                make_float4(acc_at(ai, jb * 4), acc_at(ai, jb * 4 + 1),
+                                            acc_at(ai, jb * 4 + 2), acc_at(ai, jb * 4 + 3));
                         }
                     }
-                }
+            continue;
+        }
+        {
+#pragma unroll
+            for (int h = 0; h < HALVES; h++)
+#pragma unroll
+                for (int ib = 0; ib < 2; ib++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
+                        const int r = tm * C::BM + lr;
+                        if (r >= p.shape.M) continue;
+                        float* crow = cmat + static_cast<long long>(r) * p.shape.N;
+                        const int ai = h * 8 + ib * 4 + i;
+#pragma unroll
+                        for (int jb = 0; jb < 2; jb++) {
+                            const int lc = wn * 64 + jb * 32 + tx * 4;
+                            const int cidx = tn * BN + lc;
+                            float v[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) v[j] = acc_at(ai, jb * 4 + j);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                if (bias && cidx + j < p.shape.N) v[j] += __ldg(bias + cidx + j);
+                                v[j] = apply_act(v[j], act);
+                            }
+                            if (p.c_vec_ok && cidx + 3 < p.shape.N) {
+                                *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    if (cidx + j < p.shape.N) crow[cidx + j] = v[j];
+                            }
+                        }
+                    }
+        }
+    }
+}
+
+// C = act(sum over splits (ascending) of the partial tiles + bias).  One thread per 4
+// consecutive columns of one tile row; grid covers tiles x (BM * BN / 4) threads.
+template <int BM>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, GemmShape shape,
+                     Epilogue epi, int splits, int c_vec_ok)
+{
+    constexpr int PER_TILE = BM * BN / 4;
+    const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long tiles = static_cast<long long>(shape.batch) * shape.tiles_m * shape.tiles_n;
+    if (gid >= tiles * PER_TILE) return;
+    const long long unit = gid / PER_TILE;
+    const int e = static_cast<int>(gid - unit * PER_TILE);
+    const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
+    const int tiles_per_mat = shape.tiles_m * shape.tiles_n;
+    const int bidx = static_cast<int>(unit / tiles_per_mat);
+    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
+    int tm, tn;
+    raster_tile(t, shape.tiles_m, shape.tiles_n, RASTER_GROUP, tm, tn);
+    const int r = tm * BM + lr, cidx = tn * BN + lc;
+    if (r >= shape.M || cidx >= shape.N) return;
+    const float* src = partial + unit * splits * (BM * BN) + lr * BN + lc;
+    float4 sum = *reinterpret_cast<const float4*>(src);
+    for (int sp = 1; sp < splits; sp++) {
+        const float4 q = *reinterpret_cast<const float4*>(src + static_cast<long long>(sp) * (BM * BN));
+        sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (epi.bias && cidx + j < shape.N) v[j] += __ldg(epi.bias + cidx + j);
+        v[j] = apply_act(v[j], epi.act);
+    }
+    float* crow = c + static_cast<long long>(bidx) * shape.M * shape.N + static_cast<long long>(r) * shape.N;
+    if (c_vec_ok && cidx + 3 < shape.N) {
+        *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (cidx + j < shape.N) crow[cidx + j] = v[j];
     }
 }
 

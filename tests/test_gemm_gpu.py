@@ -116,7 +116,8 @@ def test_tma_kernel_serves_aligned_shapes(rt):
     rt.ResetCounters()
     run_matmul(rt, a, b, 512, 384, 256, (256, 1, 384, 1))
     s = rt.Stats()
-    assert s["simt_tma"] == 1 and s["generic"] == 0 and s["launches"] == 1
+    # one GEMM launch, plus the split-K reduction when the plan cut K
+    assert s["simt_tma"] == 1 and s["generic"] == 0 and s["launches"] == 1 + s["splitk"]
 
 
 def test_bitwise_repeatable_and_grid_independent(rt):
@@ -132,6 +133,27 @@ def test_bitwise_repeatable_and_grid_independent(rt):
     for other in (1, 3):   # any-stride kernel, 128x128-tile kernel
         r3 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), other)
         assert np.array_equal(r1, r3)  # all kernels: one accumulator per output, ascending k, fmaf
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", [(256, 256, 2048), (128, 384, 4096), (512, 512, 1024), (130, 260, 1000), (1024, 1024, 1024)])
+def test_split_k_matches_oracle_and_is_repeatable(rt, shape, layout):
+    """Small M x N with long K: the automatic plan cuts K into ranges whose partial tiles are
+    reduced in a fixed order by the last CTA of each tile (no atomics on data)."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = layout_strides(layout, M, N, K)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 0)
+    used_split = rt.Stats()["splitk"]
+    r2 = run_matmul(rt, a, b, M, N, K, st, 0)
+    assert np.array_equal(r1, r2)
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+    if (M, N, K) == (256, 256, 2048) and M % 4 == 0:
+        assert used_split == 1
 
 
 def test_nan_propagates_like_reference(rt):

@@ -184,16 +184,45 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     p.shape.tiles_m = (g.M + generic::BM - 1) / generic::BM;
     p.shape.tiles_n = (g.N + generic::BN - 1) / generic::BN;
     p.shape.batch = g.batch_count;
-    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    const long long tiles = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    // Split K when the tiles alone leave most of the machine idle: aim at about two CTAs per
+    // SM, at least 64 k per range, and only as far as the workspace holds the partial tiles.
+    int splits = 1, kspan = g.K > 0 ? g.K : 1;
+    const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
+    if (tiles < h->num_sms && g.K >= 512) {
+        long long want = (2ll * h->num_sms + tiles - 1) / tiles;
+        const long long max_by_k = g.K / 64;
+        if (want > max_by_k) want = max_by_k;
+        if (want > 64) want = 64;
+        const size_t per_split = static_cast<size_t>(tiles) * generic::BM * generic::BN * sizeof(float);
+        if (per_split > 0 && want * per_split > ws_avail) want = static_cast<long long>(ws_avail / per_split);
+        if (want >= 2) {
+            kspan = static_cast<int>((g.K + want - 1) / want);
+            kspan = ((kspan + generic::BK - 1) / generic::BK) * generic::BK;
+            splits = (g.K + kspan - 1) / kspan;
+        }
+    }
+    p.splits = splits;
+    p.kspan = kspan;
+    p.partial = reinterpret_cast<float*>(h->workspace + g.ws_off);
+    p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
+    p.shape.work = tiles * splits;
     fill_batch_desc(g.batch, p.batch);
     p.epi = g.epi;
     p.aMs = g.aMs; p.aKs = g.aKs; p.bKs = g.bKs; p.bNs = g.bNs;
     const long long max_grid = static_cast<long long>(h->num_sms) * 8;
     const int grid = static_cast<int>(p.shape.work < max_grid ? p.shape.work : max_grid);
     generic::gemm_generic_kernel<<<grid, generic::THREADS, 0, st>>>(p);
+    h->stats.launches++;
+    if (splits > 1) {
+        const long long threads = tiles * (generic::BM * generic::BN / 4);
+        generic::generic_reduce_kernel<<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
+            p.partial, g.c, p.shape, g.epi, splits, p.c_vec_ok);
+        h->stats.launches++;
+        h->stats.splitk++;
+    }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "generic gemm launch");
-    h->stats.launches++;
     h->stats.generic++;
     return TT_OK;
 }

@@ -19,6 +19,12 @@ struct Params {
     BatchDesc batch;
     Epilogue epi;
     int aMs, aKs, bKs, bNs;
+    // split-K: work item w = tile * splits + split covers k in [split*kspan, +kspan); with
+    // splits > 1 the raw tile goes to `partial` ([tile][split][BM][BN]) and
+    // generic_reduce_kernel adds the splits in order and runs the epilogue.
+    int splits, kspan;
+    float* partial;
+    int c_vec_ok;
 };
 
 __device__ __forceinline__ float act_apply(float v, int act)
@@ -42,8 +48,12 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
     const bool b_kmaj = p.bKs == 1 || p.bNs != 1;
 
     for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
-        const int bidx = static_cast<int>(w / tiles_per_mat);
-        const int t = static_cast<int>(w - static_cast<long long>(bidx) * tiles_per_mat);
+        const long long unit = w / p.splits;
+        const int split = static_cast<int>(w - unit * p.splits);
+        const int k_begin = split * p.kspan;
+        const int k_end = min(p.shape.K, k_begin + p.kspan);
+        const int bidx = static_cast<int>(unit / tiles_per_mat);
+        const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
         const int tm = t / p.shape.tiles_n, tn = t % p.shape.tiles_n;
         long long a_off = 0, b_off = 0;
         int br = bidx;
@@ -74,7 +84,7 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
                 const int kk = a_kmaj ? (idx % BK) : (idx / BM);
                 const int mm = a_kmaj ? (idx / BK) : (idx % BM);
                 const int gm = m0 + mm, gk = k0 + kk;
-                ra[e] = (gm < p.shape.M && gk < p.shape.K)
+                ra[e] = (gm < p.shape.M && gk < k_end)
                             ? __ldg(A + static_cast<long long>(gm) * p.aMs + static_cast<long long>(gk) * p.aKs)
                             : 0.f;
             }
@@ -84,13 +94,13 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
                 const int kk = b_kmaj ? (idx % BK) : (idx / BN);
                 const int nn = b_kmaj ? (idx / BK) : (idx % BN);
                 const int gn = n0 + nn, gk = k0 + kk;
-                rb[e] = (gn < p.shape.N && gk < p.shape.K)
+                rb[e] = (gn < p.shape.N && gk < k_end)
                             ? __ldg(B + static_cast<long long>(gn) * p.bNs + static_cast<long long>(gk) * p.bKs)
                             : 0.f;
             }
         };
-        if (p.shape.K > 0) fetch(0);
-        for (int k0 = 0; k0 < p.shape.K; k0 += BK) {
+        if (k_begin < k_end) fetch(k_begin);
+        for (int k0 = k_begin; k0 < k_end; k0 += BK) {
 #pragma unroll
             for (int e = 0; e < (BM * BK) / THREADS; e++) {
                 const int idx = tid + e * THREADS;
@@ -102,7 +112,7 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
                 Bs[b_kmaj ? (idx % BK) : (idx / BN)][b_kmaj ? (idx / BK) : (idx % BN)] = rb[e];
             }
             __syncthreads();
-            if (k0 + BK < p.shape.K) fetch(k0 + BK);
+            if (k0 + BK < k_end) fetch(k0 + BK);
 #pragma unroll
             for (int kk = 0; kk < BK; kk++) {
                 const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
@@ -117,20 +127,75 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
             __syncthreads();
         }
 
+        if (p.splits > 1) {
+            float* mine = p.partial + w * (BM * BN);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                *reinterpret_cast<float4*>(mine + (ty * 4 + i) * BN + tx * 4) =
+                    make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            continue;
+        }
         float* C = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int gm = m0 + ty * 4 + i;
             if (gm >= p.shape.M) continue;
+            const int gn0 = n0 + tx * 4;
+            float v[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int gn = n0 + tx * 4 + j;
-                if (gn >= p.shape.N) continue;
-                float v = acc[i][j];
-                if (p.epi.bias) v += __ldg(p.epi.bias + gn);
-                C[static_cast<long long>(gm) * p.shape.N + gn] = act_apply(v, p.epi.act);
+                v[j] = acc[i][j];
+                if (p.epi.bias && gn0 + j < p.shape.N) v[j] += __ldg(p.epi.bias + gn0 + j);
+                v[j] = act_apply(v[j], p.epi.act);
+            }
+            float* crow = C + static_cast<long long>(gm) * p.shape.N;
+            if (p.c_vec_ok && gn0 + 3 < p.shape.N) {
+                *reinterpret_cast<float4*>(crow + gn0) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (gn0 + j < p.shape.N) crow[gn0 + j] = v[j];
             }
         }
+    }
+}
+
+// C = act(sum over splits (ascending) of the partial tiles + bias); one thread per 4 columns.
+__global__ void __launch_bounds__(256)
+generic_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, GemmShape shape,
+                      Epilogue epi, int splits, int c_vec_ok)
+{
+    constexpr int PER_TILE = BM * BN / 4;
+    const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long tiles = static_cast<long long>(shape.batch) * shape.tiles_m * shape.tiles_n;
+    if (gid >= tiles * PER_TILE) return;
+    const long long unit = gid / PER_TILE;
+    const int e = static_cast<int>(gid - unit * PER_TILE);
+    const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
+    const int tiles_per_mat = shape.tiles_m * shape.tiles_n;
+    const int bidx = static_cast<int>(unit / tiles_per_mat);
+    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
+    const int r = (t / shape.tiles_n) * BM + lr, cidx = (t % shape.tiles_n) * BN + lc;
+    if (r >= shape.M || cidx >= shape.N) return;
+    const float* src = partial + unit * splits * (BM * BN) + lr * BN + lc;
+    float4 sum = *reinterpret_cast<const float4*>(src);
+    for (int sp = 1; sp < splits; sp++) {
+        const float4 q = *reinterpret_cast<const float4*>(src + static_cast<long long>(sp) * (BM * BN));
+        sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (epi.bias && cidx + j < shape.N) v[j] += __ldg(epi.bias + cidx + j);
+        v[j] = act_apply(v[j], epi.act);
+    }
+    float* crow = c + static_cast<long long>(bidx) * shape.M * shape.N + static_cast<long long>(r) * shape.N;
+    if (c_vec_ok && cidx + 3 < shape.N) {
+        *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (cidx + j < shape.N) crow[cidx + j] = v[j];
     }
 }
 

@@ -550,13 +550,22 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     if (!plan_batch(hb, b_bs, p.batch.b_slot, p.batch.b_mult, vb)) return 3;
     if (!tma_compatible(va) || !tma_compatible(vb)) return 3;
 
-    // Tile height: 256x256 tiles halve the L2->SM traffic per flop but have a single
-    // accumulator set (no epilogue overlap) and quantise worse; use them when the grid
-    // still fills the machine and K is long enough to amortise the exposed epilogue.
+    // Tile height.  With 128x256 tiles every k-tile moves 48 KB from L2 for 512 tensor-pipe
+    // cycles, and the measured L2->SM rate (about 11.2 TB/s over 148 SMs = 40 B/clk/SM) makes
+    // that L2-bound (~1235 clk per k-tile).  256x256 tiles move 64 KB for 1024 pipe cycles
+    // (~1650 clk for twice the work) but have a single accumulator set, so their epilogue
+    // (~4000 clk) is exposed, and they quantise worse on small grids.  Pick the cheaper
+    // estimate; it depends on the shape and the SM count only.
     int mt = 1;
     if (!split) {
-        const long long work2 = static_cast<long long>(batch_count) * ((M + 255) / 256) * ((N + BN - 1) / BN);
-        if (work2 >= 2ll * num_sms && K >= 2048) mt = 2;
+        const double k_tiles = (K + BK - 1) / BK;
+        const auto waves = [&](int bm) {
+            const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
+            return static_cast<double>((work + num_sms - 1) / num_sms);
+        };
+        const double t1 = waves(128) * (k_tiles * 1235.0 + 1500.0);
+        const double t2 = waves(256) * (k_tiles * 1650.0 + 5500.0);
+        if (t2 < t1) mt = 2;
     }
     if (forced_mt == 1 || forced_mt == 2) mt = split ? 1 : forced_mt;
     const int bm = 128 * mt;

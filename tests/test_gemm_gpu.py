@@ -130,9 +130,16 @@ def test_bitwise_repeatable_and_grid_independent(rt):
     r1 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 2)
     r2 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 2)
     assert np.array_equal(r1, r2)
-    for other in (1, 3):   # any-stride kernel, 128x128-tile kernel
-        r3 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), other)
-        assert np.array_equal(r1, r3)  # all kernels: one accumulator per output, ascending k, fmaf
+    r3 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 3)   # 128x128-tile kernel
+    assert np.array_equal(r1, r3)  # both: one accumulator per output, ascending k, fused multiply-add
+    # the any-stride kernel cuts K for this small grid (fixed-order partial sums): same bound, other bits
+    r4 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 1)
+    exp = oracle.matmul2d(a, b, M, N, K, K, 1, N, 1)
+    assert np.abs(r4 - exp).max() <= fp32_bound(K, a, b)
+    # without split-K (short K) the any-stride kernel also reproduces the bits
+    a2, b2 = a[:M * 256].copy(), b[:256 * N].copy()
+    assert np.array_equal(run_matmul(rt, a2, b2, M, N, 256, (256, 1, N, 1), 2),
+                          run_matmul(rt, a2, b2, M, N, 256, (256, 1, N, 1), 1))
 
 
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
@@ -154,6 +161,26 @@ def test_split_k_matches_oracle_and_is_repeatable(rt, shape, layout):
     assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
     if (M, N, K) == (256, 256, 2048) and M % 4 == 0:
         assert used_split == 1
+
+
+@pytest.mark.parametrize("case", [
+    # (M, N, K, aMs, aKs, bKs, bNs): the last MLP layer's backward (10 classes): leading
+    # dimensions of 10 floats cannot be described by TMA, so the any-stride kernel serves them
+    (8192, 4096, 10, 10, 1, 4096, 1),      # dx = g (8192x10) . W (10x4096)
+    (10, 4096, 8192, 1, 10, 4096, 1),      # dW = g^T (10x8192) . x (8192x4096): split-K
+    (64, 64, 4096, 4096, 1, 64, 1),        # one tile, long K
+    (7, 5, 3000, 3000, 1, 1, 3000),        # ragged NT
+])
+def test_any_stride_kernel_skinny_and_split_k(rt, case):
+    M, N, K, aMs, aKs, bKs, bNs = case
+    rng = np.random.default_rng(M + N + K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    r1 = run_matmul(rt, a, b, M, N, K, (aMs, aKs, bKs, bNs), 1)
+    r2 = run_matmul(rt, a, b, M, N, K, (aMs, aKs, bKs, bNs), 1)
+    assert np.array_equal(r1, r2)
+    exp = oracle.matmul2d(a, b, M, N, K, aMs, aKs, bKs, bNs)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
 
 
 def test_nan_propagates_like_reference(rt):

@@ -348,21 +348,67 @@ def main():
     hc = torch.empty((rows, n), pin_memory=True)
     e2e_steps = max(1, min(args.steps, 5))
 
-    def e2e_step():
-        a.copy_(ha, non_blocking=True)
-        b.copy_(hb, non_blocking=True)
-        rt.LaunchMatMul(a, b, c, rows, n, n, n, 1, n, 1)
-        hc.copy_(c, non_blocking=True)
+    # Every step copies its operands from pinned host memory and returns its C-shard to the
+    # host.  A step is cut into row chunks on three streams (H2D, compute, D2H) so the copies
+    # of one chunk overlap the GEMM of another; two device buffer sets alternate between
+    # steps so step j+1 may start copying while step j still computes.
+    n_chunks = 4 if rows % 4 == 0 and rows >= 1024 else 1
+    crow = rows // n_chunks
+    s_h2d, s_d2h = torch.cuda.Stream(), torch.cuda.Stream()
+    sets = [(a, b, c), (torch.empty_like(a), torch.empty_like(b), torch.empty_like(c))]
+    d2h_done = [[None] * n_chunks for _ in range(2)]     # per set, per chunk: event of the last D2H
+    comp_done = [None, None]                             # per set: event of the last GEMM reading it
 
-    e2e_step()
+    def e2e_step(j):
+        da, db, dc = sets[j % 2]
+        with torch.cuda.stream(s_h2d):
+            if comp_done[j % 2] is not None:
+                s_h2d.wait_event(comp_done[j % 2])       # the set's previous GEMMs are done reading
+            db.copy_(hb, non_blocking=True)
+            ev_b = torch.cuda.Event()
+            ev_b.record(s_h2d)
+            ev_a = []
+            for i in range(n_chunks):
+                da[i * crow:(i + 1) * crow].copy_(ha[i * crow:(i + 1) * crow], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_h2d)
+                ev_a.append(ev)
+        stream.wait_event(ev_b)
+        for i in range(n_chunks):
+            stream.wait_event(ev_a[i])
+            if d2h_done[j % 2][i] is not None:
+                stream.wait_event(d2h_done[j % 2][i])    # the C chunk was copied out before reuse
+            rt.LaunchMatMul(da[i * crow:(i + 1) * crow], db, dc[i * crow:(i + 1) * crow],
+                            crow, n, n, n, 1, n, 1, stream=stream)
+            ev_c = torch.cuda.Event()
+            ev_c.record(stream)
+            with torch.cuda.stream(s_d2h):
+                s_d2h.wait_event(ev_c)
+                hc[i * crow:(i + 1) * crow].copy_(dc[i * crow:(i + 1) * crow], non_blocking=True)
+                ev_d = torch.cuda.Event()
+                ev_d.record(s_d2h)
+            d2h_done[j % 2][i] = ev_d
+        comp_done[j % 2] = ev_c
+
+    def e2e_drain():
+        for per_set in d2h_done:
+            for ev in per_set:
+                if ev is not None:
+                    stream.wait_event(ev)
+
+    e2e_step(0)
+    e2e_drain()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
+    s_h2d.wait_event(e0)
+    for j in range(e2e_steps):
+        e2e_step(j + 1)
+    e2e_drain()                                          # the last result has reached the host
     e1.record(stream)
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    del sets, s_h2d, s_d2h
 
     del ha, hb, hc
     extras = {}
@@ -413,7 +459,8 @@ def main():
                        % (rows * n * 4 / 2 ** 20, n * n * 4 / 2 ** 20)},
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (rows * n + n * n) * 4,
-                    "d2h_bytes_per_step": rows * n * 4, "steps": e2e_steps},
+                    "d2h_bytes_per_step": rows * n * 4, "steps": e2e_steps,
+                    "pipeline": "%d row chunks per step on H2D / compute / D2H streams, two buffer sets" % n_chunks},
             "gpu_launches": launches,
             "roofline": roof,
         }

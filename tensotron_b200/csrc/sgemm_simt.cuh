@@ -44,7 +44,11 @@ constexpr int RASTER_GROUP = 8;
 #ifndef TT_G_UNROLL
 #define TT_G_UNROLL 4
 #endif
-constexpr int G_UNROLL = TT_G_UNROLL;  // k groups (of 4) unrolled in the main loop; bounds code size
+#ifndef TT_KG
+#define TT_KG 4
+#endif
+constexpr int KG = TT_KG;              // k-steps whose fragments are loaded together
+constexpr int G_UNROLL = TT_G_UNROLL;  // k groups unrolled in the main loop; bounds code size
 
 template <int TM, bool A_KMAJ, bool B_KMAJ>
 struct Cfg {
@@ -308,26 +312,26 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint8_t* sb = (B_KMAJ ? smem + C::OFF_TB + tb * C::TB_BYTES : st + C::RAW_A) + off_bm;
 
 #pragma unroll G_UNROLL
-            for (int g = 0; g < BK / 4; g++) {  // 8 groups of 4 k
-                const uint8_t* sag = sa + g * 4 * C::ROWB_A;
-                const uint8_t* sbg = sb + g * 4 * C::ROWB_B;
-                float4 bm[4][2];  // [k][half] = 4 adjacent cols
+            for (int g = 0; g < BK / KG; g++) {  // groups of KG k-steps
+                const uint8_t* sag = sa + g * KG * C::ROWB_A;
+                const uint8_t* sbg = sb + g * KG * C::ROWB_B;
+                float4 bm[KG][2];  // [k][half] = 4 adjacent cols
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++)
+                for (int kk = 0; kk < KG; kk++)
 #pragma unroll
                     for (int jb = 0; jb < 2; jb++)
                         bm[kk][jb] = *reinterpret_cast<const float4*>(sbg + kk * C::ROWB_B + jb * 128);
 #pragma unroll
                 for (int h = 0; h < HALVES; h++) {
-                    float4 am[4][2];  // [k][ib] = 4 adjacent rows
+                    float4 am[KG][2];  // [k][ib] = 4 adjacent rows
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++)
+                    for (int kk = 0; kk < KG; kk++)
 #pragma unroll
                         for (int ib = 0; ib < 2; ib++)
                             am[kk][ib] = *reinterpret_cast<const float4*>(
                                 sag + kk * C::ROWB_A + (h * 32 + ib * 16) * 4);
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++) {
+                    for (int kk = 0; kk < KG; kk++) {
                         float2 a2[4], b2[4], b2s[4];
 #pragma unroll
                         for (int pr = 0; pr < 4; pr++) {  // row pairs of this half

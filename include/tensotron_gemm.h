@@ -87,6 +87,19 @@ TT_API int tt_matmul_batched(tt_handle_t h, void* stream, const float* a, const 
                       int batchRank, const int* batchDims, const int* aBatchStrides,
                       const int* bBatchStrides);
 
+/* Batched product whose output is summed over some batch axes: what the MatMulND backward
+ * closures compute as RawBmm followed by ReduceGradToShape
+ * (src/Tensotron/TensorOps.MatMulND.cs:80-103, src/Tensotron/TensorOps.cs:76-100) when an
+ * operand was broadcast along batch axes.  reduceAxis[ax] != 0 marks an axis that is summed;
+ * C is contiguous over the remaining axes (in order) x (M, N).  The sum runs inside the
+ * kernel's k loop in ascending axis order (no temporary of the full batch shape, no
+ * atomics).  The summed axes must merge into one strided axis (TT_ERR_UNSUPPORTED
+ * otherwise; the caller then uses the unfused path).  Always strict FP32. */
+TT_API int tt_matmul_batched_reduce(tt_handle_t h, void* stream, const float* a, const float* b, float* c,
+                             int M, int N, int K, int aMs, int aKs, int bKs, int bNs, int batchRank,
+                             const int* batchDims, const int* aBatchStrides,
+                             const int* bBatchStrides, const int* reduceAxis);
+
 /* Linear.Forward (+ the Activation module that follows it) as one launch
  * (src/Tensotron/Module.cs:100-105, src/Tensotron/TensorOps.LinearNT.cs:13-25):
  *   y = act(x (M,K) . w (N,K)^T + bias (N)),  bias may be NULL. */
@@ -151,6 +164,7 @@ typedef struct tt_stats {
     long long tcgen05;         /* calls served by the tcgen05 TF32 / 3xTF32 kernel        */
     long long generic;         /* calls served by the any-stride kernel                   */
     long long splitk;          /* calls that used the split-K workspace                   */
+    long long skinny;          /* calls served by the tiny-dimension streaming kernels    */
     long long workspace_bytes; /* size of the handle workspace                            */
 } tt_stats;
 TT_API int tt_get_stats(tt_handle_t h, tt_stats* out);

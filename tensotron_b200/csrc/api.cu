@@ -12,6 +12,7 @@
 #include "gemm_common.h"
 #include "gemm_generic.cuh"
 #include "sgemm_simt.cuh"
+#include "skinny.cuh"
 #include "tensor_map.h"
 #include "tf32_launch.h"
 
@@ -55,6 +56,9 @@ struct HostBatch {
     int dims[MAX_BATCH_RANK];
     int as[MAX_BATCH_RANK];
     int bs[MAX_BATCH_RANK];
+    // one merged batch axis that is summed into the output (1 = none)
+    int red_count = 1;
+    int red_as = 0, red_bs = 0;
 };
 
 // Drops size-1 axes and merges adjacent axes that are jointly contiguous for both
@@ -90,7 +94,7 @@ bool collapse_batch(int rank, const int* dims, const int* as, const int* bs, Hos
 // axes, merging an axis into the open slot when it continues it contiguously.
 // Fills slot/mult for the kernel and appends (extent, stride) to the view.
 bool plan_tma_batch(const HostBatch& hb, const int* strides, signed char* slot, int* mult,
-                    OperandView& view)
+                    OperandView& view, int red_stride, signed char* red_slot)
 {
     int nslots = 0;
     long long cur_extent = 0, cur_stride = 0;
@@ -114,6 +118,15 @@ bool plan_tma_batch(const HostBatch& hb, const int* strides, signed char* slot, 
         slot_stride[nslots] = strides[ax];
         nslots++;
     }
+    *red_slot = -1;
+    if (hb.red_count > 1 && red_stride != 0) {
+        // the reduced axis gets a coordinate slot of its own
+        if (nslots == 3) return false;
+        *red_slot = static_cast<signed char>(nslots);
+        slot_extent[nslots] = hb.red_count;
+        slot_stride[nslots] = red_stride;
+        nslots++;
+    }
     for (int s = 0; s < nslots; s++) {
         if (slot_stride[s] < 0) return false;
         view.dim[view.rank] = static_cast<uint64_t>(slot_extent[s]);
@@ -133,6 +146,10 @@ void fill_batch_desc(const HostBatch& hb, BatchDesc& bd)
         bd.b_stride[i] = hb.bs[i];
         bd.a_slot[i] = bd.b_slot[i] = -1;
     }
+    bd.red_count = hb.red_count;
+    bd.red_a_stride = hb.red_as;
+    bd.red_b_stride = hb.red_bs;
+    bd.red_a_slot = bd.red_b_slot = -1;
 }
 
 // ---- operand classification -----------------------------------------------------
@@ -189,7 +206,7 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     // SM, at least 64 k per range, and only as far as the workspace holds the partial tiles.
     int splits = 1, kspan = g.K > 0 ? g.K : 1;
     const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
-    if (tiles < h->num_sms && g.K >= 512) {
+    if (tiles < h->num_sms && g.K >= 512 && g.batch.red_count == 1) {
         long long want = (2ll * h->num_sms + tiles - 1) / tiles;
         const long long max_by_k = g.K / 64;
         if (want > max_by_k) want = max_by_k;
@@ -252,9 +269,10 @@ struct SimtPlan {
     int kps;
 };
 
-SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail)
+SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail, int red_count)
 {
     const int k_tiles = (K + simt::BK - 1) / simt::BK;
+    if (red_count > 1) ws_avail = 0;  // a reduced batch axis already lengthens the k loop: no split-K
     SimtPlan best{16, 1, k_tiles};
     double best_t = 1e300;
     for (int tm : {16, 8}) {
@@ -275,7 +293,8 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             const long long waves = (work + h->num_sms - 1) / h->num_sms;
             // per work item: kps k-tiles + ~2 k-tiles worth of pipeline fill / epilogue; the
             // reduction kernel costs about as much as two more k-tiles of a 128x128 tile
-            const double t = static_cast<double>(waves) * (kps + 2.0) * tile_cost + (splits > 1 ? 2.0 / 0.70 : 0.0);
+            const double t = static_cast<double>(waves) * (static_cast<double>(kps) * red_count + 2.0) * tile_cost +
+                             (splits > 1 ? 2.0 / 0.70 : 0.0);
             if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps}; }
         }
     }
@@ -295,8 +314,8 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     simt::Params p;
     memset(&p, 0, sizeof(p));
     fill_batch_desc(g.batch, p.batch);
-    if (!plan_tma_batch(g.batch, g.batch.as, p.batch.a_slot, p.batch.a_mult, va)) return TT_ERR_UNSUPPORTED;
-    if (!plan_tma_batch(g.batch, g.batch.bs, p.batch.b_slot, p.batch.b_mult, vb)) return TT_ERR_UNSUPPORTED;
+    if (!plan_tma_batch(g.batch, g.batch.as, p.batch.a_slot, p.batch.a_mult, va, g.batch.red_as, &p.batch.red_a_slot)) return TT_ERR_UNSUPPORTED;
+    if (!plan_tma_batch(g.batch, g.batch.bs, p.batch.b_slot, p.batch.b_mult, vb, g.batch.red_bs, &p.batch.red_b_slot)) return TT_ERR_UNSUPPORTED;
     if (!tma_compatible(va) || !tma_compatible(vb)) return TT_ERR_UNSUPPORTED;
 
     CUtensorMap ma, mb;
@@ -343,7 +362,7 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
 int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 {
     const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
-    SimtPlan plan = plan_simt(h, g.M, g.N, g.K, g.batch_count, ws_avail);
+    SimtPlan plan = plan_simt(h, g.M, g.N, g.K, g.batch_count, ws_avail, g.batch.red_count);
     if (h->variant == 2 || h->variant == 3) {
         // pinned tile height (A/B measurements and tests): no split-K
         plan.tm = h->variant == 2 ? 16 : 8;
@@ -351,6 +370,60 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         plan.kps = (g.K + simt::BK - 1) / simt::BK;
     }
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
+}
+
+// Products with one tiny dimension: HBM-bound streaming kernels (skinny.cuh).  Returns
+// TT_ERR_UNSUPPORTED when the call is not one of the handled forms.
+int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
+{
+    if (g.batch_count != 1 || g.batch.red_count != 1 || g.K <= 0) return TT_ERR_UNSUPPORTED;
+    const bool bias_ok = !g.epi.bias || aligned16(g.epi.bias);
+    const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
+    // (the tiny-N form only in strict FP32: in the TF32 modes the tensor-core kernel is faster)
+    if (h->math_mode == TT_MATH_FP32 && g.N <= skinny::MAXD && g.M >= 64 && g.K >= 128 && g.aKs == 1 && g.bKs == 1 && g.K % 4 == 0 &&
+        g.aMs % 4 == 0 && (g.N == 1 || g.bNs % 4 == 0) && aligned16(g.a) && aligned16(g.b)) {
+        // 8 rows per warp while the accumulators fit comfortably; 4 rows for N > 8 (8 x 16
+        // accumulators need 254 registers and run slower: 143 vs 91 us at 8192 x 10 x 4096)
+        const int rows = g.N <= 8 ? 8 : 4;
+        const long long warps = (g.M + rows - 1) / rows;
+        const unsigned int blocks = static_cast<unsigned int>((warps + 7) / 8);
+        if (g.N <= 4)
+            skinny::skinny_n_kernel<8, 4><<<blocks, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.bNs, g.epi);
+        else if (g.N <= 8)
+            skinny::skinny_n_kernel<8, 8><<<blocks, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.bNs, g.epi);
+        else
+            skinny::skinny_n_kernel<4, 16><<<blocks, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.bNs, g.epi);
+        h->stats.launches++;
+    } else if (g.M <= skinny::MAXD && g.N >= 256 && g.K >= 256 && g.bNs == 1 && g.N % 4 == 0 &&
+               g.bKs % 4 == 0 && aligned16(g.b) && aligned16(g.c) && bias_ok) {
+        const int gx = (g.N / 4 + 63) / 64;
+        long long ranges = (4ll * h->num_sms + gx - 1) / gx;
+        if (ranges > g.K / 64) ranges = g.K / 64;
+        const size_t per_range = sizeof(float) * static_cast<size_t>(g.M) * g.N;
+        if (ranges > 1 && ranges * per_range > ws_avail) ranges = static_cast<long long>(ws_avail / per_range);
+        if (ranges < 1) ranges = 1;
+        int kspan = static_cast<int>((g.K + ranges - 1) / ranges);
+        kspan = (kspan + 3) & ~3;
+        const int n_ranges = (g.K + kspan - 1) / kspan;
+        float* partial = reinterpret_cast<float*>(h->workspace + g.ws_off);
+        skinny::skinny_m_kernel<<<dim3(gx, n_ranges), 256, 0, st>>>(
+            g.a, g.b, n_ranges == 1 ? g.c : partial, g.M, g.N, g.K, g.aMs, g.aKs, g.bKs, kspan, g.epi,
+            n_ranges == 1 ? 1 : 0);
+        h->stats.launches++;
+        if (n_ranges > 1) {
+            const long long count4 = static_cast<long long>(g.M) * g.N / 4;
+            skinny::skinny_reduce_kernel<<<static_cast<unsigned int>((count4 + 255) / 256), 256, 0, st>>>(
+                partial, g.c, count4, g.N, n_ranges, static_cast<long long>(g.M) * g.N, g.epi);
+            h->stats.launches++;
+            h->stats.splitk++;
+        }
+    } else {
+        return TT_ERR_UNSUPPORTED;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "skinny gemm launch");
+    h->stats.skinny++;
+    return TT_OK;
 }
 
 int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
@@ -363,8 +436,14 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         return TT_OK;
     }
     const long long vol = static_cast<long long>(g.M) * g.N * (g.K > 0 ? g.K : 1);
+    if (g.K > 0 && h->variant == 0) {
+        // one tiny dimension: stream the large operand once, in every math mode (strict FP32
+        // arithmetic, so at least as accurate as the mode asks for)
+        const int rc = try_launch_skinny(h, st, g);
+        if (rc != TT_ERR_UNSUPPORTED) return rc;
+    }
     if (g.K > 0 && h->variant != 1) {
-        if (h->math_mode != TT_MATH_FP32) {
+        if (h->math_mode != TT_MATH_FP32 && g.batch.red_count == 1) {  // the tensor-core kernel has no reduced axis
             int n_launch = 0;
             const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
                                             g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,
@@ -535,6 +614,49 @@ TT_API int tt_matmul_batched(tt_handle_t h, void* stream, const float* a, const 
     if (batchCount == 0) return TT_OK;
     if (!collapse_batch(batchRank, batchDims, aBatchStrides, bBatchStrides, g.batch))
         return fail(h, TT_ERR_UNSUPPORTED, "more than 8 non-mergeable batch axes");
+    return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+TT_API int tt_matmul_batched_reduce(tt_handle_t h, void* stream, const float* a, const float* b, float* c,
+                                    int M, int N, int K, int aMs, int aKs, int bKs, int bNs, int batchRank,
+                                    const int* batchDims, const int* aBatchStrides,
+                                    const int* bBatchStrides, const int* reduceAxis)
+{
+    int rc = check_common(h, a, b, c, M, N, K);
+    if (rc) return rc;
+    if (batchRank < 0 || batchRank > 32) return fail(h, TT_ERR_INVALID_ARG, "bad batch rank");
+    if (batchRank > 0 && (!batchDims || !aBatchStrides || !bBatchStrides || !reduceAxis))
+        return fail(h, TT_ERR_INVALID_ARG, "null batch arrays");
+    int kd[32], ka[32], kb[32], nk = 0;
+    HostBatch hb;
+    bool have_red = false;
+    long long kept = 1;
+    for (int ax = 0; ax < batchRank; ax++) {
+        if (batchDims[ax] < 0) return fail(h, TT_ERR_INVALID_ARG, "negative batch dim");
+        if (batchDims[ax] == 0) return TT_OK;  // empty batch: nothing to compute (C is empty or stays as is)
+        if (reduceAxis[ax] && batchDims[ax] > 1) {
+            if (!have_red) {
+                hb.red_count = batchDims[ax]; hb.red_as = aBatchStrides[ax]; hb.red_bs = bBatchStrides[ax];
+                have_red = true;
+            } else if (static_cast<long long>(hb.red_as) == static_cast<long long>(batchDims[ax]) * aBatchStrides[ax] &&
+                       static_cast<long long>(hb.red_bs) == static_cast<long long>(batchDims[ax]) * bBatchStrides[ax]) {
+                hb.red_count *= batchDims[ax]; hb.red_as = aBatchStrides[ax]; hb.red_bs = bBatchStrides[ax];
+            } else {
+                return fail(h, TT_ERR_UNSUPPORTED, "reduced batch axes do not merge into one");
+            }
+        } else if (!reduceAxis[ax]) {
+            kd[nk] = batchDims[ax]; ka[nk] = aBatchStrides[ax]; kb[nk] = bBatchStrides[ax];
+            kept *= batchDims[ax];
+            nk++;
+        }
+    }
+    if ((rc = bind(h))) return rc;
+    h->stats.calls++;
+    const int rc_n = hb.red_count, rc_a = hb.red_as, rc_b = hb.red_bs;
+    if (!collapse_batch(nk, kd, ka, kb, hb))
+        return fail(h, TT_ERR_UNSUPPORTED, "more than 8 non-mergeable batch axes");
+    hb.red_count = rc_n; hb.red_as = rc_a; hb.red_bs = rc_b;
+    GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, hb, static_cast<int>(kept), Epilogue{nullptr, TT_ACT_NONE}};
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
 }
 

@@ -25,6 +25,11 @@ struct BatchDesc {
     signed char b_slot[MAX_BATCH_RANK];
     int a_mult[MAX_BATCH_RANK];
     int b_mult[MAX_BATCH_RANK];
+    // One extra batch axis that is summed into the output (fused reduction of a broadcast
+    // operand's gradient): red_count entries, visited in ascending order inside the k loop.
+    int red_count;                 // 1 = no reduced axis
+    int red_a_stride, red_b_stride;  // any-stride kernels: element strides of that axis
+    signed char red_a_slot, red_b_slot;  // TMA kernels: coordinate slot or -1
 };
 
 struct GemmShape {

@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
             a_off += static_cast<long long>(bi) * p.batch.a_stride[ax];
             b_off += static_cast<long long>(bi) * p.batch.b_stride[ax];
         }
-        const float* A = p.a + a_off;
-        const float* B = p.b + b_off;
+        const float* A0 = p.a + a_off;
+        const float* B0 = p.b + b_off;
         const int m0 = tm * BM, n0 = tn * BN;
 
         float acc[4][4];
@@ -74,6 +74,10 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
 #pragma unroll
             for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
 
+        // Entries of a reduced batch axis are accumulated in ascending order.
+        for (int red = 0; red < p.batch.red_count; red++) {
+        const float* A = A0 + static_cast<long long>(red) * p.batch.red_a_stride;
+        const float* B = B0 + static_cast<long long>(red) * p.batch.red_b_stride;
         // Global loads of k-tile i+1 are issued into registers before the FMAs of k-tile i,
         // so the global-memory latency overlaps the arithmetic.
         float ra[(BM * BK) / THREADS], rb[(BN * BK) / THREADS];
@@ -126,6 +130,7 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
             }
             __syncthreads();
         }
+        }  // reduced axis
 
         if (p.splits > 1) {
             float* mine = p.partial + w * (BM * BN);

@@ -103,6 +103,7 @@ __device__ __forceinline__ float apply_act(float v, int act)
 struct LoadCursor {
     long long w;
     int kt, ke;   // next k-tile to load, end of this work item's k range
+    int kb, r;    // start of the k range; index along the reduced batch axis
     int fresh;    // 1: the next load starts a new work item
     int m0, n0;
     int ca0, ca1, ca2, cb0, cb1, cb2;
@@ -117,6 +118,8 @@ __device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p
     const int split = static_cast<int>(cur.w - unit * p.splits);
     cur.kt = split * p.kps;
     cur.ke = min(k_tiles, cur.kt + p.kps);
+    cur.kb = cur.kt;
+    cur.r = 0;
     cur.fresh = 0;
     const int bidx = static_cast<int>(unit / tiles_per_mat);
     const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
@@ -230,12 +233,22 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         uint8_t* sb = sa + C::RAW_A;
         mbar_arrive_expect_tx(&full_bar[ps], C::STAGE_BYTES);
         const int k0 = cur.kt * BK;
-        if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[ps], k0, cur.m0, cur.ca0, cur.ca1, cur.ca2);
-        else        tma_load_5d(sa, &map_a, &full_bar[ps], cur.m0, k0, cur.ca0, cur.ca1, cur.ca2);
-        if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, cur.n0, cur.cb0, cur.cb1, cur.cb2);
-        else        tma_load_5d(sb, &map_b, &full_bar[ps], cur.n0, k0, cur.cb0, cur.cb1, cur.cb2);
+        // the reduced batch axis has a coordinate slot of its own (or none when the operand
+        // is broadcast along it)
+        const int sra = p.batch.red_a_slot, srb = p.batch.red_b_slot;
+        const int ca0 = cur.ca0 + (sra == 0 ? cur.r : 0), ca1 = cur.ca1 + (sra == 1 ? cur.r : 0),
+                  ca2 = cur.ca2 + (sra == 2 ? cur.r : 0);
+        const int cb0 = cur.cb0 + (srb == 0 ? cur.r : 0), cb1 = cur.cb1 + (srb == 1 ? cur.r : 0),
+                  cb2 = cur.cb2 + (srb == 2 ? cur.r : 0);
+        if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[ps], k0, cur.m0, ca0, ca1, ca2);
+        else        tma_load_5d(sa, &map_a, &full_bar[ps], cur.m0, k0, ca0, ca1, ca2);
+        if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, cur.n0, cb0, cb1, cb2);
+        else        tma_load_5d(sb, &map_b, &full_bar[ps], cur.n0, k0, cb0, cb1, cb2);
         if (ps + 1 == STAGES) { cur.stage = 0; cur.use++; } else { cur.stage = ps + 1; }
-        if (++cur.kt == cur.ke) { cur.fresh = 1; cur.w += gridDim.x; }
+        if (++cur.kt == cur.ke) {
+            if (++cur.r < p.batch.red_count) cur.kt = cur.kb;   // same k range, next reduced entry
+            else { cur.fresh = 1; cur.w += gridDim.x; }
+        }
     };
 
     if (tid == 0) {
@@ -300,7 +313,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int j = 0; j < 4; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
 
 #pragma unroll 1
-        for (int kt = kb; kt < ke; kt++) {
+        const int iters = (ke - kb) * p.batch.red_count;  // k-tiles x entries of the reduced axis
+        for (int it = 0; it < iters; it++) {
             if (tid == 0) produce_one();
             bool ok = true;
             if (!C::HAS_T)
@@ -311,8 +325,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint8_t* sa = (A_KMAJ ? smem + C::OFF_TA + tb * C::TA_BYTES : st) + off_am;
             const uint8_t* sb = (B_KMAJ ? smem + C::OFF_TB + tb * C::TB_BYTES : st + C::RAW_A) + off_bm;
 
-#pragma unroll G_UNROLL
-            for (int g = 0; g < BK / KG; g++) {  // groups of KG k-steps
+            const auto k_group = [&](int g) {  // one group of KG k-steps
                 const uint8_t* sag = sa + g * KG * C::ROWB_A;
                 const uint8_t* sbg = sb + g * KG * C::ROWB_B;
                 float4 bm[KG][2];  // [k][half] = 4 adjacent cols
@@ -353,7 +366,9 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             }
                     }
                 }
-            }
+            };
+#pragma unroll G_UNROLL
+            for (int g = 0; g < BK / KG; g++) k_group(g);
 
             // advance to the next k-tile's stage
             uint32_t nstage = stage + 1, nphase = phase;
@@ -364,7 +379,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (lane == 0) mbar_arrive(&empty_bar[stage]);
             }
             if (C::HAS_T) {
-                if (!(last_tile && kt == ke - 1)) {  // a next k-tile exists
+                if (!(last_tile && it == iters - 1)) {  // a next k-tile exists
                     if (mbar_wait_bounded(&full_bar[nstage], nphase, cta_abort, p.status, DEV_WAIT_FULL)) {
                         transpose_stage(nstage, tb ^ 1u);
                         if (C::ALL_T) {

@@ -75,9 +75,9 @@ def _raw_bmm(a, b, M, N, K, aMs, aKs, bKs, bNs, batch_dims, aBs, bBs):
 
 
 def _reduce_grad_to_shape(g, shape):
-    """ReduceGradToShape (src/Tensotron/TensorOps.cs:76-100): sum over broadcast axes.
-    The reduction itself is not part of the GEMM engine; torch.sum stands in for
-    LaunchReduceSum here."""
+    """ReduceGradToShape (src/Tensotron/TensorOps.cs:76-100): sum over broadcast axes.  Only
+    reached when the broadcast axes cannot be fused into the batched GEMM (they do not merge
+    into one strided axis); torch.sum stands in for LaunchReduceSum there."""
     shape = tuple(shape)
     if tuple(g.shape) == shape:
         return g.clone()
@@ -89,6 +89,30 @@ def _reduce_grad_to_shape(g, shape):
         if dt != g.shape[j]:
             axes.append(j)
     return g.sum(dim=axes, keepdim=True).reshape(shape)
+
+
+def _bmm_reduced(x, y, M, N, K, xMs, xKs, yKs, yNs, batch_dims, xBs, yBs, target_shape):
+    """RawBmm followed by ReduceGradToShape(., target_shape), fused into one launch when the
+    broadcast axes merge into one (src/Tensotron/TensorOps.MatMulND.cs:80-103); otherwise the
+    unfused pair."""
+    r = len(batch_dims)
+    tb = tuple(target_shape[:-2])
+    reduce_axis = []
+    for j in range(r):
+        axt = j - (r - len(tb))
+        dt = tb[axt] if axt >= 0 else 1
+        reduce_axis.append(1 if dt != batch_dims[j] else 0)
+    if any(reduce_axis):
+        out = torch.empty(tuple(target_shape), dtype=torch.float32, device=x.device)
+        try:
+            runtime(x.device.index).LaunchMatMulBatchedReduce(x, y, out, M, N, K, xMs, xKs, yKs, yNs,
+                                                              batch_dims, xBs, yBs, reduce_axis)
+            return out
+        except TensotronGemmError as e:
+            if e.status != 3:
+                raise
+    full = _raw_bmm(x, y, M, N, K, xMs, xKs, yKs, yNs, batch_dims, xBs, yBs)
+    return _reduce_grad_to_shape(full, target_shape)
 
 
 def _matmul_nd(a, b):
@@ -110,12 +134,10 @@ def _matmul_nd_backward(a, b, g):
     gMs, gNs = g_str[-2], g_str[-1]
     # dA[.,m,k] = sum_n g[.,m,n] * B[.,k,n]   (TensorOps.MatMulND.cs:80-91)
     bd, gBs2, bBs2 = broadcast_batch(g.shape[:-2], g_str[:-2], b.shape[:-2], b_str[:-2])
-    dA = _raw_bmm(g, b, M, K, N, gMs, gNs, b_str[-1], b_str[-2], bd, gBs2, bBs2)
-    dA = _reduce_grad_to_shape(dA, a.shape)
+    dA = _bmm_reduced(g, b, M, K, N, gMs, gNs, b_str[-1], b_str[-2], bd, gBs2, bBs2, a.shape)
     # dB[.,k,n] = sum_m A[.,m,k] * g[.,m,n]   (TensorOps.MatMulND.cs:92-103)
     bd, aBs2, gBs3 = broadcast_batch(a.shape[:-2], a_str[:-2], g.shape[:-2], g_str[:-2])
-    dB = _raw_bmm(a, g, K, N, M, a_str[-1], a_str[-2], gMs, gNs, bd, aBs2, gBs3)
-    dB = _reduce_grad_to_shape(dB, b.shape)
+    dB = _bmm_reduced(a, g, K, N, M, a_str[-1], a_str[-2], gMs, gNs, bd, aBs2, gBs3, b.shape)
     return dA, dB
 
 

@@ -18,7 +18,7 @@ ACT = {None: 0, "none": 0, "relu": 1, "tanh": 2, 0: 0, 1: 1, 2: 2}
 
 EXPORTS = [
     "tt_version", "tt_create", "tt_destroy", "tt_last_error", "tt_set_math_mode", "tt_get_math_mode",
-    "tt_matmul", "tt_matmul_batched", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
+    "tt_matmul", "tt_matmul_batched", "tt_matmul_batched_reduce", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
     "tt_set_variant", "tt_softmax_cross_entropy_static",
 ]
@@ -32,7 +32,7 @@ class TensotronGemmError(RuntimeError):
 
 class Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_longlong) for n in
-                ("launches", "calls", "simt_tma", "tcgen05", "generic", "splitk", "workspace_bytes")]
+                ("launches", "calls", "simt_tma", "tcgen05", "generic", "splitk", "skinny", "workspace_bytes")]
 
 
 _lib = None
@@ -60,6 +60,7 @@ def load_library(path=None):
     L.tt_get_math_mode.argtypes = [vp, ip]
     L.tt_matmul.argtypes = [vp, vp, vp, vp, vp] + [i] * 7
     L.tt_matmul_batched.argtypes = [vp, vp, vp, vp, vp] + [i] * 9 + [ip, ip, ip]
+    L.tt_matmul_batched_reduce.argtypes = [vp, vp, vp, vp, vp] + [i] * 8 + [ip, ip, ip, ip]
     L.tt_linear_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i]
     L.tt_linear_bwd.argtypes = [vp, vp] + [vp] * 7 + [i, i, i, i]
     L.tt_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, vp, i, i, f]
@@ -193,6 +194,15 @@ class TensorRuntime:
             self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c), batchCount, M, N, K,
             aMs, aKs, bKs, bNs, len(batchDims), _iarr(batchDims), _iarr(aBatchStrides),
             _iarr(bBatchStrides)))
+
+    def LaunchMatMulBatchedReduce(self, a, b, c, M, N, K, aMs, aKs, bKs, bNs,
+                                  batchDims, aBatchStrides, bBatchStrides, reduceAxis, stream=None):
+        """RawBmm + ReduceGradToShape in one launch; raises status 3 when the summed axes do
+        not merge (the caller then reduces separately)."""
+        self._ck(self._L.tt_matmul_batched_reduce(
+            self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c), M, N, K, aMs, aKs, bKs, bNs,
+            len(batchDims), _iarr(batchDims), _iarr(aBatchStrides), _iarr(bBatchStrides),
+            _iarr(reduceAxis)))
 
     def LaunchLinearForward(self, x, w, bias, y, M, N, K, act=0, stream=None):
         self._ck(self._L.tt_linear_fwd(self._h, self._st(stream), _ptr(x), _ptr(w), _ptr(bias),

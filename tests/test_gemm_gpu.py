@@ -183,6 +183,28 @@ def test_any_stride_kernel_skinny_and_split_k(rt, case):
     assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("case", [
+    # (M, N, K, strides, expected launches): the 10-class output layer of the MLP config
+    (8192, 10, 4096, (4096, 1, 1, 4096), 1),     # forward  y = x . W^T          (tiny N)
+    (10, 4096, 8192, (1, 10, 4096, 1), 2),       # dW = g^T . x                   (tiny M, K cut into ranges)
+    (1000, 1, 516, (516, 1, 1, 516), 1),         # matrix-vector
+    (3, 260, 300, (300, 1, 260, 1), 1),          # tiny M, one k range
+])
+def test_tiny_dimension_kernels(rt, case):
+    M, N, K, st, launches = case
+    rng = np.random.default_rng(M * 3 + N * 5 + K * 7)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    assert stats["skinny"] == 1 and stats["launches"] <= 2, stats   # the tiny-M form may add its range reduction
+    r2 = run_matmul(rt, a, b, M, N, K, st, 0)
+    assert np.array_equal(r1, r2)
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+
+
 def test_nan_propagates_like_reference(rt):
     a = np.zeros((128, 64), dtype=np.float32)
     b = np.ones((64, 128), dtype=np.float32)
@@ -296,6 +318,41 @@ def test_bmm_config3_full_size_properties(rt):
     # linearity: (2A) B == 2 (A B) exactly in binary floating point
     c2 = ops.MatMul(a * 2, b)
     assert torch.equal(c2, c * 2)
+
+
+@pytest.mark.parametrize("shapes", [
+    ((6, 1, 130, 36), (1, 5, 36, 72)),          # each operand broadcast along one axis
+    ((4, 96, 64), (64, 80)),                    # b has no batch axes: dB sums the whole batch
+    ((3, 2, 1, 40, 32), (2, 4, 32, 48)),        # summed axis in the middle / leading
+    ((2, 1, 3, 1, 16, 8), (1, 4, 1, 5, 8, 12)), # summed axes do not merge: unfused fallback
+])
+def test_broadcast_backward_fuses_the_batch_reduction(rt, shapes):
+    """dA / dB of a broadcast matmul: RawBmm + ReduceGradToShape
+    (src/Tensotron/TensorOps.MatMulND.cs:80-103) as one launch that sums the broadcast axis inside
+    the k loop, in a fixed order."""
+    a_shape, b_shape = shapes
+    rng = np.random.default_rng(sum(a_shape) + sum(b_shape))
+    a = rng.uniform(-1, 1, a_shape).astype(np.float32)
+    b = rng.uniform(-1, 1, b_shape).astype(np.float32)
+    out_shape = np.broadcast_shapes(a_shape[:-2], b_shape[:-2]) + (a_shape[-2], b_shape[-1])
+    g = rng.uniform(-1, 1, out_shape).astype(np.float32)
+    ad, bd_, gd = dev(a), dev(b), dev(g)
+    rt.ResetCounters()
+    dA, dB = ops.MatMulBackward(ad, bd_, gd)
+    launches = rt.Stats()["launches"]
+    rt.Check()
+    dA2, dB2 = ops.MatMulBackward(ad, bd_, gd)
+    assert torch.equal(dA, dA2) and torch.equal(dB, dB2)
+    ta = torch.tensor(a, dtype=torch.float64, requires_grad=True)
+    tb = torch.tensor(b, dtype=torch.float64, requires_grad=True)
+    (ta @ tb).backward(torch.tensor(g, dtype=torch.float64))
+    n_red_a = int(np.prod(out_shape[:-2])) // max(1, int(np.prod(a_shape[:-2])))
+    n_red_b = int(np.prod(out_shape[:-2])) // max(1, int(np.prod(b_shape[:-2])))
+    assert tuple(dA.shape) == a_shape and tuple(dB.shape) == b_shape
+    assert np.abs(dA.cpu().numpy() - ta.grad.numpy()).max() <= fp32_bound(b_shape[-1] * n_red_a, g, b)
+    assert np.abs(dB.cpu().numpy() - tb.grad.numpy()).max() <= fp32_bound(a_shape[-2] * n_red_b, a, g)
+    if len(a_shape) < 6:
+        assert launches == 2          # one fused launch per gradient, no full-batch temporary
 
 
 # ---- Linear forward + backward -----------------------------------------------------------

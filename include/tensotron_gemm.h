@@ -176,7 +176,8 @@ TT_API int tt_check(tt_handle_t h, void* stream);
 
 /* Forces a kernel variant for A/B measurements: 0 auto, 1 any-stride kernel,
  * 2 TMA-fed FFMA kernel with 256x128 tiles, 3 the same with 128x128 tiles,
- * 4 / 5 tcgen05 kernel (TF32 modes only) with 128- / 256-row tiles. */
+ * 4 / 5 tcgen05 kernel (TF32 modes only) with 128- / 256-row tiles,
+ * 6 FFMA kernel with 256x128 tiles and stream-K work distribution. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 #ifdef __cplusplus

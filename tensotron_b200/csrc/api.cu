@@ -246,12 +246,15 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 
 template <int TM, bool AK, bool BK_>
 int launch_simt_t(tt_handle_t h, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb,
-                  const simt::Params& p, int grid)
+                  const simt::Params& p, int grid, int mode)
 {
     constexpr int smem = simt::Cfg<TM, AK, BK_>::SMEM_BYTES;
-    // split-K exists for the 128x128 tile only (small problems)
-    if (TM == 8 && p.splits > 1) simt::sgemm_simt_kernel<8, AK, BK_, true><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
-    else simt::sgemm_simt_kernel<TM, AK, BK_, false><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+    if (mode == simt::MODE_STREAMK)
+        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_STREAMK><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+    else if (TM == 8 && mode == simt::MODE_SPLITK)   // split-K exists for the 128x128 tile only
+        simt::sgemm_simt_kernel<8, AK, BK_, simt::MODE_SPLITK><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+    else
+        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_TILES><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "simt gemm launch");
     return TT_OK;
@@ -267,6 +270,7 @@ struct SimtPlan {
     int tm;
     int splits;
     int kps;
+    bool streamk = false;   // deal tiles x k-tiles units evenly to the CTAs (partial last wave)
 };
 
 SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail, int red_count)
@@ -295,7 +299,19 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             // reduction kernel costs about as much as two more k-tiles of a 128x128 tile
             const double t = static_cast<double>(waves) * (static_cast<double>(kps) * red_count + 2.0) * tile_cost +
                              (splits > 1 ? 2.0 / 0.70 : 0.0);
-            if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps}; }
+            if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps, false}; }
+        }
+        // stream-K: no wave quantisation (work / SMs tile-times), one fix-up pass; needs two
+        // partial-tile slots per CTA and enough k-tiles for the ranges to be worth cutting
+        if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / 2) {
+            const size_t need = 2ull * h->num_sms * bm * simt::BN * sizeof(float);
+            const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
+            const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
+            if (need <= ws_avail && fill < 0.97) {
+                const double t = (static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost +
+                                 2.0 * tile_cost + 2.0 / 0.70;
+                if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true}; }
+            }
         }
     }
     return best;
@@ -333,22 +349,33 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     p.splits = plan.splits;
     p.kps = plan.kps;
     p.partial = reinterpret_cast<float*>(h->workspace + g.ws_off);
-    p.shape.work = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * plan.splits;
+    const long long tiles = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
+    const int k_tiles = (g.K + simt::BK - 1) / simt::BK;
+    const int mode = plan.streamk ? simt::MODE_STREAMK : plan.splits > 1 ? simt::MODE_SPLITK : simt::MODE_TILES;
+    // work = what the CTAs share out: tiles x k-tiles units (stream-K) or tiles x splits items
+    p.shape.work = plan.streamk ? tiles * k_tiles : tiles * plan.splits;
     p.epi = g.epi;
     p.c = g.c;
     p.status = h->status;
     p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
     const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
-    if (plan.splits > 1) h->stats.splitk++;
+    if (plan.splits > 1 || plan.streamk) h->stats.splitk++;
     int rc;
-    if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid);
-    else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid);
-    else if (!ak && !bk) rc = launch_simt_t<TM, false, false>(h, st, ma, mb, p, grid);
-    else rc = launch_simt_t<TM, false, true>(h, st, ma, mb, p, grid);
+    if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid, mode);
+    else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid, mode);
+    else if (!ak && !bk) rc = launch_simt_t<TM, false, false>(h, st, ma, mb, p, grid, mode);
+    else rc = launch_simt_t<TM, false, true>(h, st, ma, mb, p, grid, mode);
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
-    if (plan.splits > 1) {
+    if (plan.streamk) {
+        const long long threads = tiles * (BM * simt::BN / 4);
+        simt::streamk_fixup_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
+            p.partial, g.c, p.shape, g.epi, k_tiles, grid, p.c_vec_ok);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "stream-K fix-up launch");
+        h->stats.launches++;
+    } else if (plan.splits > 1) {
         const long long threads = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * (BM * simt::BN / 4);
         simt::splitk_reduce_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
             p.partial, g.c, p.shape, g.epi, plan.splits, p.c_vec_ok);
@@ -368,6 +395,10 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         plan.tm = h->variant == 2 ? 16 : 8;
         plan.splits = 1;
         plan.kps = (g.K + simt::BK - 1) / simt::BK;
+        plan.streamk = false;
+    }
+    if (h->variant == 6) {   // pinned: 256x128 tiles with stream-K (measurements)
+        plan.tm = 16; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
     }
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
@@ -454,7 +485,7 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
             if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
         }
-        if (h->variant == 2 || h->variant == 3 || vol >= TMA_MIN_FLOP_ELEMS) {
+        if (h->variant == 2 || h->variant == 3 || h->variant == 6 || vol >= TMA_MIN_FLOP_ELEMS) {
             const int rc = try_launch_simt(h, st, g);
             if (rc != TT_ERR_UNSUPPORTED) return rc;
         }
@@ -467,13 +498,15 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
 template <int TM, bool AK, bool BK_>
 cudaError_t init_simt_one()
 {
-    cudaError_t e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         simt::Cfg<TM, AK, BK_>::SMEM_BYTES);
+    const int bytes = simt::Cfg<TM, AK, BK_>::SMEM_BYTES;
+    cudaError_t e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_TILES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_STREAMK>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess || TM != 8) return e;
-    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<8, AK, BK_, true>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                simt::Cfg<8, AK, BK_>::SMEM_BYTES);
+    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<8, AK, BK_, simt::MODE_SPLITK>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
 template <int TM>
@@ -575,7 +608,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 5) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 6) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }

@@ -111,13 +111,22 @@ struct LoadCursor {
     int ok;
 };
 
-template <int BM>
-__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat, int k_tiles)
+template <int BM, int MODE>
+__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat, int k_tiles,
+                                                long long w_end)
 {
-    const long long unit = cur.w / p.splits;
-    const int split = static_cast<int>(cur.w - unit * p.splits);
-    cur.kt = split * p.kps;
-    cur.ke = min(k_tiles, cur.kt + p.kps);
+    long long unit;
+    if (MODE == 2) {
+        unit = cur.w / k_tiles;
+        cur.kt = static_cast<int>(cur.w - unit * k_tiles);
+        const long long left = w_end - cur.w;
+        cur.ke = static_cast<int>(min(static_cast<long long>(k_tiles), cur.kt + left));
+    } else {
+        unit = cur.w / p.splits;
+        const int split = static_cast<int>(cur.w - unit * p.splits);
+        cur.kt = split * p.kps;
+        cur.ke = min(k_tiles, cur.kt + p.kps);
+    }
     cur.kb = cur.kt;
     cur.r = 0;
     cur.fresh = 0;
@@ -169,9 +178,16 @@ __device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst,
     }
 }
 
-// SPLITK is a compile-time switch because the mere presence of a second epilogue changes
-// the register allocation of the main loop (measured: 56 -> 48 TFLOP/s at 8192^3).
-template <int TM, bool A_KMAJ, bool B_KMAJ, bool SPLITK>
+// How a CTA's work is cut (compile-time, because a second epilogue body in the kernel cost
+// the main loop 14 % through register allocation; the three modes share one store loop):
+//   MODE_TILES   whole output tiles, round-robin over the CTAs;
+//   MODE_SPLITK  every tile cut into `splits` equal k ranges (small M x N);
+//   MODE_STREAMK the tiles x k-tiles units are dealt to the CTAs as equal contiguous ranges,
+//                so no SM idles in a partial last wave; a range that ends inside a tile
+//                leaves a partial tile in the workspace for streamk_fixup_kernel.
+constexpr int MODE_TILES = 0, MODE_SPLITK = 1, MODE_STREAMK = 2;
+
+template <int TM, bool A_KMAJ, bool B_KMAJ, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b, const Params p)
@@ -195,6 +211,10 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
 
     const int k_tiles = (p.shape.K + BK - 1) / BK;
     const int tiles_per_mat = p.shape.tiles_m * p.shape.tiles_n;
+    // This CTA's work: items blockIdx.x, +gridDim.x, ... (< work), or for MODE_STREAMK the
+    // contiguous unit range [w_begin, w_end) of the work = tiles x k-tiles units.
+    const long long w_begin = MODE == 2 ? (p.shape.work * blockIdx.x) / gridDim.x : blockIdx.x;
+    const long long w_end = MODE == 2 ? (p.shape.work * (blockIdx.x + 1)) / gridDim.x : p.shape.work;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -205,7 +225,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         fence_mbar_init();
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
-        cur.w = blockIdx.x;
+        cur.w = w_begin;
         cur.kt = 0;
         cur.ke = 0;
         cur.fresh = 1;
@@ -218,8 +238,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     // Issues the TMA loads of the cursor's (tile, k-tile) into cur.stage and advances
     // (thread 0 only; its state lives in shared memory so it costs no registers).
     auto produce_one = [&]() {
-        if (cur.w >= p.shape.work || !cur.ok) return;
-        if (cur.fresh) cursor_set_tile<C::BM>(cur, p, tiles_per_mat, k_tiles);
+        if (cur.w >= w_end || !cur.ok) return;
+        if (cur.fresh) cursor_set_tile<C::BM, MODE>(cur, p, tiles_per_mat, k_tiles, w_end);
         const uint32_t ps = cur.stage;
         if (cur.use > 0) {
             // the stage was used before: wait until all warps released that use
@@ -247,7 +267,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ps + 1 == STAGES) { cur.stage = 0; cur.use++; } else { cur.stage = ps + 1; }
         if (++cur.kt == cur.ke) {
             if (++cur.r < p.batch.red_count) cur.kt = cur.kb;   // same k range, next reduced entry
-            else { cur.fresh = 1; cur.w += gridDim.x; }
+            else { cur.fresh = 1; cur.w += (MODE == 2) ? (cur.ke - cur.kb) : static_cast<int>(gridDim.x); }
         }
     };
 
@@ -288,16 +308,27 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const int off_am = (wm * WROWS + ty * 4) * 4;
     const int off_bm = (wn * 64 + tx * 4) * 4;
 
-    for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
-        const long long unit = w / p.splits;
-        const int split = static_cast<int>(w - unit * p.splits);
-        const int kb = split * p.kps;
-        const int ke = min(k_tiles, kb + p.kps);
+    for (long long w = w_begin; w < w_end;) {
+        long long unit;
+        int kb, ke;
+        long long w_next;
+        if (MODE == 2) {
+            unit = w / k_tiles;
+            kb = static_cast<int>(w - unit * k_tiles);
+            ke = static_cast<int>(min(static_cast<long long>(k_tiles), kb + (w_end - w)));
+            w_next = w + (ke - kb);
+        } else {
+            unit = w / p.splits;
+            const int split = static_cast<int>(w - unit * p.splits);
+            kb = split * p.kps;
+            ke = min(k_tiles, kb + p.kps);
+            w_next = w + gridDim.x;
+        }
         const int bidx = static_cast<int>(unit / tiles_per_mat);
         const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
         int tm, tn;
         raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
-        const bool last_tile = w + gridDim.x >= p.shape.work;
+        const bool last_tile = w_next >= w_end;
 
         // Accumulators are packed float2 for the two-wide FP32 FMA.  For a row pair
         // (i, i+1) and a column pair (j, j+1):
@@ -403,33 +434,11 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             const float2 v = ((r & 1) == (c & 1)) ? d0[r >> 1][c >> 1] : d1[r >> 1][c >> 1];
             return (r & 1) ? v.y : v.x;
         };
-        float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
-        const float* bias = p.epi.bias;
-        const int act = p.epi.act;
-
-        if (SPLITK && p.splits > 1) {
-            // park this split's partial tile ([BM][BN] floats, dense) in the workspace; a
-            // separate kernel adds the partials of a tile in split order and runs the epilogue
-            float* mine = p.partial + w * (C::BM * BN);
-#pragma unroll
-            for (int h = 0; h < HALVES; h++)
-#pragma unroll
-                for (int ib = 0; ib < 2; ib++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
-                        const int ai = h * 8 + ib * 4 + i;
-#pragma unroll
-                        for (int jb = 0; jb < 2; jb++) {
-                            const int lc = wn * 64 + jb * 32 + tx * 4;
-                            *reinterpret_cast<float4*>(mine + lr * BN + lc) =
-                                make_float4(acc_at(ai, jb * 4), acc_at(ai, jb * 4 + 1),
-                                            acc_at(ai, jb * 4 + 2), acc_at(ai, jb * 4 + 3));
-                        }
-                    }
-            continue;
-        }
-        {
+        if constexpr (MODE == MODE_TILES) {
+            // whole tiles only: store straight to C
+            float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
+            const float* bias = p.epi.bias;
+            const int act = p.epi.act;
 #pragma unroll
             for (int h = 0; h < HALVES; h++)
 #pragma unroll
@@ -462,7 +471,66 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             }
                         }
                     }
+        } else {
+            // One store loop for all modes.  A finished tile goes to C (bounds, bias, activation);
+            // a partial one (split-K range, or a stream-K range that covers only part of the
+            // tile's k) goes densely ([BM][BN]) to its workspace slot for the reduction kernel.
+            bool partial_tile = false;
+            long long slot = 0;
+            if (MODE == 1) {
+                partial_tile = p.splits > 1;
+                slot = w;
+            } else if (MODE == 2) {
+                partial_tile = !(kb == 0 && ke == k_tiles);
+                slot = 2ll * blockIdx.x + (w == w_begin ? 0 : 1);   // first / last segment of this CTA's range
+            }
+            float* base;
+            int ld, row_lim, col_lim, vec_ok;
+            const float* bias = nullptr;
+            int act = 0;
+            if (partial_tile) {
+                base = p.partial + slot * (C::BM * BN);
+                ld = BN; row_lim = C::BM; col_lim = BN; vec_ok = 1;
+            } else {
+                base = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N +
+                       static_cast<long long>(tm) * C::BM * p.shape.N + tn * BN;
+                ld = p.shape.N; row_lim = p.shape.M - tm * C::BM; col_lim = p.shape.N - tn * BN;
+                vec_ok = p.c_vec_ok;
+                bias = p.epi.bias ? p.epi.bias + tn * BN : nullptr;
+                act = p.epi.act;
+            }
+    #pragma unroll
+            for (int h = 0; h < HALVES; h++)
+    #pragma unroll
+                for (int ib = 0; ib < 2; ib++)
+    #pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
+                        if (lr >= row_lim) continue;
+                        float* crow = base + static_cast<long long>(lr) * ld;
+                        const int ai = h * 8 + ib * 4 + i;
+    #pragma unroll
+                        for (int jb = 0; jb < 2; jb++) {
+                            const int lc = wn * 64 + jb * 32 + tx * 4;
+                            float v[4];
+    #pragma unroll
+                            for (int j = 0; j < 4; j++) v[j] = acc_at(ai, jb * 4 + j);
+    #pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                if (bias && lc + j < col_lim) v[j] += __ldg(bias + lc + j);
+                                v[j] = apply_act(v[j], act);
+                            }
+                            if (vec_ok && lc + 3 < col_lim) {
+                                *reinterpret_cast<float4*>(crow + lc) = make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+    #pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    if (lc + j < col_lim) crow[lc + j] = v[j];
+                            }
+                        }
+                    }
         }
+        w = w_next;
     }
 }
 
@@ -492,6 +560,64 @@ splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, G
     for (int sp = 1; sp < splits; sp++) {
         const float4 q = *reinterpret_cast<const float4*>(src + static_cast<long long>(sp) * (BM * BN));
         sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (epi.bias && cidx + j < shape.N) v[j] += __ldg(epi.bias + cidx + j);
+        v[j] = apply_act(v[j], epi.act);
+    }
+    float* crow = c + static_cast<long long>(bidx) * shape.M * shape.N + static_cast<long long>(r) * shape.N;
+    if (c_vec_ok && cidx + 3 < shape.N) {
+        *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (cidx + j < shape.N) crow[cidx + j] = v[j];
+    }
+}
+
+// Fix-up for MODE_STREAMK.  CTA c of the GEMM owned the units [b(c), b(c+1)), b(c) =
+// work * c / grid.  A tile whose k-tiles were shared by several CTAs has one partial tile per
+// sharing CTA (slot 2c for a CTA's first segment, 2c + 1 for its last); they are added in
+// ascending CTA = ascending k order, then bias / activation, then C.  Tiles that one CTA
+// computed alone were written by the GEMM itself and are skipped.
+template <int BM>
+__global__ void __launch_bounds__(256)
+streamk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ c, GemmShape shape,
+                     Epilogue epi, int k_tiles, int grid, int c_vec_ok)
+{
+    constexpr int PER_TILE = BM * BN / 4;
+    const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long tiles = static_cast<long long>(shape.batch) * shape.tiles_m * shape.tiles_n;
+    if (gid >= tiles * PER_TILE) return;
+    const long long unit = gid / PER_TILE;
+    const long long u_lo = unit * k_tiles, u_hi = u_lo + k_tiles;   // this tile's units
+    const auto bound = [&](long long cta) { return (shape.work * cta) / grid; };
+    const auto cta_of = [&](long long u) {
+        long long cta = (u * grid) / shape.work;
+        while (cta + 1 < grid && bound(cta + 1) <= u) cta++;
+        while (cta > 0 && bound(cta) > u) cta--;
+        return cta;
+    };
+    const long long c_lo = cta_of(u_lo), c_hi = cta_of(u_hi - 1);
+    if (c_lo == c_hi) return;   // one CTA computed the whole tile and stored it
+    const int e = static_cast<int>(gid - unit * PER_TILE);
+    const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
+    const int tiles_per_mat = shape.tiles_m * shape.tiles_n;
+    const int bidx = static_cast<int>(unit / tiles_per_mat);
+    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
+    int tm, tn;
+    raster_tile(t, shape.tiles_m, shape.tiles_n, RASTER_GROUP, tm, tn);
+    const int r = tm * BM + lr, cidx = tn * BN + lc;
+    if (r >= shape.M || cidx >= shape.N) return;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long cta = c_lo; cta <= c_hi; cta++) {
+        const long long seg_start = max(bound(cta), u_lo);
+        const long long slot = 2 * cta + (seg_start == bound(cta) ? 0 : 1);
+        const float4 q = *reinterpret_cast<const float4*>(partial + slot * (BM * BN) + lr * BN + lc);
+        if (cta == c_lo) sum = q;
+        else { sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w; }
     }
     float v[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll

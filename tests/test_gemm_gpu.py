@@ -183,6 +183,30 @@ def test_any_stride_kernel_skinny_and_split_k(rt, case):
     assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape", [(1024, 2048, 2048), (1000, 2052, 1028), (2048, 2048, 1024), (3072, 1536, 1056)])
+def test_stream_k_matches_oracle_and_is_repeatable(rt, shape, layout):
+    """Grids that would leave SMs idle in a partial last wave deal tiles x k-tiles units evenly
+    to the CTAs; tiles shared by several CTAs are summed in ascending k by the fix-up kernel."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = layout_strides(layout, M, N, K)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 6)      # 256x128 tiles, stream-K pinned
+    stats = rt.Stats()
+    assert stats["simt_tma"] == 1 and stats["splitk"] == 1 and stats["launches"] == 2, stats
+    r2 = run_matmul(rt, a, b, M, N, K, st, 6)
+    assert np.array_equal(r1, r2)
+    r0 = run_matmul(rt, a, b, M, N, K, st, 0)      # whatever the plan picks
+    oracle.set_threads("auto")
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    oracle.set_threads(1)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+    assert np.abs(r0 - exp).max() <= fp32_bound(K, a, b)
+
+
 @pytest.mark.parametrize("case", [
     # (M, N, K, strides, expected launches): the 10-class output layer of the MLP config
     (8192, 10, 4096, (4096, 1, 1, 4096), 1),     # forward  y = x . W^T          (tiny N)

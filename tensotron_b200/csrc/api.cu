@@ -308,8 +308,10 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
             if (need <= ws_avail && fill < 0.97) {
-                const double t = (static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost +
-                                 2.0 * tile_cost + 2.0 / 0.70;
+                // measured: the partial-tile stores, the kernel boundary and the fix-up pass cost
+                // about 32 us (18 units) whatever the shape, and a fully busy chip clocks a little
+                // lower than one with idle SMs (5 %)
+                const double t = ((static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost + 18.0) * 1.05;
                 if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true}; }
             }
         }
@@ -368,9 +370,10 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
-    if (plan.streamk) {
-        const long long threads = tiles * (BM * simt::BN / 4);
-        simt::streamk_fixup_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
+    if (plan.streamk && grid > 1) {
+        // one group of blocks per boundary between two CTAs' unit ranges
+        const unsigned int blocks = static_cast<unsigned int>(grid - 1) * (BM * simt::BN / 4 / 256);
+        simt::streamk_fixup_kernel<BM><<<blocks, 256, 0, st>>>(
             p.partial, g.c, p.shape, g.epi, k_tiles, grid, p.c_vec_ok);
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(h, e, "stream-K fix-up launch");

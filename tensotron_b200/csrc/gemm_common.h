@@ -6,11 +6,25 @@ namespace tt {
 
 constexpr int MAX_BATCH_RANK = 8;
 
+constexpr int MAX_PEERS = 8;
+
 // Epilogue fused into the store path: C = act(acc + bias[n]).
 struct Epilogue {
     const float* bias;  // per output column, may be null
     int act;            // TT_ACT_*
+    // Row-block scatter (gradient exchange between GPUs): with scatter_rows > 0, output row r
+    // is stored at scatter[r / scatter_rows] + r * N + n instead of c + r * N + n; the bases may
+    // be peer-GPU addresses.  scatter_rows is a multiple of every kernel's tile height, so a
+    // tile never straddles two bases.  Honoured by the stream-K form of the FMA kernel, its
+    // fix-up kernel and the tensor-core kernel; the host routes scatter calls to those only.
+    int scatter_rows;
+    float* scatter[MAX_PEERS];
 };
+
+__device__ __forceinline__ float* scatter_base(const Epilogue& e, float* c, int row)
+{
+    return e.scatter_rows > 0 ? e.scatter[row / e.scatter_rows] : c;
+}
 
 // Batch structure after the host collapsed mergeable axes.  The linear batch index
 // is decoded last-axis-fastest over dims[0..rank).

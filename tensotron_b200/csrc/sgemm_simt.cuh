@@ -492,7 +492,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 base = p.partial + slot * (C::BM * BN);
                 ld = BN; row_lim = C::BM; col_lim = BN; vec_ok = 1;
             } else {
-                base = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N +
+                base = scatter_base(p.epi, p.c, tm * C::BM) + static_cast<long long>(bidx) * p.shape.M * p.shape.N +
                        static_cast<long long>(tm) * C::BM * p.shape.N + tn * BN;
                 ld = p.shape.N; row_lim = p.shape.M - tm * C::BM; col_lim = p.shape.N - tn * BN;
                 vec_ok = p.c_vec_ok;
@@ -581,28 +581,41 @@ splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, G
 // work * c / grid.  A tile whose k-tiles were shared by several CTAs has one partial tile per
 // sharing CTA (slot 2c for a CTA's first segment, 2c + 1 for its last); they are added in
 // ascending CTA = ascending k order, then bias / activation, then C.  Tiles that one CTA
-// computed alone were written by the GEMM itself and are skipped.
+// computed alone were written by the GEMM itself and are never visited: the grid is laid over
+// the grid - 1 range boundaries (BM * BN / 1024 blocks each), a boundary that falls strictly
+// inside a tile marks a shared tile, and the first such boundary of a tile handles it.  The
+// 64-bit divisions are done by one thread per block.
 template <int BM>
 __global__ void __launch_bounds__(256)
 streamk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ c, GemmShape shape,
                      Epilogue epi, int k_tiles, int grid, int c_vec_ok)
 {
-    constexpr int PER_TILE = BM * BN / 4;
-    const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const long long tiles = static_cast<long long>(shape.batch) * shape.tiles_m * shape.tiles_n;
-    if (gid >= tiles * PER_TILE) return;
-    const long long unit = gid / PER_TILE;
-    const long long u_lo = unit * k_tiles, u_hi = u_lo + k_tiles;   // this tile's units
+    constexpr int BLOCKS_PER_TILE = BM * BN / 4 / 256;
+    __shared__ long long s_unit;
+    __shared__ int s_lo, s_hi;
+    const int boundary = blockIdx.x / BLOCKS_PER_TILE + 1;   // 1 .. grid - 1
     const auto bound = [&](long long cta) { return (shape.work * cta) / grid; };
-    const auto cta_of = [&](long long u) {
-        long long cta = (u * grid) / shape.work;
-        while (cta + 1 < grid && bound(cta + 1) <= u) cta++;
-        while (cta > 0 && bound(cta) > u) cta--;
-        return cta;
-    };
-    const long long c_lo = cta_of(u_lo), c_hi = cta_of(u_hi - 1);
-    if (c_lo == c_hi) return;   // one CTA computed the whole tile and stored it
-    const int e = static_cast<int>(gid - unit * PER_TILE);
+    if (threadIdx.x == 0) {
+        const long long u = bound(boundary);
+        const long long unit = u / k_tiles;
+        const long long u_lo = unit * k_tiles, u_hi = u_lo + k_tiles;
+        int lo = -1, hi = -1;
+        // strictly inside the tile, and no earlier boundary inside the same tile
+        if (u != u_lo && bound(boundary - 1) <= u_lo) {
+            lo = boundary - 1;
+            hi = boundary;
+            while (hi + 1 < grid && bound(hi + 1) < u_hi) hi++;
+        }
+        s_unit = unit;
+        s_lo = lo;
+        s_hi = hi;
+    }
+    __syncthreads();
+    const int c_lo = s_lo, c_hi = s_hi;
+    if (c_lo < 0) return;
+    const long long unit = s_unit;
+    const long long u_lo = unit * k_tiles;
+    const int e = (blockIdx.x % BLOCKS_PER_TILE) * 256 + threadIdx.x;
     const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
     const int tiles_per_mat = shape.tiles_m * shape.tiles_n;
     const int bidx = static_cast<int>(unit / tiles_per_mat);
@@ -611,13 +624,13 @@ streamk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ c, G
     raster_tile(t, shape.tiles_m, shape.tiles_n, RASTER_GROUP, tm, tn);
     const int r = tm * BM + lr, cidx = tn * BN + lc;
     if (r >= shape.M || cidx >= shape.N) return;
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (long long cta = c_lo; cta <= c_hi; cta++) {
-        const long long seg_start = max(bound(cta), u_lo);
-        const long long slot = 2 * cta + (seg_start == bound(cta) ? 0 : 1);
-        const float4 q = *reinterpret_cast<const float4*>(partial + slot * (BM * BN) + lr * BN + lc);
-        if (cta == c_lo) sum = q;
-        else { sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w; }
+    // the first sharer's segment is the tail of its range (slot 2c+1, or 2c when its range
+    // starts exactly at this tile); every later sharer's segment starts its range (slot 2c)
+    const long long first_slot = 2ll * c_lo + (bound(c_lo) == u_lo ? 0 : 1);
+    float4 sum = *reinterpret_cast<const float4*>(partial + first_slot * (BM * BN) + lr * BN + lc);
+    for (int cta = c_lo + 1; cta <= c_hi; cta++) {
+        const float4 q = *reinterpret_cast<const float4*>(partial + 2ll * cta * (BM * BN) + lr * BN + lc);
+        sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
     }
     float v[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
@@ -625,7 +638,8 @@ streamk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ c, G
         if (epi.bias && cidx + j < shape.N) v[j] += __ldg(epi.bias + cidx + j);
         v[j] = apply_act(v[j], epi.act);
     }
-    float* crow = c + static_cast<long long>(bidx) * shape.M * shape.N + static_cast<long long>(r) * shape.N;
+    float* crow = scatter_base(epi, c, tm * BM) + static_cast<long long>(bidx) * shape.M * shape.N +
+                  static_cast<long long>(r) * shape.N;
     if (c_vec_ok && cidx + 3 < shape.N) {
         *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
     } else {

@@ -331,7 +331,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const TileCoord tc = decode_tile(w, p.shape);
             if (!mbar_wait_bounded(&acc_full[acc], acc_phase, cta_abort, p.status, DEV_WAIT_MMA)) break;
             tc_fence_after();
-            float* cmat = p.c + static_cast<long long>(tc.bidx) * p.shape.M * p.shape.N;
+            float* cmat = scatter_base(p.epi, p.c, tc.tm * C::BM) + static_cast<long long>(tc.bidx) * p.shape.M * p.shape.N;
             const int n0 = tc.tn * BN;
 #pragma unroll 1
             for (int j = 0; j < MT; j++) {

@@ -210,7 +210,10 @@ def bmm_config3(rt):
 
 def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
     """Config 4: 784-4096-4096-4096-10 MLP, global batch 8192 split over the ranks,
-    cross-entropy on random labels, Adam lr 1e-3; gradient all-reduce over NCCL."""
+    cross-entropy on random labels, Adam lr 1e-3.  Gradient exchange: the peer-memory path
+    (weight-gradient tiles stored into the owner's memory from the GEMM epilogue, owner-side
+    sum + Adam, parameters stored back to every rank); the per-layer NCCL all-reduce form
+    (plain Adam on one GPU) is timed beside it ("*_nccl")."""
     import torch
     import torch.distributed as dist
 
@@ -223,9 +226,11 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
     gen.manual_seed(1)
     y = torch.randint(0, 10, (gb,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
     res = {}
-    for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32)):
+    runs = [("fp32", TT_MATH_FP32, "peer"), ("tf32", TT_MATH_TF32, "peer"),
+            ("fp32_nccl", TT_MATH_FP32, "nccl"), ("tf32_nccl", TT_MATH_TF32, "nccl")]
+    for name, mode, exchange in runs:
         tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
-                        process_group=pg, math_mode=mode)
+                        process_group=pg, math_mode=mode, exchange=exchange)
         for _ in range(warmup):
             tr.step(x, y, global_batch=gb)
         if world > 1:
@@ -243,8 +248,10 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.all_reduce(lt)
         ms = t.item() / steps
-        res[name] = {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "loss": lt.item(),
+        res[name] = {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "loss": lt.item(), "exchange": exchange,
                      "tflops": 1756.5 / ms}      # 1756.5 GFLOP of GEMM work per step
+        rt.Check()
+        tr.close()
         del tr
     rt.SetCuBlasMathMode(TT_MATH_FP32)
     return res

@@ -180,6 +180,78 @@ TT_API int tt_check(tt_handle_t h, void* stream);
  * 6 FFMA kernel with 256x128 tiles and stream-K work distribution. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
+/* ---- Data-parallel gradient exchange over peer memory ---------------------------------
+ *
+ * No counterpart in the reference, which runs on one GPU: this is the multi-GPU form of its
+ * Linear backward + Adam step (src/Tensotron/TensorOps.LinearNT.cs:31-52,
+ * src/Tensotron/Optimizers.cs:144-193).  One process per GPU; every rank maps every other
+ * rank's buffers through CUDA IPC and the kernels load / store peer memory directly (NVLink).
+ *
+ * Buffers (each allocated with tt_peer_alloc on its own rank, zero-filled, exported with
+ * tt_peer_export, opened on the other ranks with tt_peer_open), n = floats of the flat
+ * parameter buffer:
+ *   stage   world x n floats  slot s = gradients produced by rank s; this rank's own slot
+ *                             (stage + rank * n) is its local gradient buffer
+ *   params  n floats          flat parameters
+ *   flags   64 x uint32       arrival flags (step numbers), zero at the start
+ * Row ownership: rows [o * own_rows, (o + 1) * own_rows) of a weight matrix belong to rank o
+ * (own_rows a multiple of 256).  The owner sums the world slots in ascending rank order, runs
+ * Adam on its rows and stores the new rows into every rank's params; small segments
+ * (biases, narrow layers) are replicated: pushed to everybody, summed and updated identically
+ * everywhere.  All ranks hold bit-identical parameters after every step.
+ *
+ * Every wait on another GPU is bounded (5 s); a wait that gives up records a code that
+ * tt_check returns as TT_ERR_DEVICE_WAIT.  The step number is host state of the group, so
+ * these calls are not meant for CUDA-graph capture.  All ranks must issue the same sequence
+ * of tt_peer_* calls. */
+#define TT_MAX_PEERS 8
+#define TT_MAX_SEGMENTS 16
+#define TT_IPC_HANDLE_BYTES 64
+typedef struct tt_peer_group_s* tt_peer_group_t;
+
+TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr);
+TT_API int tt_peer_free(tt_handle_t h, void* ptr);
+TT_API int tt_peer_export(tt_handle_t h, void* ptr, unsigned char* handle_out /* TT_IPC_HANDLE_BYTES */);
+TT_API int tt_peer_open(tt_handle_t h, const unsigned char* handle, void** out_ptr);
+TT_API int tt_peer_close(tt_handle_t h, void* ptr);
+
+/* stage / params / flags: world pointers each, entry r = rank r's buffer as mapped in this
+ * process (entry `rank` is the local allocation).  world <= TT_MAX_PEERS. */
+TT_API int tt_peer_group_create(tt_handle_t h, int world, int rank, long long n, void* const* stage,
+                                void* const* params, void* const* flags, tt_peer_group_t* out);
+TT_API int tt_peer_group_destroy(tt_peer_group_t g);
+/* Upper bound of one wait for another rank's flag (default 5000 ms). */
+TT_API int tt_peer_set_wait_limit(tt_peer_group_t g, int milliseconds);
+
+/* tt_linear_bwd whose weight gradient (N x K, at float offset w_off of the flat buffer) is
+ * stored row block by row block into the owners' slots for this rank, straight from the GEMM
+ * epilogue (stream-K FFMA kernel in strict FP32, tcgen05 kernel in the TF32 modes); when the
+ * shape is outside those kernels it is computed into the local slot and copied to the owners.
+ * The bias gradient (b_off >= 0) goes to the local slot.  own_rows = 0: the whole weight
+ * gradient goes to the local slot (a replicated layer).  *fused (optional) reports whether
+ * the epilogue did the scatter. */
+TT_API int tt_peer_linear_bwd(tt_handle_t h, void* stream, tt_peer_group_t g, const float* x, const float* w,
+                              const float* y, const float* dy, float* dx, long long w_off, long long b_off,
+                              int M, int N, int K, int act, int own_rows, int* fused);
+
+/* Ends the backward pass of a step: copies the replicated segments (float offsets / lengths,
+ * multiples of 4, at most TT_MAX_SEGMENTS) of the local slot to every other rank, then tells
+ * every rank that this rank's gradients of the step have been stored. */
+TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_segments, const long long* offsets,
+                        const long long* lengths);
+
+/* Waits for every rank's gradients, sums the slots, runs Adam (arguments as tt_adam_step) on
+ * the owned segments (result stored to every rank's params) and on the replicated segments
+ * (result stored locally) and tells the other ranks.  m, v: n floats each, local. */
+TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int n_owned, const long long* owned_off,
+                             const long long* owned_len, int n_repl, const long long* repl_off,
+                             const long long* repl_len, float* m, float* v, float* adv, float beta1, float beta2,
+                             float lr, float eps, float coupled_wd, float decoupled_factor, int advance);
+
+/* Ends a step: waits until every rank's updated rows of this step have arrived in this rank's
+ * params (must precede the next forward pass, and the next step's stores into the slots). */
+TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g);
+
 #ifdef __cplusplus
 }
 #endif

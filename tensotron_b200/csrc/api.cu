@@ -11,6 +11,7 @@
 #include "elementwise.cuh"
 #include "gemm_common.h"
 #include "gemm_generic.cuh"
+#include "peer.cuh"
 #include "sgemm_simt.cuh"
 #include "skinny.cuh"
 #include "tensor_map.h"
@@ -400,8 +401,10 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         plan.kps = (g.K + simt::BK - 1) / simt::BK;
         plan.streamk = false;
     }
-    if (h->variant == 6) {   // pinned: 256x128 tiles with stream-K (measurements)
+    if (h->variant == 6 || g.epi.scatter_rows > 0) {
+        // pinned: 256x128 tiles with stream-K (measurements; the scatter epilogue lives in this form)
         plan.tm = 16; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
+        if (2ull * h->num_sms * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
@@ -468,6 +471,25 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             g.c, 0, sizeof(float) * static_cast<size_t>(g.batch_count) * g.M * g.N, st);
         if (e != cudaSuccess) return cuda_fail(h, e, "memset C");
         return TT_OK;
+    }
+    if (g.epi.scatter_rows > 0) {
+        // Row-block scatter: only the tensor-core kernel and the stream-K FMA kernel store
+        // through the scatter table; anything else is the caller's fallback (local + copy).
+        if (g.K == 0 || g.batch_count != 1 || g.batch.red_count != 1 || h->variant == 1 ||
+            g.epi.scatter_rows % 256 != 0)
+            return TT_ERR_UNSUPPORTED;
+        if (h->math_mode != TT_MATH_FP32) {
+            int n_launch = 0;
+            const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
+                                            g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,
+                                            g.batch.dims, g.batch.as, g.batch.bs, g.epi, h->num_sms,
+                                            h->status, h->workspace + g.ws_off,
+                                            h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0, &n_launch,
+                                            h->variant == 4 ? 1 : h->variant == 5 ? 2 : 0);
+            if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
+            if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
+        }
+        return try_launch_simt(h, st, g);
     }
     const long long vol = static_cast<long long>(g.M) * g.N * (g.K > 0 ? g.K : 1);
     if (g.K > 0 && h->variant == 0) {
@@ -548,6 +570,75 @@ int bind(tt_handle_t h)
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaSetDevice");
     return TT_OK;
 }
+
+// Linear backward (activation backward + bias gradient, dX, dW).  With `scatter` the weight
+// gradient is first offered to the kernels whose epilogue stores through the scatter table;
+// *fused tells the caller whether one of them took it (otherwise dw holds the whole gradient).
+int linear_bwd_impl(tt_handle_t h, cudaStream_t st, const float* x, const float* w, const float* y,
+                    const float* dy, float* dx, float* dw, float* dbias, int M, int N, int K, int act,
+                    const Epilogue* scatter, int* fused)
+{
+    if (fused) *fused = 0;
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (M < 0 || N < 0 || K < 0) return fail(h, TT_ERR_INVALID_ARG, "negative dimension");
+    if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
+    if (!dy || !x || !w || !dw || (act != TT_ACT_NONE && !y))
+        return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+
+    const float* g = dy;
+    size_t ws_used = 0;  // the masked gradient and the column-sum partials stay live during the GEMMs
+    if (static_cast<long long>(M) * N > 0 && (act != TT_ACT_NONE || dbias)) {
+        const int chunks = ew::colsum_chunks(M);
+        const size_t g_bytes = act != TT_ACT_NONE ? sizeof(float) * static_cast<size_t>(M) * N : 0;
+        const size_t g_bytes_al = (g_bytes + 255) & ~static_cast<size_t>(255);
+        const size_t part_bytes = dbias ? sizeof(float) * static_cast<size_t>(chunks) * N : 0;
+        if (g_bytes_al + part_bytes > h->workspace_bytes)
+            return fail(h, TT_ERR_WORKSPACE, "workspace too small for linear backward");
+        float* gbuf = act != TT_ACT_NONE ? reinterpret_cast<float*>(h->workspace) : nullptr;
+        float* partial = dbias ? reinterpret_cast<float*>(h->workspace + g_bytes_al) : nullptr;
+        const bool vec = (N % 4 == 0) && aligned16(dy) && (!act || aligned16(y));
+        const dim3 grid((N + ew::COLSUM_COLS - 1) / ew::COLSUM_COLS, chunks);
+        if (vec) ew::act_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
+        else     ew::act_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
+        h->stats.launches++;
+        if (dbias) {
+            ew::colsum_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>(partial, dbias, N, chunks);
+            h->stats.launches++;
+        }
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "linear backward elementwise launch");
+        if (gbuf) g = gbuf;
+        ws_used = (g_bytes_al + part_bytes + 255) & ~static_cast<size_t>(255);
+    } else if (dbias && N > 0) {
+        const cudaError_t e = cudaMemsetAsync(dbias, 0, sizeof(float) * N, st);
+        if (e != cudaSuccess) return cuda_fail(h, e, "memset dbias");
+    }
+    if (dx) {
+        // dx[m,k] = sum_n g[m*N + n] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:36)
+        GemmCall gx{g, w, dx, M, K, N, N, 1, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+        gx.ws_off = ws_used;
+        if ((rc = run_gemm(h, st, gx))) return rc;
+    }
+    // dw[n,k] = sum_m g[m*N + n] * x[m*K + k]       (src/Tensotron/TensorOps.LinearNT.cs:44)
+    GemmCall gw{g, x, dw, N, K, M, 1, N, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+    gw.ws_off = ws_used;
+    if (scatter && scatter->scatter_rows > 0) {
+        gw.epi.scatter_rows = scatter->scatter_rows;
+        for (int o = 0; o < MAX_PEERS; o++) gw.epi.scatter[o] = scatter->scatter[o];
+        rc = run_gemm(h, st, gw);
+        if (rc == TT_OK) {
+            if (fused) *fused = 1;
+            return TT_OK;
+        }
+        if (rc != TT_ERR_UNSUPPORTED) return rc;
+        gw.epi.scatter_rows = 0;
+    }
+    return run_gemm(h, st, gw);
+}
+
 
 }  // namespace
 
@@ -712,54 +803,8 @@ TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const floa
 TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* y,
                   const float* dy, float* dx, float* dw, float* dbias, int M, int N, int K, int act)
 {
-    if (!h) return TT_ERR_INVALID_ARG;
-    if (M < 0 || N < 0 || K < 0) return fail(h, TT_ERR_INVALID_ARG, "negative dimension");
-    if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
-    if (!dy || !x || !w || !dw || (act != TT_ACT_NONE && !y))
-        return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
-    int rc = bind(h);
-    if (rc) return rc;
-    h->stats.calls++;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-    const float* g = dy;
-    size_t ws_used = 0;  // the masked gradient and the column-sum partials stay live during the GEMMs
-    if (static_cast<long long>(M) * N > 0 && (act != TT_ACT_NONE || dbias)) {
-        const int chunks = ew::colsum_chunks(M);
-        const size_t g_bytes = act != TT_ACT_NONE ? sizeof(float) * static_cast<size_t>(M) * N : 0;
-        const size_t g_bytes_al = (g_bytes + 255) & ~static_cast<size_t>(255);
-        const size_t part_bytes = dbias ? sizeof(float) * static_cast<size_t>(chunks) * N : 0;
-        if (g_bytes_al + part_bytes > h->workspace_bytes)
-            return fail(h, TT_ERR_WORKSPACE, "workspace too small for linear backward");
-        float* gbuf = act != TT_ACT_NONE ? reinterpret_cast<float*>(h->workspace) : nullptr;
-        float* partial = dbias ? reinterpret_cast<float*>(h->workspace + g_bytes_al) : nullptr;
-        const bool vec = (N % 4 == 0) && aligned16(dy) && (!act || aligned16(y));
-        const dim3 grid((N + ew::COLSUM_COLS - 1) / ew::COLSUM_COLS, chunks);
-        if (vec) ew::act_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
-        else     ew::act_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
-        h->stats.launches++;
-        if (dbias) {
-            ew::colsum_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>(partial, dbias, N, chunks);
-            h->stats.launches++;
-        }
-        const cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return cuda_fail(h, e, "linear backward elementwise launch");
-        if (gbuf) g = gbuf;
-        ws_used = (g_bytes_al + part_bytes + 255) & ~static_cast<size_t>(255);
-    } else if (dbias && N > 0) {
-        const cudaError_t e = cudaMemsetAsync(dbias, 0, sizeof(float) * N, st);
-        if (e != cudaSuccess) return cuda_fail(h, e, "memset dbias");
-    }
-    if (dx) {
-        // dx[m,k] = sum_n g[m*N + n] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:36)
-        GemmCall gx{g, w, dx, M, K, N, N, 1, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
-        gx.ws_off = ws_used;
-        if ((rc = run_gemm(h, st, gx))) return rc;
-    }
-    // dw[n,k] = sum_m g[m*N + n] * x[m*K + k]       (src/Tensotron/TensorOps.LinearNT.cs:44)
-    GemmCall gw{g, x, dw, N, K, M, 1, N, K, 1, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
-    gw.ws_off = ws_used;
-    return run_gemm(h, st, gw);
+    return linear_bwd_impl(h, static_cast<cudaStream_t>(stream), x, w, y, dy, dx, dw, dbias, M, N, K, act,
+                           nullptr, nullptr);
 }
 
 TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
@@ -890,6 +935,276 @@ TT_API int tt_check(tt_handle_t h, void* stream)
         cudaMemset(h->status, 0, sizeof(word));
         return TT_ERR_DEVICE_WAIT;
     }
+    return TT_OK;
+}
+
+// ---- gradient exchange over peer memory --------------------------------------------------
+
+struct tt_peer_group_s {
+    tt_handle_t h;
+    int world, rank;
+    long long n;
+    float* stage[MAX_PEERS];
+    float* params[MAX_PEERS];
+    unsigned int* flags[MAX_PEERS];
+    unsigned int epoch;   // step number; advanced by tt_peer_push
+    unsigned long long wait_limit_ns;
+};
+
+static_assert(sizeof(cudaIpcMemHandle_t) == TT_IPC_HANDLE_BYTES, "IPC handle size");
+static_assert(TT_MAX_PEERS == MAX_PEERS && TT_MAX_SEGMENTS == peer::MAX_SEGS, "header constants");
+
+TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr)
+{
+    if (!h || !out_ptr || bytes == 0) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer allocation");
+    e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) { cudaFree(p); return cuda_fail(h, e, "peer buffer clear"); }
+    *out_ptr = p;
+    return TT_OK;
+}
+
+TT_API int tt_peer_free(tt_handle_t h, void* ptr)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    const cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer free");
+    return TT_OK;
+}
+
+TT_API int tt_peer_export(tt_handle_t h, void* ptr, unsigned char* handle_out)
+{
+    if (!h || !ptr || !handle_out) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    cudaIpcMemHandle_t hd;
+    const cudaError_t e = cudaIpcGetMemHandle(&hd, ptr);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcGetMemHandle");
+    memcpy(handle_out, &hd, sizeof(hd));
+    return TT_OK;
+}
+
+TT_API int tt_peer_open(tt_handle_t h, const unsigned char* handle, void** out_ptr)
+{
+    if (!h || !handle || !out_ptr) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle, sizeof(hd));
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcOpenMemHandle");
+    *out_ptr = p;
+    return TT_OK;
+}
+
+TT_API int tt_peer_close(tt_handle_t h, void* ptr)
+{
+    if (!h || !ptr) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcCloseMemHandle");
+    return TT_OK;
+}
+
+TT_API int tt_peer_group_create(tt_handle_t h, int world, int rank, long long n, void* const* stage,
+                                void* const* params, void* const* flags, tt_peer_group_t* out)
+{
+    if (!h || !out) return TT_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || n <= 0 || n % 4 != 0 || !stage || !params || !flags)
+        return fail(h, TT_ERR_INVALID_ARG, "bad peer group arguments");
+    tt_peer_group_s* g = new tt_peer_group_s();
+    memset(g, 0, sizeof(*g));
+    g->h = h; g->world = world; g->rank = rank; g->n = n;
+    g->wait_limit_ns = peer::PEER_WAIT_LIMIT_NS;
+    for (int r = 0; r < world; r++) {
+        if (!stage[r] || !params[r] || !flags[r] || !aligned16(stage[r]) || !aligned16(params[r])) {
+            delete g;
+            return fail(h, TT_ERR_INVALID_ARG, "null or unaligned peer buffer");
+        }
+        g->stage[r] = static_cast<float*>(stage[r]);
+        g->params[r] = static_cast<float*>(params[r]);
+        g->flags[r] = static_cast<unsigned int*>(flags[r]);
+    }
+    *out = g;
+    return TT_OK;
+}
+
+TT_API int tt_peer_set_wait_limit(tt_peer_group_t g, int milliseconds)
+{
+    if (!g || milliseconds < 1 || milliseconds > 600000) return TT_ERR_INVALID_ARG;
+    g->wait_limit_ns = 1000000ull * static_cast<unsigned long long>(milliseconds);
+    return TT_OK;
+}
+
+TT_API int tt_peer_group_destroy(tt_peer_group_t g)
+{
+    if (!g) return TT_ERR_INVALID_ARG;
+    delete g;
+    return TT_OK;
+}
+
+TT_API int tt_peer_linear_bwd(tt_handle_t h, void* stream, tt_peer_group_t g, const float* x, const float* w,
+                              const float* y, const float* dy, float* dx, long long w_off, long long b_off,
+                              int M, int N, int K, int act, int own_rows, int* fused)
+{
+    if (fused) *fused = 0;
+    if (!h || !g) return TT_ERR_INVALID_ARG;
+    if (N < 0 || K < 0 || w_off < 0 || w_off % 4 != 0 || w_off + static_cast<long long>(N) * K > g->n ||
+        (b_off >= 0 && b_off + N > g->n))
+        return fail(h, TT_ERR_INVALID_ARG, "gradient range outside the flat buffer");
+    if (own_rows < 0 || own_rows % 256 != 0 || (own_rows > 0 && (N + own_rows - 1) / own_rows > g->world))
+        return fail(h, TT_ERR_INVALID_ARG, "own_rows must be a multiple of 256 that covers N with at most world blocks");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* local = g->stage[g->rank] + static_cast<long long>(g->rank) * g->n;
+    const bool exchange = own_rows > 0;
+    Epilogue sc{nullptr, TT_ACT_NONE};
+    if (exchange) {
+        sc.scatter_rows = own_rows;
+        for (int o = 0; o < g->world; o++) sc.scatter[o] = g->stage[o] + static_cast<long long>(g->rank) * g->n + w_off;
+    }
+    int did_fuse = 0;
+    int rc = linear_bwd_impl(h, st, x, w, y, dy, dx, local + w_off, b_off >= 0 ? local + b_off : nullptr, M, N, K,
+                             act, exchange ? &sc : nullptr, &did_fuse);
+    if (rc) return rc;
+    if (fused) *fused = did_fuse;
+    if (exchange && !did_fuse) {
+        // the whole gradient is in the local slot: copy every other owner's row block to it
+        for (int o = 0; o < g->world; o++) {
+            if (o == g->rank) continue;
+            const long long r0 = static_cast<long long>(o) * own_rows;
+            if (r0 >= N) break;
+            const long long rows = (N - r0) < own_rows ? (N - r0) : own_rows;
+            const long long count = rows * K, at = w_off + r0 * K;
+            if (count % 4 != 0 || at % 4 != 0)
+                return fail(h, TT_ERR_UNSUPPORTED, "row blocks of the weight gradient are not 16-byte aligned");
+            long long blocks = (count / 4 + 255) / 256;
+            const long long cap = static_cast<long long>(h->num_sms) * 8;
+            if (blocks > cap) blocks = cap;
+            peer::copy_to_peer_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+                local + at, g->stage[o] + static_cast<long long>(g->rank) * g->n + at, count / 4);
+            h->stats.launches++;
+        }
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "peer copy launch");
+    }
+    return TT_OK;
+}
+
+namespace {
+int fill_segments(tt_handle_t h, tt_peer_group_t g, int n, const long long* off, const long long* len,
+                  peer::SegList& out, long long& total4)
+{
+    total4 = 0;
+    out.n = 0;
+    if (n < 0 || n > peer::MAX_SEGS || (n > 0 && (!off || !len)))
+        return fail(h, TT_ERR_INVALID_ARG, "bad segment list");
+    for (int i = 0; i < n; i++) {
+        if (off[i] < 0 || len[i] < 0 || off[i] % 4 != 0 || len[i] % 4 != 0 || off[i] + len[i] > g->n)
+            return fail(h, TT_ERR_INVALID_ARG, "segment not a multiple of 4 floats or outside the flat buffer");
+        out.off[i] = off[i];
+        out.len[i] = len[i];
+        total4 += len[i] / 4;
+    }
+    out.n = n;
+    return TT_OK;
+}
+}  // namespace
+
+TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_segments, const long long* offsets,
+                        const long long* lengths)
+{
+    if (!h || !g) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    peer::SegList segs;
+    long long total4 = 0;
+    if ((rc = fill_segments(h, g, n_segments, offsets, lengths, segs, total4))) return rc;
+    g->epoch++;
+    if (g->world > 1 && total4 > 0) {
+        peer::PeerPtrs dst;
+        for (int o = 0; o < MAX_PEERS; o++)
+            dst.p[o] = (o < g->world && o != g->rank) ? g->stage[o] + static_cast<long long>(g->rank) * g->n : nullptr;
+        long long blocks = (total4 + 255) / 256;
+        const long long cap = static_cast<long long>(h->num_sms) * 8;
+        if (blocks > cap) blocks = cap;
+        peer::push_segments_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+            g->stage[g->rank] + static_cast<long long>(g->rank) * g->n, dst, g->world, segs, total4);
+        h->stats.launches++;
+    }
+    peer::FlagPtrs f;
+    for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + g->rank : nullptr;
+    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->epoch);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "peer push launch");
+    return TT_OK;
+}
+
+TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int n_owned, const long long* owned_off,
+                             const long long* owned_len, int n_repl, const long long* repl_off,
+                             const long long* repl_len, float* m, float* v, float* adv, float beta1, float beta2,
+                             float lr, float eps, float coupled_wd, float decoupled_factor, int advance)
+{
+    if (!h || !g) return TT_ERR_INVALID_ARG;
+    if (!m || !v || !adv || !aligned16(m) || !aligned16(v)) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    peer::SegList owned, repl;
+    long long owned4 = 0, repl4 = 0;
+    if ((rc = fill_segments(h, g, n_owned, owned_off, owned_len, owned, owned4))) return rc;
+    if ((rc = fill_segments(h, g, n_repl, repl_off, repl_len, repl, repl4))) return rc;
+    // gradients of this step from every rank
+    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank], g->world, g->epoch, h->status, g->wait_limit_ns);
+    h->stats.launches++;
+    if (advance) {
+        ew::adam_advance_kernel<<<1, 1, 0, st>>>(adv, beta1, beta2);
+        h->stats.launches++;
+    }
+    if (owned4 + repl4 > 0) {
+        peer::PeerPtrs pp;
+        for (int o = 0; o < MAX_PEERS; o++) pp.p[o] = o < g->world ? g->params[o] : nullptr;
+        long long blocks = (owned4 + repl4 + 255) / 256;
+        const long long cap = static_cast<long long>(h->num_sms) * 16;
+        if (blocks > cap) blocks = cap;
+        peer::reduce_adam_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+            g->stage[g->rank], g->n, g->world, g->rank, pp, m, v, adv, owned, owned4, repl, repl4, beta1, beta2, lr,
+            eps, coupled_wd, decoupled_factor);
+        h->stats.launches++;
+    }
+    // tell every rank that this rank's rows are in its parameter buffer
+    peer::FlagPtrs f;
+    for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + MAX_PEERS + g->rank : nullptr;
+    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->epoch);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "peer Adam launch");
+    return TT_OK;
+}
+
+TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g)
+{
+    if (!h || !g) return TT_ERR_INVALID_ARG;
+    int rc = bind(h);
+    if (rc) return rc;
+    h->stats.calls++;
+    peer::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(g->flags[g->rank] + MAX_PEERS, g->world,
+                                                                     g->epoch, h->status, g->wait_limit_ns);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "peer sync launch");
     return TT_OK;
 }
 

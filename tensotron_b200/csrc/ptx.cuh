@@ -14,6 +14,7 @@ enum : unsigned int {
     DEV_WAIT_EMPTY = 2,   // producer gave up waiting for a free stage
     DEV_WAIT_MMA = 3,     // epilogue gave up waiting for tcgen05 completion
     DEV_WAIT_TMEM = 4,    // MMA issuer gave up waiting for a drained accumulator
+    DEV_WAIT_PEER = 5,    // a wait for another GPU's flag (gradient / parameter exchange) gave up
 };
 
 // Upper bound on one wait, in nanoseconds of %globaltimer.  The longest legitimate

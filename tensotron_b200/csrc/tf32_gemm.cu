@@ -49,7 +49,12 @@ struct Cfg {
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
     static constexpr int ACC_BUFS = MT == 1 ? 2 : 1;
     static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
-    static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+    // epilogue staging: per epilogue warp 32 rows x 32 columns, rows padded to 36 floats
+    static constexpr int OUT_ROWB = 36 * 4;
+    static constexpr int OUT_WARP_BYTES = 32 * OUT_ROWB;
+    static constexpr int OFF_OUT = OFF_BAR + 256;
+    static constexpr int SMEM_BYTES = OFF_OUT + 4 * OUT_WARP_BYTES + 1024;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory budget");
     static_assert(STAGES >= 2, "shared-memory budget");
 };
 
@@ -327,6 +332,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t acc = 0, acc_phase = 0;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
+        uint8_t* out_stage = smem + C::OFF_OUT + q * C::OUT_WARP_BYTES;
         for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
             const TileCoord tc = decode_tile(w, p.shape);
             if (!mbar_wait_bounded(&acc_full[acc], acc_phase, cta_abort, p.status, DEV_WAIT_MMA)) break;
@@ -335,8 +341,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int n0 = tc.tn * BN;
 #pragma unroll 1
             for (int j = 0; j < MT; j++) {
-                const int row = tc.tm * C::BM + j * 128 + q * 32 + lane;
-                float* crow = cmat + static_cast<long long>(row) * p.shape.N;
+                const int row0 = tc.tm * C::BM + j * 128 + q * 32;   // first row of this warp's block
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * BN) + j * BN;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -344,24 +349,41 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     uint32_t r[32];
                     tmem_ld_32x32(t_row + c0, r);
                     tmem_ld_wait();
-                    if (row < p.shape.M) {
+                    // The TMEM load gives lane l the 32 columns of row l.  Stored that way, one
+                    // store instruction would touch 32 rows with 16 bytes each; the block goes
+                    // through shared memory instead and comes back with 8 lanes per row, so an
+                    // instruction writes 4 rows x 128 contiguous bytes (full sectors for L2, and
+                    // full-size packets when the row block belongs to another GPU).
+                    __syncwarp();   // the previous chunk's reads of the staging block are done
 #pragma unroll
-                        for (int v4 = 0; v4 < 8; v4++) {
-                            const int col = n0 + c0 + v4 * 4;
-                            float v[4];
+                    for (int v4 = 0; v4 < 8; v4++) {
+                        const int col = n0 + c0 + v4 * 4;
+                        float v[4];
 #pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                v[e] = __uint_as_float(r[v4 * 4 + e]);
-                                if (bias && col + e < p.shape.N) v[e] += __ldg(bias + col + e);
-                                v[e] = act_apply(v[e], act);
-                            }
-                            if (p.c_vec_ok && col + 3 < p.shape.N) {
-                                *reinterpret_cast<float4*>(crow + col) = make_float4(v[0], v[1], v[2], v[3]);
-                            } else {
+                        for (int e = 0; e < 4; e++) {
+                            v[e] = __uint_as_float(r[v4 * 4 + e]);
+                            if (bias && col + e < p.shape.N) v[e] += __ldg(bias + col + e);
+                            v[e] = act_apply(v[e], act);
+                        }
+                        *reinterpret_cast<float4*>(out_stage + lane * C::OUT_ROWB + v4 * 16) =
+                            make_float4(v[0], v[1], v[2], v[3]);
+                    }
+                    __syncwarp();
+                    const int col = n0 + c0 + (lane & 7) * 4;
 #pragma unroll
-                                for (int e = 0; e < 4; e++)
-                                    if (col + e < p.shape.N) crow[col + e] = v[e];
-                            }
+                    for (int i = 0; i < 8; i++) {
+                        const int lr = i * 4 + (lane >> 3);
+                        const int grow = row0 + lr;
+                        if (grow >= p.shape.M) continue;
+                        const float4 v = *reinterpret_cast<const float4*>(out_stage + lr * C::OUT_ROWB + (lane & 7) * 16);
+                        float* crow = cmat + static_cast<long long>(grow) * p.shape.N;
+                        if (p.c_vec_ok && col + 3 < p.shape.N) {
+                            *reinterpret_cast<float4*>(crow + col) = v;
+                        } else {
+                            const float ve[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++)
+                                if (col + e < p.shape.N) crow[col + e] = ve[e];
                         }
                     }
                 }

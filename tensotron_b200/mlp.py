@@ -9,9 +9,13 @@ src/Tensotron/Optimizers.cs:144-193), with every product going through the C-ABI
   loss      softmax cross-entropy forward+backward, device labels       tt_softmax_cross_entropy
   backward  per layer: activation backward + fixed-order bias gradient,
             dX (NN GEMM), dW (TN GEMM)                                  tt_linear_bwd
-  exchange  one NCCL all-reduce (sum) per layer's gradient slice, issued as soon as the
-            slice is final so it overlaps the rest of the backward pass
+  exchange  "nccl": one NCCL all-reduce (sum) per layer's gradient slice, issued as soon as
+            the slice is final so it overlaps the rest of the backward pass, then
   update    one fused Adam over the flat parameter buffer                tt_adam_step
+  exchange  "peer": the weight-gradient GEMM stores every finished tile into the memory of the
+            rank that owns those rows (NVLink stores from the epilogue); the owner sums the
+            ranks' copies in rank order, runs Adam on its rows and stores the new rows into
+            every rank's parameters (peer.py)               tt_peer_linear_bwd / _push / _adam_step
 
 Parameters, gradients and Adam moments live in flat buffers laid out layer by layer
 (W_i then b_i), so a layer's gradients are one contiguous slice and Adam is one launch.
@@ -48,7 +52,8 @@ def layer_layout(dims):
 
 
 class MlpTrainer:
-    def __init__(self, dims, rt=None, device=0, lr=1e-3, seed=2, process_group=None, math_mode=TT_MATH_FP32):
+    def __init__(self, dims, rt=None, device=0, lr=1e-3, seed=2, process_group=None, math_mode=TT_MATH_FP32,
+                 exchange="nccl", peer_group=None):
         self.dims = list(dims)
         self.L = len(dims) - 1
         self.device = device
@@ -58,8 +63,20 @@ class MlpTrainer:
         self.math_mode = math_mode
         self.offs, total = layer_layout(self.dims)
         dev = torch.device("cuda", device)
-        self.params = torch.zeros(total, device=dev)
-        self.grads = torch.zeros(total, device=dev)
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.exchange = exchange
+        self.peer = None
+        if exchange == "peer":
+            from .peer import PeerGroup, exchange_plan
+            self.peer = peer_group or PeerGroup(self.rt, total, process_group)
+            self.own_rows, owned, self.replicated = exchange_plan(self.dims, self.peer.world, self.offs)
+            self.owned = owned[self.peer.rank]
+            self.params, self.grads = self.peer.params, self.peer.grads
+            self.fused = [False] * self.L     # which layers' scatter ran in the GEMM epilogue (last step)
+        else:
+            self.params = torch.zeros(total, device=dev)
+            self.grads = torch.zeros(total, device=dev)
         self.m = torch.zeros(total, device=dev)
         self.v = torch.zeros(total, device=dev)
         self.adv = torch.zeros(3, device=dev)
@@ -99,10 +116,8 @@ class MlpTrainer:
         self._dacts = [torch.empty((batch, d), device=dev) for d in self.dims[1:]]
         self._batch = batch
 
-    # ---- one training step ----
-    def step(self, x, labels, global_batch=None, apply_update=True):
-        """x: (rows, dims[0]) float32 CUDA, labels: (rows,) int32 CUDA.  Returns the device
-        scalar holding this rank's share of the mean loss (sum over ranks = global mean)."""
+    def forward(self, x, labels, global_batch=None):
+        """Forward pass + softmax cross-entropy (loss and its gradient w.r.t. the logits)."""
         rt = self.rt
         rt.SetCuBlasMathMode(self.math_mode)
         rows = x.shape[0]
@@ -117,6 +132,21 @@ class MlpTrainer:
             inp = self._acts[i]
         rt.LaunchSoftmaxCrossEntropy(self._acts[L - 1], labels, self._dacts[L - 1], self.loss, rows,
                                      self.dims[L], 1.0 / gb)
+
+    # ---- one training step ----
+    def step(self, x, labels, global_batch=None, apply_update=True):
+        """x: (rows, dims[0]) float32 CUDA, labels: (rows,) int32 CUDA.  Returns the device
+        scalar holding this rank's share of the mean loss (sum over ranks = global mean)."""
+        rt, L, rows = self.rt, self.L, x.shape[0]
+        self.forward(x, labels, global_batch)
+        if self.peer is not None:
+            if not apply_update:
+                raise ValueError("the peer exchange reduces inside the optimizer step: apply_update must be True")
+            self.peer_backward(x)
+            self.peer_push()
+            self.peer_update()
+            self.peer_sync()
+            return self.loss
         handles = []
         for i in reversed(range(L)):
             act = 1 if i < L - 1 else 0
@@ -133,3 +163,29 @@ class MlpTrainer:
         if apply_update:
             rt.LaunchAdam(self.params, self.grads, self.m, self.v, self.adv, self.n_params, lr=self.lr)
         return self.loss
+
+    # The peer exchange in its four phases (step() runs them in order; a test that emulates
+    # several ranks on one GPU runs each phase for all ranks before the next one).
+    def peer_backward(self, x):
+        L, pr, rows = self.L, self.peer, x.shape[0]
+        for i in reversed(range(L)):
+            act = 1 if i < L - 1 else 0
+            layer_in = x if i == 0 else self._acts[i - 1]
+            dx = self._dacts[i - 1] if i > 0 else None
+            w_off, b_off = self.offs[i]
+            self.fused[i] = pr.linear_bwd(layer_in, self.weight(i), self._acts[i], self._dacts[i], dx, w_off, b_off,
+                                          rows, self.dims[i + 1], self.dims[i], act, self.own_rows[i])
+
+    def peer_push(self):
+        self.peer.push(self.replicated)
+
+    def peer_update(self):
+        self.peer.adam_step(self.owned, self.replicated, self.m, self.v, self.adv, lr=self.lr)
+
+    def peer_sync(self):
+        self.peer.sync()
+
+    def close(self):
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None

@@ -21,6 +21,9 @@ EXPORTS = [
     "tt_matmul", "tt_matmul_batched", "tt_matmul_batched_reduce", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
     "tt_set_variant", "tt_softmax_cross_entropy_static",
+    "tt_peer_alloc", "tt_peer_free", "tt_peer_export", "tt_peer_open", "tt_peer_close", "tt_peer_group_create",
+    "tt_peer_group_destroy", "tt_peer_linear_bwd", "tt_peer_push", "tt_peer_adam_step", "tt_peer_sync",
+    "tt_peer_set_wait_limit",
 ]
 
 

@@ -229,8 +229,12 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
     runs = [("fp32", TT_MATH_FP32, "peer"), ("tf32", TT_MATH_TF32, "peer"),
             ("fp32_nccl", TT_MATH_FP32, "nccl"), ("tf32_nccl", TT_MATH_TF32, "nccl")]
     for name, mode, exchange in runs:
-        tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
-                        process_group=pg, math_mode=mode, exchange=exchange)
+        try:
+            tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
+                            process_group=pg, math_mode=mode, exchange=exchange)
+        except Exception as ex:     # e.g. peer mapping refused by the platform: report, keep the other runs
+            res[name] = {"error": "%s: %s" % (type(ex).__name__, ex)}
+            continue
         for _ in range(warmup):
             tr.step(x, y, global_batch=gb)
         if world > 1:

@@ -211,6 +211,35 @@ adam_step_kernel(float* __restrict__ p, const float* __restrict__ g, float* __re
     }
 }
 
+// dst[c * ld_dst + r] = src[r * ld_src + c] for an R x C matrix (R, C, both leading dimensions
+// multiples of 4, both bases 16-byte aligned).  64 x 64 tiles through shared memory, 128-bit
+// accesses on both sides.  Used to bring a large K-major GEMM operand into the MN-major form the
+// FMA kernel reads without a shared-memory transposition.
+__global__ void __launch_bounds__(256)
+transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int R, int C, long long ld_src,
+                 long long ld_dst)
+{
+    __shared__ float t[64][65];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int q = threadIdx.x & 15, p = threadIdx.x >> 4;   // 16 float4 columns x 16 rows per pass
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = p + 16 * i, c = q * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r0 + r < R && c0 + c < C)
+            v = *reinterpret_cast<const float4*>(src + static_cast<long long>(r0 + r) * ld_src + c0 + c);
+        t[r][c] = v.x; t[r][c + 1] = v.y; t[r][c + 2] = v.z; t[r][c + 3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int c = p + 16 * i, r = q * 4;                // dst row c0 + c, dst columns r0 + r ..
+        if (c0 + c < C && r0 + r < R)
+            *reinterpret_cast<float4*>(dst + static_cast<long long>(c0 + c) * ld_dst + r0 + r) =
+                make_float4(t[r][c], t[r + 1][c], t[r + 2][c], t[r + 3][c]);
+    }
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 add_into_kernel(float* __restrict__ target, const float* __restrict__ source, long long n)

@@ -30,7 +30,7 @@ UNIT = "TFLOP/s"
 # DRAM bytes (read + write) per launch of sgemm_simt_kernel from ncu, keyed by problem edge.
 # 8192 is captured (profiles/sgemm_simt_kernel_nn_8192_dram_traffic.md); 16384 is that capture
 # scaled (reads x 8, writes x 4), because a 3 GB / 157 ms launch is too large to capture.
-NCU_TRAFFIC_BYTES = {8192: 2242259712 + 256432640, 16384: 8 * 2242259712 + 4 * 256432640}
+NCU_TRAFFIC_BYTES = {8192: 3366821376 + 254345472, 16384: 8 * 3366821376 + 4 * 254345472}
 
 
 def env_int(name, default):
@@ -455,7 +455,8 @@ def main():
             "traffic_note": "ncu DRAM bytes per launch; 16384 is the 8192^3 capture scaled (reads x 8, writes x 4)",
             "peak_source": "derived: %d SMs x 128 FP32 lanes x 2 x %.0f MHz (max SM clock); the "
                            "measured-peaks file has no FP32 SIMT figure" % (sms, max_mhz),
-            "kernel": "sgemm_simt_kernel<K-major A, N-major B>",
+            "kernel": "sgemm_simt_kernel<MN-major A (transposed once into the workspace), N-major B>; "
+                      "`achieved` is over the whole step, transposition included",
             "algorithmic_flops_per_launch": 2.0 * rows * n * n,
         }
         if clocks and clocks.get("sm_mhz"):

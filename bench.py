@@ -181,6 +181,75 @@ def sgemm_modes_8192(rt, sms, max_mhz):
     return out
 
 
+def small_configs(rt):
+    """Configs 1 and 2 (latency-bound): device time per call under CUDA-graph replay, the regime
+    the reference runs small networks in, plus the eager host cost and the launch counts."""
+    import time
+
+    import torch
+
+    def replay_us(fn, iters=20, replays=10):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        host_us = (time.perf_counter() - t0) / iters * 1e6
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (iters * replays) * 1e3, host_us
+
+    out = {}
+    a = torch.rand((256, 512), device="cuda") * 2 - 1
+    b = torch.rand((512, 256), device="cuda") * 2 - 1
+    c = torch.empty((256, 256), device="cuda")
+    l0 = rt.Stats()["launches"]
+    rt.LaunchMatMul(a, b, c, 256, 256, 512, 512, 1, 256, 1)
+    launches = rt.Stats()["launches"] - l0
+    us, host = replay_us(lambda: rt.LaunchMatMul(a, b, c, 256, 256, 512, 512, 1, 256, 1))
+    out["matmul_256x256x512"] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches,
+                                 "tflops": 2.0 * 256 * 256 * 512 / us / 1e6}
+    x = torch.randn((64, 128), device="cuda")
+    w = (torch.rand((64, 128), device="cuda") * 2 - 1) / 128 ** 0.5
+    bias = torch.zeros(64, device="cuda")
+    y, dy = torch.empty((64, 64), device="cuda"), torch.randn((64, 64), device="cuda")
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(bias)
+
+    def fwd_bwd():
+        rt.LaunchLinearForward(x, w, bias, y, 64, 64, 128, 1)
+        rt.LaunchLinearBackward(x, w, y, dy, dx, dw, db, 64, 64, 128, 1)
+
+    l0 = rt.Stats()["launches"]
+    fwd_bwd()
+    launches = rt.Stats()["launches"] - l0
+    us, host = replay_us(fwd_bwd)
+    out["linear_relu_64x128x64_fwd_bwd"] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches}
+
+    # RL-policy shape: 8-64-64-2 MLP, batch 64, whole training step (forward, cross-entropy,
+    # backward, Adam) as one replayed graph
+    from tensotron_b200.mlp import MlpTrainer
+    tr = MlpTrainer([8, 64, 64, 2], rt=rt, lr=1e-3, seed=3)
+    xs = torch.randn((64, 8), device="cuda")
+    ys = torch.randint(0, 2, (64,), device="cuda", dtype=torch.int32)
+    l0 = rt.Stats()["launches"]
+    tr.step(xs, ys)
+    launches = rt.Stats()["launches"] - l0
+    us, host = replay_us(lambda: tr.step(xs, ys), iters=10)
+    out["mlp_8_64_64_2_batch64_train_step"] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches}
+    return out
+
+
 def bmm_config3(rt):
     """Config 3: A [32,1,384,256] x B [1,16,256,192] -> [32,16,384,192], one launch through
     LaunchMatMulBatched (the reference issues 512 cuBLAS calls); FP32 and TF32.  In TF32 the
@@ -219,16 +288,22 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
 
     from tensotron_b200.mlp import MlpTrainer, shard_rows
     from tensotron_b200.runtime import TT_MATH_FP32, TT_MATH_TF32
-    gb = 8192
-    s, e = shard_rows(gb, world, rank)
-    gen = torch.Generator(device="cuda").manual_seed(0)
-    x = torch.randn((gb, 784), generator=gen, device="cuda")[s:e].contiguous()
-    gen.manual_seed(1)
-    y = torch.randint(0, 10, (gb,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
-    res = {}
-    runs = [("fp32", TT_MATH_FP32, "peer"), ("tf32", TT_MATH_TF32, "peer"),
-            ("fp32_nccl", TT_MATH_FP32, "nccl"), ("tf32_nccl", TT_MATH_TF32, "nccl")]
-    for name, mode, exchange in runs:
+    res = {"scaling": "strong: global batch 8192 split over the ranks (the '*_weak' runs keep 8192 rows per rank)"}
+    runs = [("fp32", TT_MATH_FP32, "peer", 8192), ("tf32", TT_MATH_TF32, "peer", 8192),
+            ("fp32_nccl", TT_MATH_FP32, "nccl", 8192), ("tf32_nccl", TT_MATH_TF32, "nccl", 8192)]
+    if world > 1:
+        runs += [("fp32_weak", TT_MATH_FP32, "peer", 8192 * world), ("tf32_weak", TT_MATH_TF32, "peer", 8192 * world)]
+    x = y = None
+    cur_gb = 0
+    for name, mode, exchange, gb in runs:
+        if gb != cur_gb:
+            del x, y
+            s, e = shard_rows(gb, world, rank)
+            gen = torch.Generator(device="cuda").manual_seed(0)
+            x = torch.randn((gb, 784), generator=gen, device="cuda")[s:e].contiguous()
+            gen.manual_seed(1)
+            y = torch.randint(0, 10, (gb,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
+            cur_gb = gb
         try:
             tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
                             process_group=pg, math_mode=mode, exchange=exchange)
@@ -253,7 +328,8 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
             dist.all_reduce(lt)
         ms = t.item() / steps
         res[name] = {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "loss": lt.item(), "exchange": exchange,
-                     "tflops": 1756.5 / ms}      # 1756.5 GFLOP of GEMM work per step
+                     "global_batch": gb,
+                     "tflops": 1756.5 * (gb / 8192.0) / ms}      # 1756.5 GFLOP of GEMM work per 8192 rows
         rt.Check()
         tr.close()
         del tr
@@ -431,6 +507,7 @@ def main():
         if world == 1:
             props0 = torch.cuda.get_device_properties(local_rank)
             extras["bmm_32x16_384x256x192"] = bmm_config3(rt)
+            extras["small_configs"] = small_configs(rt)
             extras["sgemm_8192"] = sgemm_modes_8192(rt, props0.multi_processor_count,
                                                     (clocks or {}).get("sm_max_mhz") or 1965.0)
 

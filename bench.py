@@ -503,13 +503,20 @@ def main():
         pg = dist.group.WORLD if world > 1 else None
         del a, b, c
         torch.cuda.empty_cache()
-        extras["mlp_784_4096x3_10_batch8192"] = mlp_steps_per_s(rt, rank, world, local_rank, pg)
+        def guarded(name, fn):
+            # an extra never costs the headline line: a failure is reported in its place
+            try:
+                extras[name] = fn()
+            except Exception as ex:
+                extras[name] = {"error": "%s: %s" % (type(ex).__name__, ex)}
+
+        guarded("mlp_784_4096x3_10_batch8192", lambda: mlp_steps_per_s(rt, rank, world, local_rank, pg))
         if world == 1:
             props0 = torch.cuda.get_device_properties(local_rank)
-            extras["bmm_32x16_384x256x192"] = bmm_config3(rt)
-            extras["small_configs"] = small_configs(rt)
-            extras["sgemm_8192"] = sgemm_modes_8192(rt, props0.multi_processor_count,
-                                                    (clocks or {}).get("sm_max_mhz") or 1965.0)
+            guarded("bmm_32x16_384x256x192", lambda: bmm_config3(rt))
+            guarded("small_configs", lambda: small_configs(rt))
+            guarded("sgemm_8192", lambda: sgemm_modes_8192(rt, props0.multi_processor_count,
+                                                           (clocks or {}).get("sm_max_mhz") or 1965.0))
 
     t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
     if world > 1:

@@ -201,9 +201,9 @@ TT_API int tt_set_variant(tt_handle_t h, int variant);
  * everywhere.  All ranks hold bit-identical parameters after every step.
  *
  * Every wait on another GPU is bounded (5 s); a wait that gives up records a code that
- * tt_check returns as TT_ERR_DEVICE_WAIT.  The step number is host state of the group, so
- * these calls are not meant for CUDA-graph capture.  All ranks must issue the same sequence
- * of tt_peer_* calls. */
+ * tt_check returns as TT_ERR_DEVICE_WAIT.  The step number lives in device memory (a word of
+ * `flags`), none of these calls allocates or synchronises, and a step's calls take the same
+ * arguments every step.  All ranks must issue the same sequence of tt_peer_* calls. */
 #define TT_MAX_PEERS 8
 #define TT_MAX_SEGMENTS 16
 #define TT_IPC_HANDLE_BYTES 64

@@ -981,7 +981,6 @@ struct tt_peer_group_s {
     float* stage[MAX_PEERS];
     float* params[MAX_PEERS];
     unsigned int* flags[MAX_PEERS];
-    unsigned int epoch;   // step number; advanced by tt_peer_push
     unsigned long long wait_limit_ns;
 };
 
@@ -1164,7 +1163,6 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_se
     peer::SegList segs;
     long long total4 = 0;
     if ((rc = fill_segments(h, g, n_segments, offsets, lengths, segs, total4))) return rc;
-    g->epoch++;
     if (g->world > 1 && total4 > 0) {
         peer::PeerPtrs dst;
         for (int o = 0; o < MAX_PEERS; o++)
@@ -1178,7 +1176,7 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_se
     }
     peer::FlagPtrs f;
     for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + g->rank : nullptr;
-    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->epoch);
+    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->flags[g->rank] + 2 * MAX_PEERS, 1);   // starts step e + 1
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer push launch");
@@ -1201,7 +1199,8 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     if ((rc = fill_segments(h, g, n_owned, owned_off, owned_len, owned, owned4))) return rc;
     if ((rc = fill_segments(h, g, n_repl, repl_off, repl_len, repl, repl4))) return rc;
     // gradients of this step from every rank
-    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank], g->world, g->epoch, h->status, g->wait_limit_ns);
+    unsigned int* step_counter = g->flags[g->rank] + 2 * MAX_PEERS;
+    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank], g->world, step_counter, h->status, g->wait_limit_ns);
     h->stats.launches++;
     if (advance) {
         ew::adam_advance_kernel<<<1, 1, 0, st>>>(adv, beta1, beta2);
@@ -1221,7 +1220,7 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     // tell every rank that this rank's rows are in its parameter buffer
     peer::FlagPtrs f;
     for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + MAX_PEERS + g->rank : nullptr;
-    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->epoch);
+    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, step_counter, 0);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer Adam launch");
@@ -1234,8 +1233,8 @@ TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g)
     int rc = bind(h);
     if (rc) return rc;
     h->stats.calls++;
-    peer::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(g->flags[g->rank] + MAX_PEERS, g->world,
-                                                                     g->epoch, h->status, g->wait_limit_ns);
+    peer::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + 2 * MAX_PEERS, h->status, g->wait_limit_ns);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer sync launch");

@@ -8,8 +8,11 @@
 //                              (stored there by rank s's weight-gradient GEMM, tile by tile)
 //                              and the small replicated segments (pushed by push_segments)
 //   params  n floats           the parameters; owners store updated rows into every rank's copy
-//   flags   2 x 8 words        [s]: gradients of step e from rank s have landed (value e);
-//                              [8 + s]: parameters owned by rank s are updated for step e
+//   flags   2 x 8 + 1 words    [s]: gradients of step e from rank s have landed (value e);
+//                              [8 + s]: parameters owned by rank s are updated for step e;
+//                              [16]: this rank's step counter e (device-resident, so that the
+//                              calls of a step carry no per-step host state and a captured
+//                              graph of the step can be replayed)
 //
 // One step on every rank, all on one stream:
 //   backward GEMMs (scatter epilogue) -> push_segments -> signal(grads) ->
@@ -83,22 +86,32 @@ copy_to_peer_kernel(const float* __restrict__ src, float* __restrict__ dst, long
         reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
 }
 
-// Thread o stores `epoch` into flag word dst.p[o] (already offset to this rank's word).
-__global__ void signal_kernel(FlagPtrs dst, int world, unsigned int epoch)
+// Thread o stores this rank's step number into flag word dst.p[o] (already offset to this
+// rank's word).  advance = 1: the step counter is incremented first (start of an exchange).
+__global__ void signal_kernel(FlagPtrs dst, int world, unsigned int* step_counter, int advance)
 {
+    __shared__ unsigned int s_epoch;
+    if (threadIdx.x == 0) {
+        unsigned int e = *step_counter;
+        if (advance) *step_counter = ++e;
+        s_epoch = e;
+    }
+    __syncthreads();
     __threadfence_system();
     const int o = threadIdx.x;
     if (o < world && dst.p[o]) {
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.p[o]), "r"(epoch) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.p[o]), "r"(s_epoch) : "memory");
     }
 }
 
-// Thread s waits until flags[s] has reached `epoch` (wrap-safe comparison), at most limit_ns.
-__global__ void wait_kernel(const unsigned int* flags, int world, unsigned int epoch, unsigned int* status,
-                            unsigned long long limit_ns)
+// Thread s waits until flags[s] has reached this rank's step number (wrap-safe comparison),
+// at most limit_ns.
+__global__ void wait_kernel(const unsigned int* flags, int world, const unsigned int* step_counter,
+                            unsigned int* status, unsigned long long limit_ns)
 {
     const int s = threadIdx.x;
     if (s >= world) return;
+    const unsigned int epoch = *step_counter;
     const unsigned long long t0 = global_timer_ns();
     unsigned int spins = 0;
     for (;;) {

@@ -207,6 +207,31 @@ def test_stream_k_matches_oracle_and_is_repeatable(rt, shape, layout):
     assert np.abs(r0 - exp).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("layout,shape", [("NN", (1028, 1540, 1032)), ("NT", (2564, 1540, 1028)), ("NT", (1028, 1540, 1032))])
+def test_large_k_major_operands_are_transposed_once_without_changing_a_bit(rt, layout, shape):
+    """A large K-major operand is copied MN-major into the workspace before the FMA kernel runs
+    (A when N >= 1536, B when M >= 2560): one extra launch per transposed operand, same sums in
+    the same order, so the result equals the untransposed run bit for bit."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = layout_strides(layout, M, N, K)
+    pinned = run_matmul(rt, a, b, M, N, K, st, 2)          # pinned variant: no pre-transposition
+    rt.ResetCounters()
+    auto = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    transposed = 1 + (1 if (layout == "NT" and M >= 2560) else 0)
+    gemm_launches = 2 if stats["splitk"] else 1
+    assert stats["simt_tma"] == 1 and stats["launches"] == transposed + gemm_launches, stats
+    if not stats["splitk"]:
+        assert np.array_equal(auto, pinned)                # stream-K would regroup the partial sums
+    oracle.set_threads("auto")
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    oracle.set_threads(1)
+    assert np.abs(auto - exp).max() <= fp32_bound(K, a, b)
+
+
 @pytest.mark.parametrize("case", [
     # (M, N, K, strides, expected launches): the 10-class output layer of the MLP config
     (8192, 10, 4096, (4096, 1, 1, 4096), 1),     # forward  y = x . W^T          (tiny N)

@@ -32,7 +32,7 @@ def _emulated_trainers(world, mode, variant=0):
             for r in range(world)]
 
 
-def _emulated_step(trs, x, y):
+def _emulated_step(trs, x, y, check=True):
     world, batch = len(trs), x.shape[0]
     for r, t in enumerate(trs):
         lo, hi = shard_rows(batch, world, r)
@@ -44,7 +44,7 @@ def _emulated_step(trs, x, y):
         t.peer_update()
     for t in trs:
         t.peer_sync()
-    for t in trs:
+    for t in trs if check else []:
         t.rt.Check()
 
 
@@ -135,4 +135,31 @@ def test_a_wait_for_a_rank_that_never_signals_gives_up_with_an_error_code():
         trs[0].rt.Check()                     # the status word was cleared; the context is still usable
     finally:
         for t in trs:
+            t.close()
+
+
+def test_exchange_step_replays_from_a_cuda_graph():
+    """The step counter of the exchange lives in device memory, so a captured step (all phases of
+    two emulated ranks on one stream) can be replayed: same bits as issuing the steps eagerly."""
+    x, y = _data(512, seed=6)
+    eager = _emulated_trainers(2, TT_MATH_FP32)
+    graphed = _emulated_trainers(2, TT_MATH_FP32)
+    try:
+        for _ in range(4):
+            _emulated_step(eager, x, y)
+        _emulated_step(graphed, x, y)                      # warm-up: buffers allocated, step 1 done
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            _emulated_step(graphed, x, y, check=False)     # step 2 runs during capture? no: only recorded
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        for t in graphed:
+            t.rt.Check()
+        assert torch.equal(graphed[0].params, eager[0].params)
+        assert torch.equal(graphed[1].params, graphed[0].params)
+        assert graphed[0].adv[0].item() == 4
+    finally:
+        for t in eager + graphed:
             t.close()

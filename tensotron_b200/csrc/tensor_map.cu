@@ -39,7 +39,7 @@ bool tma_compatible(const OperandView& v)
 }
 
 int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uint32_t box1,
-                      Swizzle swz)
+                      Swizzle swz, uint32_t box2)
 {
     PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
     if (!enc) return 999;
@@ -50,7 +50,7 @@ int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uin
     uint64_t last_bytes = 16;
     for (int i = 0; i < 5; i++) {
         dims[i] = i < v.rank ? v.dim[i] : 1;
-        box[i] = i == 0 ? box0 : i == 1 ? box1 : 1;
+        box[i] = i == 0 ? box0 : i == 1 ? box1 : i == 2 ? box2 : 1;
         estr[i] = 1;
         if (i > 0) {
             // Padded size-1 dims still need a legal stride: reuse the span of the last real dim.

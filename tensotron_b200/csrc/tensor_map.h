@@ -24,9 +24,9 @@ struct OperandView {
 // Returns false when the view cannot be expressed as a TMA descriptor (alignment).
 bool tma_compatible(const OperandView& v);
 
-// box = extents of the copied tile for dims 0 and 1 (dims 2.. use 1).
+// box = extents of the copied tile for dims 0, 1 and 2 (dims 3.. use 1).
 // Returns cudaSuccess-like 0 on success, non-zero CUresult otherwise.
 int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uint32_t box1,
-                      Swizzle swz);
+                      Swizzle swz, uint32_t box2 = 1);
 
 }  // namespace tt

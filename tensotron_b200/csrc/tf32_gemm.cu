@@ -1,14 +1,16 @@
 // TF32 / 3xTF32 GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
 //
-// Persistent, warp-specialised CTA (one per SM, 192 threads):
+// Persistent, warp-specialised CTA (one per SM, 320 threads):
 //   warp 0     TMA producer: streams A (MT x 128 rows x 32 k) and B (256 cols x 32 k)
 //              float tiles into a shared-memory ring (mbarrier full/empty hand-over);
 //   warp 1     MMA issuer: one elected thread issues tcgen05.mma.kind::tf32 (M = 128,
 //              N = 256, K = 8 per instruction) with shared-memory operand descriptors and
 //              FP32 accumulators in tensor memory; tcgen05.commit releases ring stages
 //              and signals finished accumulators.  The same warp owns the TMEM allocation;
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32-lane TMEM
-//              sub-partition), add bias / apply the activation, store C.
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (a warp reads the 32-lane TMEM
+//              sub-partition warp % 4; the two warps of a sub-partition take one half of the
+//              columns each), add bias / apply the activation, store C.  The load of the next
+//              32-column chunk is in flight while the current one is stored.
 // MT = 1: 128x256 tiles with two accumulator buffers (the epilogue of tile i overlaps
 // the MMAs of tile i+1).  MT = 2: 256x256 tiles (two M = 128 MMAs share every B tile,
 // halving L2->SM traffic per flop) with a single accumulator set.
@@ -35,7 +37,8 @@ namespace tt {
 namespace tf32 {
 
 constexpr int BN = 256, BK = 32, UMMA_K = 8;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 8;
 
@@ -49,11 +52,12 @@ struct Cfg {
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
     static constexpr int ACC_BUFS = MT == 1 ? 2 : 1;
     static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
-    // epilogue staging: per epilogue warp 32 rows x 32 columns, rows padded to 36 floats
-    static constexpr int OUT_ROWB = 36 * 4;
-    static constexpr int OUT_WARP_BYTES = 32 * OUT_ROWB;
+    // epilogue staging: per epilogue warp 32 rows x 32 columns (128-byte rows, the 16-byte
+    // chunks of row r stored at chunk index c ^ (r & 7), so both the row-wise writes and the
+    // 4-rows-at-a-time reads are free of bank conflicts)
+    static constexpr int OUT_WARP_BYTES = 32 * 128;
     static constexpr int OFF_OUT = OFF_BAR + 256;
-    static constexpr int SMEM_BYTES = OFF_OUT + 4 * OUT_WARP_BYTES + 1024;
+    static constexpr int SMEM_BYTES = OFF_OUT + EPI_WARPS * OUT_WARP_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory budget");
     static_assert(STAGES >= 2, "shared-memory budget");
 };
@@ -65,6 +69,10 @@ struct Params {
     float* c;
     unsigned int* status;
     int c_vec_ok;
+    // MN-major operand whose rows are a multiple of 32: the tensor map splits the row axis into
+    // (32, rows / 32), so one TMA instruction brings all 32-column boxes of a k-tile
+    // (coordinates {0, k, row / 32, batch...}) instead of one instruction per box.
+    int a_grouped, b_grouped;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------
@@ -126,6 +134,19 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, with the loaded registers as in/out operands: the compiler then sees every
+// later use of r as depending on the wait and cannot schedule arithmetic on r ahead of it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
 
 // Shared-memory operand descriptor (sm_100 format): start address, leading / stride byte
 // offsets in 16-byte units, version 1, layout type (2 = 128-byte swizzle of 16-byte
@@ -202,7 +223,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int b = 0; b < ACC_BUFS; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);
+            mbar_init(&acc_empty[b], EPI_WARPS);
         }
         *cta_abort = 0u;
         fence_mbar_init();
@@ -255,6 +276,8 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         uint8_t* sb = sa + C::A_BYTES;
                         if (A_KMAJ) {
                             tma_load_5d(sa, ma, &full_bar[stage], k0, m0, ca[0], ca[1], ca[2]);
+                        } else if (p.a_grouped) {
+                            tma_load_5d(sa, ma, &full_bar[stage], 0, k0, m0 >> 5, ca[0], ca[1]);
                         } else {
 #pragma unroll
                             for (int i = 0; i < C::BM / 32; i++)
@@ -262,6 +285,8 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         if (B_KMAJ) {
                             tma_load_5d(sb, mb, &full_bar[stage], k0, n0, cb[0], cb[1], cb[2]);
+                        } else if (p.b_grouped) {
+                            tma_load_5d(sb, mb, &full_bar[stage], 0, k0, n0 >> 5, cb[0], cb[1]);
                         } else {
 #pragma unroll
                             for (int i = 0; i < BN / 32; i++)
@@ -328,64 +353,76 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else {
         // --------------------------------- epilogue ---------------------------------
-        const int q = warp & 3;  // TMEM sub-partition of this warp: lanes 32q .. 32q+31
+        const int ew = warp - 2;   // 0 .. 7
+        const int q = warp & 3;    // TMEM sub-partition a warp may read: lanes 32q .. 32q+31
+        const int cbeg = (ew >> 2) * (BN / 2), cend = cbeg + BN / 2;   // this warp's half of the columns
         uint32_t acc = 0, acc_phase = 0;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
-        uint8_t* out_stage = smem + C::OFF_OUT + q * C::OUT_WARP_BYTES;
+        uint8_t* out_stage = smem + C::OFF_OUT + ew * C::OUT_WARP_BYTES;
         for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
             const TileCoord tc = decode_tile(w, p.shape);
             if (!mbar_wait_bounded(&acc_full[acc], acc_phase, cta_abort, p.status, DEV_WAIT_MMA)) break;
             tc_fence_after();
             float* cmat = scatter_base(p.epi, p.c, tc.tm * C::BM) + static_cast<long long>(tc.bidx) * p.shape.M * p.shape.N;
             const int n0 = tc.tn * BN;
+            // One 32 x 32 block: bias / activation, through the staging block, out with 8 lanes per
+            // row.  (The TMEM load gives lane l the 32 columns of row l; stored that way one
+            // instruction would touch 32 rows with 16 bytes each.  After the exchange an
+            // instruction writes 4 rows x 128 contiguous bytes: full sectors for L2, full-size
+            // packets when the row block belongs to another GPU.)
+            const auto emit = [&](const uint32_t (&r)[32], int row0, int c0) {
+                __syncwarp();   // the previous block's reads of the staging block are done
+#pragma unroll
+                for (int v4 = 0; v4 < 8; v4++) {
+                    const int col = n0 + c0 + v4 * 4;
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        v[e] = __uint_as_float(r[v4 * 4 + e]);
+                        if (bias && col + e < p.shape.N) v[e] += __ldg(bias + col + e);
+                        v[e] = act_apply(v[e], act);
+                    }
+                    *reinterpret_cast<float4*>(out_stage + lane * 128 + ((v4 ^ (lane & 7)) << 4)) =
+                        make_float4(v[0], v[1], v[2], v[3]);
+                }
+                __syncwarp();
+                const int col = n0 + c0 + (lane & 7) * 4;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int lr = i * 4 + (lane >> 3);
+                    const int grow = row0 + lr;
+                    if (grow >= p.shape.M) continue;
+                    const float4 v = *reinterpret_cast<const float4*>(out_stage + lr * 128 + (((lane & 7) ^ (lr & 7)) << 4));
+                    float* crow = cmat + static_cast<long long>(grow) * p.shape.N;
+                    if (p.c_vec_ok && col + 3 < p.shape.N) {
+                        *reinterpret_cast<float4*>(crow + col) = v;
+                    } else {
+                        const float ve[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            if (col + e < p.shape.N) crow[col + e] = ve[e];
+                    }
+                }
+            };
 #pragma unroll 1
             for (int j = 0; j < MT; j++) {
-                const int row0 = tc.tm * C::BM + j * 128 + q * 32;   // first row of this warp's block
+                const int row0 = tc.tm * C::BM + j * 128 + q * 32;   // first row of this warp's blocks
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * BN) + j * BN;
+                // chunks of 32 columns, two register sets: the load of chunk i + 1 is issued before
+                // chunk i is stored (all conditions are warp-uniform)
+                uint32_t ra[32], rb[32];
+                if (n0 + cbeg < p.shape.N) tmem_ld_32x32(t_row + cbeg, ra);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (n0 + c0 >= p.shape.N) break;  // warp-uniform: whole chunk out of range
-                    uint32_t r[32];
-                    tmem_ld_32x32(t_row + c0, r);
-                    tmem_ld_wait();
-                    // The TMEM load gives lane l the 32 columns of row l.  Stored that way, one
-                    // store instruction would touch 32 rows with 16 bytes each; the block goes
-                    // through shared memory instead and comes back with 8 lanes per row, so an
-                    // instruction writes 4 rows x 128 contiguous bytes (full sectors for L2, and
-                    // full-size packets when the row block belongs to another GPU).
-                    __syncwarp();   // the previous chunk's reads of the staging block are done
-#pragma unroll
-                    for (int v4 = 0; v4 < 8; v4++) {
-                        const int col = n0 + c0 + v4 * 4;
-                        float v[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            v[e] = __uint_as_float(r[v4 * 4 + e]);
-                            if (bias && col + e < p.shape.N) v[e] += __ldg(bias + col + e);
-                            v[e] = act_apply(v[e], act);
-                        }
-                        *reinterpret_cast<float4*>(out_stage + lane * C::OUT_ROWB + v4 * 16) =
-                            make_float4(v[0], v[1], v[2], v[3]);
-                    }
-                    __syncwarp();
-                    const int col = n0 + c0 + (lane & 7) * 4;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int lr = i * 4 + (lane >> 3);
-                        const int grow = row0 + lr;
-                        if (grow >= p.shape.M) continue;
-                        const float4 v = *reinterpret_cast<const float4*>(out_stage + lr * C::OUT_ROWB + (lane & 7) * 16);
-                        float* crow = cmat + static_cast<long long>(grow) * p.shape.N;
-                        if (p.c_vec_ok && col + 3 < p.shape.N) {
-                            *reinterpret_cast<float4*>(crow + col) = v;
-                        } else {
-                            const float ve[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                            for (int e = 0; e < 4; e++)
-                                if (col + e < p.shape.N) crow[col + e] = ve[e];
-                        }
-                    }
+                for (int c0 = cbeg; c0 < cend && n0 + c0 < p.shape.N; c0 += 64) {
+                    tmem_ld_wait(ra);
+                    const bool more_b = c0 + 32 < cend && n0 + c0 + 32 < p.shape.N;
+                    if (more_b) tmem_ld_32x32(t_row + c0 + 32, rb);
+                    emit(ra, row0, c0);
+                    if (!more_b) break;
+                    tmem_ld_wait(rb);
+                    if (c0 + 64 < cend && n0 + c0 + 64 < p.shape.N) tmem_ld_32x32(t_row + c0 + 64, ra);
+                    emit(rb, row0, c0 + 32);
                 }
             }
             // all of this warp's TMEM reads of the buffer have completed (wait::ld above)
@@ -572,12 +609,13 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     if (!plan_batch(hb, b_bs, p.batch.b_slot, p.batch.b_mult, vb)) return 3;
     if (!tma_compatible(va) || !tma_compatible(vb)) return 3;
 
-    // Tile height.  With 128x256 tiles every k-tile moves 48 KB from L2 for 512 tensor-pipe
-    // cycles, and the measured L2->SM rate (about 11.2 TB/s over 148 SMs = 40 B/clk/SM) makes
-    // that L2-bound (~1235 clk per k-tile).  256x256 tiles move 64 KB for 1024 pipe cycles
-    // (~1650 clk for twice the work) but have a single accumulator set, so their epilogue
-    // (~4000 clk) is exposed, and they quantise worse on small grids.  Pick the cheaper
-    // estimate; it depends on the shape and the SM count only.
+    // Tile height.  Measured per k-tile (32 k) and SM: about 980 clk with 128x256 tiles and
+    // about 1545 clk with 256x256 tiles, which do twice the work (two MMAs share each B tile,
+    // so less L2 -> SM traffic per flop).  The 128-row form has two accumulator sets, so its
+    // epilogue (about 14000 clk) hides behind the next tile's MMAs unless K is very short; the
+    // 256-row form has one set and its epilogue (about 28000 clk) is exposed, and it quantises
+    // worse on small grids.  Pick the cheaper estimate; it depends on the shape and the SM
+    // count only.
     int mt = 1;
     if (!split) {
         const double k_tiles = (K + BK - 1) / BK;
@@ -585,8 +623,9 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
             const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
             return static_cast<double>((work + num_sms - 1) / num_sms);
         };
-        const double t1 = waves(128) * (k_tiles * 1235.0 + 1500.0);
-        const double t2 = waves(256) * (k_tiles * 1650.0 + 5500.0);
+        const double mma1 = k_tiles * 980.0;
+        const double t1 = waves(128) * (mma1 > 14000.0 ? mma1 : 14000.0) + 14000.0;
+        const double t2 = waves(256) * (k_tiles * 1545.0 + 28000.0);
         if (t2 < t1) mt = 2;
     }
     if (forced_mt == 1 || forced_mt == 2) mt = split ? 1 : forced_mt;
@@ -613,13 +652,30 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
         views[1].base = b_hi; views[3].base = b_lo;
     }
 
+    // MN-major operands: all boxes of a k-tile in one instruction when the row axis splits evenly
+    const auto can_group = [](const OperandView& v) { return v.dim[0] % 32 == 0 && v.rank <= 4; };
+    const auto grouped_view = [](const OperandView& v) {
+        OperandView g;
+        g.base = v.base;
+        g.rank = v.rank + 1;
+        g.dim[0] = 32;            g.stride_elems[0] = 1;
+        g.dim[1] = v.dim[1];      g.stride_elems[1] = v.stride_elems[1];
+        g.dim[2] = v.dim[0] / 32; g.stride_elems[2] = 32;
+        for (int i = 2; i < v.rank; i++) { g.dim[i + 1] = v.dim[i]; g.stride_elems[i + 1] = v.stride_elems[i]; }
+        return g;
+    };
+    p.a_grouped = (!ak && can_group(va)) ? 1 : 0;
+    p.b_grouped = (!bk && can_group(vb)) ? 1 : 0;
     CUtensorMap maps[4];
     for (int i = 0; i < (split ? 4 : 2); i++) {
         const bool is_a = (i % 2) == 0;
         const bool kmaj = is_a ? ak : bk;
         const int rows_box = is_a ? bm : BN;
-        const int r = kmaj ? encode_tensor_map(&maps[i], views[i], BK, rows_box, Swizzle::B128)
-                           : encode_tensor_map(&maps[i], views[i], 32, BK, Swizzle::B128_A32);
+        int r;
+        if (kmaj) r = encode_tensor_map(&maps[i], views[i], BK, rows_box, Swizzle::B128);
+        else if (is_a ? p.a_grouped : p.b_grouped)
+            r = encode_tensor_map(&maps[i], grouped_view(views[i]), 32, BK, Swizzle::B128_A32, rows_box / 32);
+        else r = encode_tensor_map(&maps[i], views[i], 32, BK, Swizzle::B128_A32);
         if (r != 0) return 3;
     }
     if (!split) { maps[2] = maps[0]; maps[3] = maps[1]; }

@@ -151,7 +151,7 @@ def test_exchange_step_replays_from_a_cuda_graph():
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            _emulated_step(graphed, x, y, check=False)     # step 2 runs during capture? no: only recorded
+            _emulated_step(graphed, x, y, check=False)     # recorded, not run
         for _ in range(3):
             g.replay()
         torch.cuda.synchronize()

@@ -193,7 +193,7 @@ TT_API int tt_set_variant(tt_handle_t h, int variant);
  *   stage   world x n floats  slot s = gradients produced by rank s; this rank's own slot
  *                             (stage + rank * n) is its local gradient buffer
  *   params  n floats          flat parameters
- *   flags   64 x uint32       arrival flags (step numbers), zero at the start
+ *   flags   TT_PEER_FLAG_WORDS x uint32  arrival flags and the step counter, zero at the start
  * Row ownership: rows [o * own_rows, (o + 1) * own_rows) of a weight matrix belong to rank o
  * (own_rows a multiple of 256).  The owner sums the world slots in ascending rank order, runs
  * Adam on its rows and stores the new rows into every rank's params; small segments
@@ -234,23 +234,34 @@ TT_API int tt_peer_linear_bwd(tt_handle_t h, void* stream, tt_peer_group_t g, co
                               const float* y, const float* dy, float* dx, long long w_off, long long b_off,
                               int M, int N, int K, int act, int own_rows, int* fused);
 
-/* Ends the backward pass of a step: copies the replicated segments (float offsets / lengths,
- * multiples of 4, at most TT_MAX_SEGMENTS) of the local slot to every other rank, then tells
- * every rank that this rank's gradients of the step have been stored. */
-TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_segments, const long long* offsets,
-                        const long long* lengths);
+/* Channels.  The exchange of a step can be cut into up to TT_PEER_CHANNELS independent parts
+ * (one per layer): each channel has its own arrival flags, so the optimizer step of one layer
+ * (and the NVLink traffic of its updated rows) can run while the backward pass of the layers
+ * below it is still computing.  A step's first tt_peer_push passes new_step = 1 (it advances the
+ * step counter); the other pushes of the step pass 0. */
+#define TT_PEER_CHANNELS 8
+#define TT_PEER_FLAG_WORDS 256   /* uint32 words of a `flags` buffer */
 
-/* Waits for every rank's gradients, sums the slots, runs Adam (arguments as tt_adam_step) on
- * the owned segments (result stored to every rank's params) and on the replicated segments
- * (result stored locally) and tells the other ranks.  m, v: n floats each, local. */
-TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int n_owned, const long long* owned_off,
-                             const long long* owned_len, int n_repl, const long long* repl_off,
-                             const long long* repl_len, float* m, float* v, float* adv, float beta1, float beta2,
-                             float lr, float eps, float coupled_wd, float decoupled_factor, int advance);
+/* Ends the gradient production of one channel: copies the replicated segments (float offsets /
+ * lengths, multiples of 4, at most TT_MAX_SEGMENTS) of the local slot to every other rank, then
+ * tells every rank that this rank's gradients of this channel and step have been stored. */
+TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int channel, int new_step, int n_segments,
+                        const long long* offsets, const long long* lengths);
 
-/* Ends a step: waits until every rank's updated rows of this step have arrived in this rank's
- * params (must precede the next forward pass, and the next step's stores into the slots). */
-TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g);
+/* Waits for every rank's gradients of the channel, sums the slots, runs Adam (arguments as
+ * tt_adam_step) on the owned segments (result stored to every rank's params) and on the
+ * replicated segments (result stored locally) and tells the other ranks.  m, v: n floats each,
+ * local.  advance = 1 on the first optimizer call of a step only. */
+TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int channel, int n_owned,
+                             const long long* owned_off, const long long* owned_len, int n_repl,
+                             const long long* repl_off, const long long* repl_len, float* m, float* v, float* adv,
+                             float beta1, float beta2, float lr, float eps, float coupled_wd,
+                             float decoupled_factor, int advance);
+
+/* Ends a step: waits until every rank's updated rows of channels 0 .. n_channels-1 of this step
+ * have arrived in this rank's params (must precede the next forward pass, and the next step's
+ * stores into the slots). */
+TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g, int n_channels);
 
 #ifdef __cplusplus
 }

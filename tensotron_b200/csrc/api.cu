@@ -985,7 +985,9 @@ struct tt_peer_group_s {
 };
 
 static_assert(sizeof(cudaIpcMemHandle_t) == TT_IPC_HANDLE_BYTES, "IPC handle size");
-static_assert(TT_MAX_PEERS == MAX_PEERS && TT_MAX_SEGMENTS == peer::MAX_SEGS, "header constants");
+static_assert(TT_MAX_PEERS == MAX_PEERS && TT_MAX_SEGMENTS == peer::MAX_SEGS && TT_PEER_CHANNELS == peer::CHANNELS &&
+                  TT_PEER_FLAG_WORDS == peer::FLAG_WORDS && peer::STEP_COUNTER_WORD < peer::FLAG_WORDS,
+              "header constants");
 
 TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr)
 {
@@ -1152,10 +1154,11 @@ int fill_segments(tt_handle_t h, tt_peer_group_t g, int n, const long long* off,
 }
 }  // namespace
 
-TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_segments, const long long* offsets,
-                        const long long* lengths)
+TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int channel, int new_step, int n_segments,
+                        const long long* offsets, const long long* lengths)
 {
     if (!h || !g) return TT_ERR_INVALID_ARG;
+    if (channel < 0 || channel >= peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad exchange channel");
     int rc = bind(h);
     if (rc) return rc;
     h->stats.calls++;
@@ -1175,20 +1178,23 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int n_se
         h->stats.launches++;
     }
     peer::FlagPtrs f;
-    for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + g->rank : nullptr;
-    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->flags[g->rank] + 2 * MAX_PEERS, 1);   // starts step e + 1
+    for (int o = 0; o < MAX_PEERS; o++)
+        f.p[o] = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + g->rank : nullptr;
+    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, new_step ? 1 : 0);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer push launch");
     return TT_OK;
 }
 
-TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int n_owned, const long long* owned_off,
-                             const long long* owned_len, int n_repl, const long long* repl_off,
-                             const long long* repl_len, float* m, float* v, float* adv, float beta1, float beta2,
-                             float lr, float eps, float coupled_wd, float decoupled_factor, int advance)
+TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int channel, int n_owned,
+                             const long long* owned_off, const long long* owned_len, int n_repl,
+                             const long long* repl_off, const long long* repl_len, float* m, float* v, float* adv,
+                             float beta1, float beta2, float lr, float eps, float coupled_wd,
+                             float decoupled_factor, int advance)
 {
     if (!h || !g) return TT_ERR_INVALID_ARG;
+    if (channel < 0 || channel >= peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad exchange channel");
     if (!m || !v || !adv || !aligned16(m) || !aligned16(v)) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
     int rc = bind(h);
     if (rc) return rc;
@@ -1199,8 +1205,9 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     if ((rc = fill_segments(h, g, n_owned, owned_off, owned_len, owned, owned4))) return rc;
     if ((rc = fill_segments(h, g, n_repl, repl_off, repl_len, repl, repl4))) return rc;
     // gradients of this step from every rank
-    unsigned int* step_counter = g->flags[g->rank] + 2 * MAX_PEERS;
-    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank], g->world, step_counter, h->status, g->wait_limit_ns);
+    unsigned int* step_counter = g->flags[g->rank] + peer::STEP_COUNTER_WORD;
+    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank] + channel * peer::CHANNEL_WORDS, g->world, step_counter,
+                                        h->status, g->wait_limit_ns);
     h->stats.launches++;
     if (advance) {
         ew::adam_advance_kernel<<<1, 1, 0, st>>>(adv, beta1, beta2);
@@ -1219,7 +1226,8 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     }
     // tell every rank that this rank's rows are in its parameter buffer
     peer::FlagPtrs f;
-    for (int o = 0; o < MAX_PEERS; o++) f.p[o] = o < g->world ? g->flags[o] + MAX_PEERS + g->rank : nullptr;
+    for (int o = 0; o < MAX_PEERS; o++)
+        f.p[o] = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + MAX_PEERS + g->rank : nullptr;
     peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, step_counter, 0);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
@@ -1227,14 +1235,16 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     return TT_OK;
 }
 
-TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g)
+TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g, int n_channels)
 {
     if (!h || !g) return TT_ERR_INVALID_ARG;
+    if (n_channels < 1 || n_channels > peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad channel count");
     int rc = bind(h);
     if (rc) return rc;
     h->stats.calls++;
-    peer::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + 2 * MAX_PEERS, h->status, g->wait_limit_ns);
+    peer::wait_kernel<<<1, 32 * n_channels, 0, static_cast<cudaStream_t>(stream)>>>(
+        g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, h->status,
+        g->wait_limit_ns);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer sync launch");

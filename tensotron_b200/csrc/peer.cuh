@@ -8,11 +8,14 @@
 //                              (stored there by rank s's weight-gradient GEMM, tile by tile)
 //                              and the small replicated segments (pushed by push_segments)
 //   params  n floats           the parameters; owners store updated rows into every rank's copy
-//   flags   2 x 8 + 1 words    [s]: gradients of step e from rank s have landed (value e);
-//                              [8 + s]: parameters owned by rank s are updated for step e;
-//                              [16]: this rank's step counter e (device-resident, so that the
+//   flags   256 words          channel c (0..7): [16c + s]: gradients of channel c, step e, from
+//                              rank s have landed (value e); [16c + 8 + s]: rank s's rows of
+//                              channel c are updated for step e;
+//                              [128]: this rank's step counter e (device-resident, so that the
 //                              calls of a step carry no per-step host state and a captured
 //                              graph of the step can be replayed)
+// A channel is an independent part of the exchange (a layer): its optimizer step can run, and
+// its updated rows can travel, while the backward pass of the layers below is still computing.
 //
 // One step on every rank, all on one stream:
 //   backward GEMMs (scatter epilogue) -> push_segments -> signal(grads) ->
@@ -35,6 +38,10 @@ namespace tt {
 namespace peer {
 
 constexpr int MAX_SEGS = 16;
+constexpr int CHANNELS = 8;
+constexpr int CHANNEL_WORDS = 2 * MAX_PEERS;           // grads flags, params flags
+constexpr int STEP_COUNTER_WORD = CHANNELS * CHANNEL_WORDS;
+constexpr int FLAG_WORDS = 256;
 constexpr unsigned long long PEER_WAIT_LIMIT_NS = 5000000000ull;   // default limit of one wait: 5 s
 
 // Segments of the flat buffer: float offsets and lengths, all multiples of 4 (128-bit accesses).
@@ -104,13 +111,14 @@ __global__ void signal_kernel(FlagPtrs dst, int world, unsigned int* step_counte
     }
 }
 
-// Thread s waits until flags[s] has reached this rank's step number (wrap-safe comparison),
-// at most limit_ns.
+// Warp c, lane s waits until flags[c * CHANNEL_WORDS + s] has reached this rank's step number
+// (wrap-safe comparison), at most limit_ns.  One warp per channel waited for.
 __global__ void wait_kernel(const unsigned int* flags, int world, const unsigned int* step_counter,
                             unsigned int* status, unsigned long long limit_ns)
 {
-    const int s = threadIdx.x;
+    const int s = threadIdx.x & 31;
     if (s >= world) return;
+    flags += (threadIdx.x >> 5) * CHANNEL_WORDS;
     const unsigned int epoch = *step_counter;
     const unsigned long long t0 = global_timer_ns();
     unsigned int spins = 0;

@@ -68,10 +68,18 @@ class MlpTrainer:
         self.exchange = exchange
         self.peer = None
         if exchange == "peer":
-            from .peer import PeerGroup, exchange_plan
+            from .peer import CHANNELS, PeerGroup, exchange_plan, merge_segments
             self.peer = peer_group or PeerGroup(self.rt, total, process_group)
-            self.own_rows, owned, self.replicated = exchange_plan(self.dims, self.peer.world, self.offs)
-            self.owned = owned[self.peer.rank]
+            self.own_rows, owned, replicated = exchange_plan(self.dims, self.peer.world, self.offs)
+            # One exchange channel per layer, so a layer's optimizer step and the transfer of its
+            # updated rows overlap the backward pass of the layers below; networks with more
+            # layers than channels exchange everything in one piece after the backward pass.
+            self.pipelined = self.L <= CHANNELS
+            if self.pipelined:
+                self.owned, self.replicated = owned[self.peer.rank], replicated
+            else:
+                self.owned = [merge_segments([s for lay in owned[self.peer.rank] for s in lay])]
+                self.replicated = [merge_segments([s for lay in replicated for s in lay])]
             self.params, self.grads = self.peer.params, self.peer.grads
             self.fused = [False] * self.L     # which layers' scatter ran in the GEMM epilogue (last step)
         else:
@@ -142,9 +150,18 @@ class MlpTrainer:
         if self.peer is not None:
             if not apply_update:
                 raise ValueError("the peer exchange reduces inside the optimizer step: apply_update must be True")
-            self.peer_backward(x)
-            self.peer_push()
-            self.peer_update()
+            if self.pipelined:
+                for i in reversed(range(L)):
+                    self.peer_backward_layer(x, i)
+                    self.peer_push(i)
+                    if i + 1 < L:
+                        self.peer_update(i + 1)      # one layer late: the other ranks have had time to finish it
+                self.peer_update(0)
+            else:
+                for i in reversed(range(L)):
+                    self.peer_backward_layer(x, i)
+                self.peer_push(0)
+                self.peer_update(0)
             self.peer_sync()
             return self.loss
         handles = []
@@ -164,26 +181,31 @@ class MlpTrainer:
             rt.LaunchAdam(self.params, self.grads, self.m, self.v, self.adv, self.n_params, lr=self.lr)
         return self.loss
 
-    # The peer exchange in its four phases (step() runs them in order; a test that emulates
-    # several ranks on one GPU runs each phase for all ranks before the next one).
-    def peer_backward(self, x):
+    # The peer exchange in its phases (step() issues them in the order above; a test that
+    # emulates several ranks on one GPU issues each phase for all ranks before the next one, so
+    # that every flag is set before the kernel that waits for it runs).  `ch` is the exchange
+    # channel = the layer (0 when the exchange is not pipelined).
+    def peer_backward_layer(self, x, i):
         L, pr, rows = self.L, self.peer, x.shape[0]
-        for i in reversed(range(L)):
-            act = 1 if i < L - 1 else 0
-            layer_in = x if i == 0 else self._acts[i - 1]
-            dx = self._dacts[i - 1] if i > 0 else None
-            w_off, b_off = self.offs[i]
-            self.fused[i] = pr.linear_bwd(layer_in, self.weight(i), self._acts[i], self._dacts[i], dx, w_off, b_off,
-                                          rows, self.dims[i + 1], self.dims[i], act, self.own_rows[i])
+        act = 1 if i < L - 1 else 0
+        layer_in = x if i == 0 else self._acts[i - 1]
+        dx = self._dacts[i - 1] if i > 0 else None
+        w_off, b_off = self.offs[i]
+        self.fused[i] = pr.linear_bwd(layer_in, self.weight(i), self._acts[i], self._dacts[i], dx, w_off, b_off,
+                                      rows, self.dims[i + 1], self.dims[i], act, self.own_rows[i])
 
-    def peer_push(self):
-        self.peer.push(self.replicated)
+    def _first_channel(self):
+        return self.L - 1 if self.pipelined else 0     # the channel whose calls come first in a step
 
-    def peer_update(self):
-        self.peer.adam_step(self.owned, self.replicated, self.m, self.v, self.adv, lr=self.lr)
+    def peer_push(self, ch):
+        self.peer.push(self.replicated[ch], channel=ch, new_step=(ch == self._first_channel()))
+
+    def peer_update(self, ch):
+        self.peer.adam_step(self.owned[ch], self.replicated[ch], self.m, self.v, self.adv, channel=ch, lr=self.lr,
+                            advance=(ch == self._first_channel()))
 
     def peer_sync(self):
-        self.peer.sync()
+        self.peer.sync(self.L if self.pipelined else 1)
 
     def close(self):
         if self.peer is not None:

@@ -15,16 +15,19 @@ from .runtime import _ptr
 
 MAX_PEERS = 8
 MAX_SEGMENTS = 16
+CHANNELS = 8                 # independent parts of a step's exchange (one per layer)
+FLAG_WORDS = 256
 ROW_BLOCK = 256              # ownership granularity = tallest GEMM tile
 MIN_PARTITIONED = 1 << 20    # weight matrices below this many elements are replicated
 
 
 def exchange_plan(dims, world, offs=None):
-    """Which rank owns what.  dims: layer widths; offs: (w_off, b_off) per layer as laid out by
-    mlp.layer_layout (computed when omitted).  Returns (own_rows, owned, replicated):
-    own_rows[i]   rows of W_i per owner (0 = the layer is replicated),
-    owned[r]      list of (offset, length) float segments of the flat buffer owned by rank r,
-    replicated    list of (offset, length) segments every rank reduces and updates itself.
+    """Which rank owns what, layer by layer.  dims: layer widths; offs: (w_off, b_off) per layer
+    as laid out by mlp.layer_layout (computed when omitted).  Returns (own_rows, owned, replicated):
+    own_rows[i]       rows of W_i per owner (0 = the layer is replicated),
+    owned[r][i]       list of (offset, length) float segments of layer i owned by rank r,
+    replicated[i]     list of (offset, length) segments of layer i that every rank reduces and
+                      updates itself (the bias, or the whole layer when it is replicated).
     Segments are multiples of 4 floats; together they cover the flat buffer exactly once."""
     from .mlp import layer_layout
     if offs is None:
@@ -32,14 +35,7 @@ def exchange_plan(dims, world, offs=None):
     else:
         total = layer_layout(dims)[1]
     L = len(dims) - 1
-    own_rows, owned, repl = [], [[] for _ in range(world)], []
-
-    def add_repl(lo, hi):
-        if repl and repl[-1][0] + repl[-1][1] == lo:
-            repl[-1] = (repl[-1][0], repl[-1][1] + hi - lo)
-        elif hi > lo:
-            repl.append((lo, hi - lo))
-
+    own_rows, owned, repl = [], [[[] for _ in range(L)] for _ in range(world)], [[] for _ in range(L)]
     for i in range(L):
         fan_in, fan_out = dims[i], dims[i + 1]
         w_off, b_off = offs[i]
@@ -53,16 +49,28 @@ def exchange_plan(dims, world, offs=None):
             for r in range(world):
                 lo, hi = min(fan_out, r * rows), min(fan_out, (r + 1) * rows)
                 if hi > lo:
-                    owned[r].append((w_off + lo * fan_in, (hi - lo) * fan_in))
-            add_repl(b_off, end)
+                    owned[r][i].append((w_off + lo * fan_in, (hi - lo) * fan_in))
+            repl[i].append((b_off, end - b_off))
         else:
-            add_repl(w_off, end)
-    for segs in owned + [repl]:
-        if len(segs) > MAX_SEGMENTS:
-            raise ValueError("more than %d exchange segments" % MAX_SEGMENTS)
-        for off, ln in segs:
+            repl[i].append((w_off, end - w_off))
+        for off, ln in repl[i] + [s for r in range(world) for s in owned[r][i]]:
             assert off % 4 == 0 and ln % 4 == 0
     return own_rows, owned, repl
+
+
+def merge_segments(segs):
+    """Sorts (offset, length) segments and joins the adjacent ones."""
+    out = []
+    for off, ln in sorted(segs):
+        if ln <= 0:
+            continue
+        if out and out[-1][0] + out[-1][1] == off:
+            out[-1] = (out[-1][0], out[-1][1] + ln)
+        else:
+            out.append((off, ln))
+    if len(out) > MAX_SEGMENTS:
+        raise ValueError("more than %d exchange segments" % MAX_SEGMENTS)
+    return out
 
 
 class _DeviceBuffer:
@@ -95,7 +103,7 @@ class PeerGroup:
         if self.world > MAX_PEERS:
             raise ValueError("at most %d ranks" % MAX_PEERS)
         self.n = n_floats
-        self._sizes = {"stage": 4 * self.world * n_floats, "params": 4 * n_floats, "flags": 256}
+        self._sizes = {"stage": 4 * self.world * n_floats, "params": 4 * n_floats, "flags": 4 * FLAG_WORDS}
         self._own, self._opened, self._g = {}, [], None
         for name, nbytes in self._sizes.items():
             p = ctypes.c_void_p()
@@ -167,9 +175,9 @@ class PeerGroup:
         L.tt_peer_group_create.argtypes = [vp, i, i, ll, pvp, pvp, pvp, pvp]
         L.tt_peer_group_destroy.argtypes = [vp]
         L.tt_peer_linear_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, ll, i, i, i, i, i, ctypes.POINTER(i)]
-        L.tt_peer_push.argtypes = [vp, vp, vp, i, pll, pll]
-        L.tt_peer_adam_step.argtypes = [vp, vp, vp, i, pll, pll, i, pll, pll, vp, vp, vp, f, f, f, f, f, f, i]
-        L.tt_peer_sync.argtypes = [vp, vp, vp]
+        L.tt_peer_push.argtypes = [vp, vp, vp, i, i, i, pll, pll]
+        L.tt_peer_adam_step.argtypes = [vp, vp, vp, i, i, pll, pll, i, pll, pll, vp, vp, vp, f, f, f, f, f, f, i]
+        L.tt_peer_sync.argtypes = [vp, vp, vp, i]
         L.tt_peer_set_wait_limit.argtypes = [vp, i]
         L._peer_declared = True
 
@@ -182,25 +190,26 @@ class PeerGroup:
                                         _ptr(dx), w_off, b_off, M, N, K, act, own_rows, ctypes.byref(fused)))
         return bool(fused.value)
 
-    def push(self, segments, stream=None):
+    def push(self, segments, channel=0, new_step=True, stream=None):
         rt = self.rt
-        rt._ck(rt._L.tt_peer_push(rt._h, rt._st(stream), self._g, len(segments),
+        rt._ck(rt._L.tt_peer_push(rt._h, rt._st(stream), self._g, channel, 1 if new_step else 0, len(segments),
                                   _larr([s[0] for s in segments]), _larr([s[1] for s in segments])))
 
-    def adam_step(self, owned, replicated, m, v, adv, b1=0.9, b2=0.999, lr=1e-3, eps=1e-8, coupledWd=0.0,
-                  decoupledFactor=1.0, advance=True, stream=None):
+    def adam_step(self, owned, replicated, m, v, adv, channel=0, b1=0.9, b2=0.999, lr=1e-3, eps=1e-8,
+                  coupledWd=0.0, decoupledFactor=1.0, advance=True, stream=None):
         rt = self.rt
         rt._ck(rt._L.tt_peer_adam_step(
-            rt._h, rt._st(stream), self._g, len(owned), _larr([s[0] for s in owned]), _larr([s[1] for s in owned]),
-            len(replicated), _larr([s[0] for s in replicated]), _larr([s[1] for s in replicated]),
-            _ptr(m), _ptr(v), _ptr(adv), b1, b2, lr, eps, coupledWd, decoupledFactor, 1 if advance else 0))
+            rt._h, rt._st(stream), self._g, channel, len(owned), _larr([s[0] for s in owned]),
+            _larr([s[1] for s in owned]), len(replicated), _larr([s[0] for s in replicated]),
+            _larr([s[1] for s in replicated]), _ptr(m), _ptr(v), _ptr(adv), b1, b2, lr, eps, coupledWd,
+            decoupledFactor, 1 if advance else 0))
 
     def set_wait_limit(self, milliseconds):
         self.rt._ck(self.rt._L.tt_peer_set_wait_limit(self._g, int(milliseconds)))
 
-    def sync(self, stream=None):
+    def sync(self, n_channels=1, stream=None):
         rt = self.rt
-        rt._ck(rt._L.tt_peer_sync(rt._h, rt._st(stream), self._g))
+        rt._ck(rt._L.tt_peer_sync(rt._h, rt._st(stream), self._g, n_channels))
 
     # -- lifetime -------------------------------------------------------------------------------
     def close(self):

@@ -33,15 +33,22 @@ def _emulated_trainers(world, mode, variant=0):
 
 
 def _emulated_step(trs, x, y, check=True):
-    world, batch = len(trs), x.shape[0]
+    """One step of all emulated ranks, phase by phase in the order MlpTrainer.step() uses."""
+    world, batch, L = len(trs), x.shape[0], trs[0].L
+    shard = [x[slice(*shard_rows(batch, world, r))] for r in range(world)]
     for r, t in enumerate(trs):
         lo, hi = shard_rows(batch, world, r)
-        t.forward(x[lo:hi], y[lo:hi], batch)
-        t.peer_backward(x[lo:hi])
+        t.forward(shard[r], y[lo:hi], batch)
+    assert trs[0].pipelined
+    for i in reversed(range(L)):
+        for r, t in enumerate(trs):
+            t.peer_backward_layer(shard[r], i)
+            t.peer_push(i)
+        if i + 1 < L:
+            for t in trs:
+                t.peer_update(i + 1)
     for t in trs:
-        t.peer_push()
-    for t in trs:
-        t.peer_update()
+        t.peer_update(0)
     for t in trs:
         t.peer_sync()
     for t in trs if check else []:
@@ -60,7 +67,8 @@ def test_scattered_weight_gradient_lands_in_the_owners_slots(mode, variant, fuse
         for r, t in enumerate(trs):
             lo, hi = shard_rows(batch, world, r)
             t.forward(x[lo:hi], y[lo:hi], batch)
-            t.peer_backward(x[lo:hi])
+            for i in reversed(range(t.L)):
+                t.peer_backward_layer(x[lo:hi], i)
             assert t.fused == [fused, fused, False]
         torch.cuda.synchronize()
         for r in range(world):
@@ -69,7 +77,7 @@ def test_scattered_weight_gradient_lands_in_the_owners_slots(mode, variant, fuse
             plain.step(x[lo:hi], y[lo:hi], global_batch=batch, apply_update=False)
             for o in range(world):
                 slot = trs[o].peer.stage[r]              # what owner o received from rank r
-                for off, ln in owned[o]:
+                for off, ln in [s for lay in owned[o] for s in lay]:
                     got, want = slot[off:off + ln], plain.grads[off:off + ln]
                     tol = (1e-6 if mode == TT_MATH_FP32 else 2e-4) * float(want.abs().max())
                     assert float((got - want).abs().max()) <= tol
@@ -126,9 +134,10 @@ def test_a_wait_for_a_rank_that_never_signals_gives_up_with_an_error_code():
     try:
         trs[0].peer.set_wait_limit(200)       # milliseconds
         trs[0].forward(x[:128], y[:128], 256)
-        trs[0].peer_backward(x[:128])
-        trs[0].peer_push()
-        trs[0].peer_update()                  # rank 1 never pushed: the wait for its flag runs out
+        top = trs[0].L - 1
+        trs[0].peer_backward_layer(x[:128], top)
+        trs[0].peer_push(top)
+        trs[0].peer_update(top)               # rank 1 never pushed: the wait for its flag runs out
         with pytest.raises(TensotronGemmError) as e:
             trs[0].rt.Check()
         assert e.value.status == 5

@@ -12,7 +12,7 @@ def test_plan_covers_the_flat_buffer_exactly_once(dims, world):
     offs, total = layer_layout(dims)
     own_rows, owned, repl = exchange_plan(dims, world, offs)
     cover = np.zeros(total, dtype=np.int32)
-    for segs in owned + [repl]:
+    for segs in [lay for r in owned for lay in r] + repl:
         assert len(segs) <= MAX_SEGMENTS
         for off, ln in segs:
             assert off % 4 == 0 and ln % 4 == 0 and ln > 0
@@ -25,11 +25,12 @@ def test_plan_covers_the_flat_buffer_exactly_once(dims, world):
             # rank r owns exactly the rows [r * rows, (r + 1) * rows) of W_i
             for r in range(world):
                 lo, hi = min(fan_out, r * rows), min(fan_out, (r + 1) * rows)
-                mine = [s for s in owned[r] if offs[i][0] <= s[0] < offs[i][0] + fan_out * fan_in]
-                assert mine == ([(offs[i][0] + lo * fan_in, (hi - lo) * fan_in)] if hi > lo else [])
+                assert owned[r][i] == ([(offs[i][0] + lo * fan_in, (hi - lo) * fan_in)] if hi > lo else [])
+            assert repl[i][0][0] == offs[i][1]            # the bias (and the padding behind it)
         else:
-            # a replicated layer lies inside the replicated segments
-            assert any(off <= offs[i][0] and offs[i][1] + fan_out <= off + ln for off, ln in repl)
+            # a replicated layer is one replicated segment: weights, bias, padding
+            assert all(owned[r][i] == [] for r in range(world))
+            assert repl[i][0][0] == offs[i][0] and repl[i][0][1] >= fan_out * fan_in + fan_out
 
 
 def test_rank_order_sum_is_what_every_rank_ends_up_with():
@@ -37,7 +38,9 @@ def test_rank_order_sum_is_what_every_rank_ends_up_with():
     everyone receives the owner's result, so the ranks agree bit for bit."""
     dims, world = [1024, 1024, 1024, 10], 4
     offs, total = layer_layout(dims)
-    _, owned, repl = exchange_plan(dims, world, offs)
+    _, owned_l, repl_l = exchange_plan(dims, world, offs)
+    owned = [[s for lay in owned_l[r] for s in lay] for r in range(world)]
+    repl = [s for lay in repl_l for s in lay]
     rng = np.random.default_rng(0)
     slots = rng.standard_normal((world, total)).astype(np.float32)    # slot s = rank s's gradients
     want = slots[0].copy()

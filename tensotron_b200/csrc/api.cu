@@ -1166,22 +1166,26 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int chan
     peer::SegList segs;
     long long total4 = 0;
     if ((rc = fill_segments(h, g, n_segments, offsets, lengths, segs, total4))) return rc;
-    if (g->world > 1 && total4 > 0) {
-        peer::PeerPtrs dst;
-        for (int o = 0; o < MAX_PEERS; o++)
-            dst.p[o] = (o < g->world && o != g->rank) ? g->stage[o] + static_cast<long long>(g->rank) * g->n : nullptr;
-        long long blocks = (total4 + 255) / 256;
-        const long long cap = static_cast<long long>(h->num_sms) * 8;
-        if (blocks > cap) blocks = cap;
-        peer::push_segments_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
-            g->stage[g->rank] + static_cast<long long>(g->rank) * g->n, dst, g->world, segs, total4);
-        h->stats.launches++;
-    }
+    peer::PeerPtrs dst;
+    for (int o = 0; o < MAX_PEERS; o++)
+        dst.p[o] = (o < g->world && o != g->rank) ? g->stage[o] + static_cast<long long>(g->rank) * g->n : nullptr;
     peer::FlagPtrs f;
     for (int o = 0; o < MAX_PEERS; o++)
         f.p[o] = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + g->rank : nullptr;
-    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, new_step ? 1 : 0);
-    h->stats.launches++;
+    unsigned int* step_counter = g->flags[g->rank] + peer::STEP_COUNTER_WORD;
+    const float* local = g->stage[g->rank] + static_cast<long long>(g->rank) * g->n;
+    if (g->world == 1) total4 = 0;   // nobody to copy to
+    if (total4 <= peer::PUSH_SINGLE_BLOCK_MAX4) {
+        peer::push_signal_kernel<<<1, 1024, 0, st>>>(local, dst, g->world, segs, total4, f, step_counter, new_step ? 1 : 0);
+        h->stats.launches++;
+    } else {
+        long long blocks = (total4 + 255) / 256;
+        const long long cap = static_cast<long long>(h->num_sms) * 8;
+        if (blocks > cap) blocks = cap;
+        peer::push_segments_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(local, dst, g->world, segs, total4);
+        peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, step_counter, new_step ? 1 : 0);
+        h->stats.launches += 2;
+    }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer push launch");
     return TT_OK;
@@ -1204,31 +1208,21 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     long long owned4 = 0, repl4 = 0;
     if ((rc = fill_segments(h, g, n_owned, owned_off, owned_len, owned, owned4))) return rc;
     if ((rc = fill_segments(h, g, n_repl, repl_off, repl_len, repl, repl4))) return rc;
-    // gradients of this step from every rank
     unsigned int* step_counter = g->flags[g->rank] + peer::STEP_COUNTER_WORD;
-    peer::wait_kernel<<<1, 32, 0, st>>>(g->flags[g->rank] + channel * peer::CHANNEL_WORDS, g->world, step_counter,
-                                        h->status, g->wait_limit_ns);
-    h->stats.launches++;
-    if (advance) {
-        ew::adam_advance_kernel<<<1, 1, 0, st>>>(adv, beta1, beta2);
-        h->stats.launches++;
-    }
-    if (owned4 + repl4 > 0) {
-        peer::PeerPtrs pp;
-        for (int o = 0; o < MAX_PEERS; o++) pp.p[o] = o < g->world ? g->params[o] : nullptr;
-        long long blocks = (owned4 + repl4 + 255) / 256;
-        const long long cap = static_cast<long long>(h->num_sms) * 16;
-        if (blocks > cap) blocks = cap;
-        peer::reduce_adam_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
-            g->stage[g->rank], g->n, g->world, g->rank, pp, m, v, adv, owned, owned4, repl, repl4, beta1, beta2, lr,
-            eps, coupled_wd, decoupled_factor);
-        h->stats.launches++;
-    }
-    // tell every rank that this rank's rows are in its parameter buffer
+    peer::PeerPtrs pp;
+    for (int o = 0; o < MAX_PEERS; o++) pp.p[o] = o < g->world ? g->params[o] : nullptr;
+    // tell every rank that this rank's rows are in its parameter buffer (last block of the kernel)
     peer::FlagPtrs f;
     for (int o = 0; o < MAX_PEERS; o++)
         f.p[o] = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + MAX_PEERS + g->rank : nullptr;
-    peer::signal_kernel<<<1, 32, 0, st>>>(f, g->world, step_counter, 0);
+    long long blocks = (owned4 + repl4 + 255) / 256;
+    const long long cap = static_cast<long long>(h->num_sms) * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    peer::reduce_adam_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
+        g->stage[g->rank], g->n, g->world, g->rank, pp, m, v, adv, advance ? 1 : 0, owned, owned4, repl, repl4, beta1,
+        beta2, lr, eps, coupled_wd, decoupled_factor, g->flags[g->rank] + channel * peer::CHANNEL_WORDS, step_counter,
+        h->status, g->wait_limit_ns, f, g->flags[g->rank] + peer::DONE_COUNTER_WORD + channel);
     h->stats.launches++;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer Adam launch");

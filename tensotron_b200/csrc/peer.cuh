@@ -17,12 +17,13 @@
 // A channel is an independent part of the exchange (a layer): its optimizer step can run, and
 // its updated rows can travel, while the backward pass of the layers below is still computing.
 //
-// One step on every rank, all on one stream:
-//   backward GEMMs (scatter epilogue) -> push_segments -> signal(grads) ->
-//   wait(grads) -> reduce_adam (sum the slots in rank order, Adam, store parameters to all
-//   ranks) -> signal(params) -> wait(params)
-// A signal is a kernel that runs after the kernels whose stores it announces (stream order),
-// fences at system scope and stores the step number into every rank's flag word.  A wait
+// One step on every rank, all on one stream, per channel:
+//   backward GEMMs (scatter epilogue) -> push (copy the replicated segments, signal "gradients
+//   stored") -> reduce_adam (wait for every rank's signal, sum the slots in rank order, Adam,
+//   store parameters to all ranks, signal "rows updated") ... -> wait(rows updated, all channels)
+// A signal comes after the stores it announces: a later kernel in stream order for the GEMM
+// epilogue's stores, a system-scope fence + CTA barrier (+ a last-block-done counter) for the
+// stores of its own kernel; it stores the step number into every rank's flag word.  A wait
 // spins with a time limit and records DEV_WAIT_PEER in the status word when it gives up, so
 // a missing rank ends in an error code, not a hang.  The sums run in ascending rank order on
 // the one rank that owns the element (or identically on every rank for the replicated
@@ -41,6 +42,8 @@ constexpr int MAX_SEGS = 16;
 constexpr int CHANNELS = 8;
 constexpr int CHANNEL_WORDS = 2 * MAX_PEERS;           // grads flags, params flags
 constexpr int STEP_COUNTER_WORD = CHANNELS * CHANNEL_WORDS;
+constexpr int DONE_COUNTER_WORD = STEP_COUNTER_WORD + 1;   // + channel: blocks of reduce_adam that have finished
+constexpr int PUSH_SINGLE_BLOCK_MAX4 = 32768;              // replicated segments up to this many float4s: one kernel
 constexpr int FLAG_WORDS = 256;
 constexpr unsigned long long PEER_WAIT_LIMIT_NS = 5000000000ull;   // default limit of one wait: 5 s
 
@@ -93,6 +96,50 @@ copy_to_peer_kernel(const float* __restrict__ src, float* __restrict__ dst, long
         reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
 }
 
+// Polls flags[s] until it has reached `epoch` (wrap-safe), at most limit_ns.
+__device__ __forceinline__ void wait_flag(const unsigned int* flags, int s, unsigned int epoch,
+                                          unsigned int* status, unsigned long long limit_ns)
+{
+    const unsigned long long t0 = global_timer_ns();
+    unsigned int spins = 0;
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
+        if (static_cast<int>(v - epoch) >= 0) break;
+        if ((++spins & 255u) == 0 && global_timer_ns() - t0 > limit_ns) {
+            atomicCAS(status, 0u, static_cast<unsigned int>(DEV_WAIT_PEER));
+            break;
+        }
+        __nanosleep(200);
+    }
+}
+
+// push_segments_kernel + signal_kernel in one launch of one block, for small segment lists
+// (biases, narrow layers): copy, fence, CTA barrier, flags.
+__global__ void __launch_bounds__(1024)
+push_signal_kernel(const float* __restrict__ src, PeerPtrs dst, int world, SegList segs, long long total4,
+                   FlagPtrs flags, unsigned int* step_counter, int advance)
+{
+    __shared__ unsigned int s_epoch;
+    if (threadIdx.x == 0) {
+        unsigned int e = *step_counter;
+        if (advance) *step_counter = ++e;
+        s_epoch = e;
+    }
+    for (long long i = threadIdx.x; i < total4; i += blockDim.x) {
+        const long long at = seg_locate(segs, i);
+        const float4 v = reinterpret_cast<const float4*>(src)[at];
+        for (int o = 0; o < world; o++)
+            if (dst.p[o]) reinterpret_cast<float4*>(dst.p[o])[at] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    const int o = threadIdx.x;
+    if (o < world && flags.p[o]) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[o]), "r"(s_epoch) : "memory");
+    }
+}
+
 // Thread o stores this rank's step number into flag word dst.p[o] (already offset to this
 // rank's word).  advance = 1: the step counter is incremented first (start of an exchange).
 __global__ void signal_kernel(FlagPtrs dst, int world, unsigned int* step_counter, int advance)
@@ -119,34 +166,38 @@ __global__ void wait_kernel(const unsigned int* flags, int world, const unsigned
     const int s = threadIdx.x & 31;
     if (s >= world) return;
     flags += (threadIdx.x >> 5) * CHANNEL_WORDS;
-    const unsigned int epoch = *step_counter;
-    const unsigned long long t0 = global_timer_ns();
-    unsigned int spins = 0;
-    for (;;) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
-        if (static_cast<int>(v - epoch) >= 0) break;
-        if ((++spins & 255u) == 0 && global_timer_ns() - t0 > limit_ns) {
-            atomicCAS(status, 0u, static_cast<unsigned int>(DEV_WAIT_PEER));
-            break;
-        }
-        __nanosleep(200);
-    }
+    wait_flag(flags, s, *step_counter, status, limit_ns);
     __threadfence_system();
 }
 
-// For every element of the owned segments: g = sum over slots 0..world-1 (ascending) of
-// stage[slot][i], Adam on (p, m, v), and the new p goes to every rank's parameter buffer
-// (params.p[o], all o; this rank's own copy included).  Replicated segments: same sum and
-// update, stored to this rank's copy only.  The arithmetic per element is ew::adam_one, so
-// with world == 1 the result equals ew::adam_step_kernel bit for bit.
+// The optimizer step of one channel, one launch:
+//  1. every block waits (bounded) until all ranks' gradients of the channel have been stored;
+//  2. for every element of the owned segments: g = sum over slots 0..world-1 (ascending) of
+//     stage[slot][i], Adam on (p, m, v), and the new p goes to every rank's parameter buffer
+//     (params.p[o], all o; this rank's own copy included).  Replicated segments: same sum and
+//     update, stored to this rank's copy only.  The arithmetic per element is ew::adam_one, so
+//     with world == 1 the result equals ew::adam_step_kernel bit for bit;
+//  3. the last block to finish tells every rank that this rank's rows are updated, and, when
+//     `advance` is set (first optimizer call of a step), stores the step's bias corrections:
+//     adv = [t, 1/(1-b1^t), 1/(1-b2^t)] with the expressions of ew::adam_advance_kernel.  With
+//     `advance` every block computes the same corrections for itself from adv[0] + 1.
 __global__ void __launch_bounds__(256)
 reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int rank, PeerPtrs params,
-                   float* __restrict__ m, float* __restrict__ v, const float* __restrict__ adv,
+                   float* __restrict__ m, float* __restrict__ v, float* adv, int advance,
                    SegList owned, long long owned4, SegList repl, long long repl4, float b1, float b2,
-                   float lr, float eps, float cwd, float dfac)
+                   float lr, float eps, float cwd, float dfac, const unsigned int* wait_flags,
+                   const unsigned int* step_counter, unsigned int* status, unsigned long long limit_ns,
+                   FlagPtrs signal, unsigned int* done_counter)
 {
-    const float ibc1 = adv[1], ibc2 = adv[2];
+    __shared__ unsigned int s_last;
+    if (threadIdx.x < world) wait_flag(wait_flags, threadIdx.x, *step_counter, status, limit_ns);
+    __syncthreads();
+    float t = adv[0], ibc1 = adv[1], ibc2 = adv[2];
+    if (advance) {
+        t += 1.f;
+        ibc1 = 1.f / (1.f - powf(b1, t));
+        ibc2 = 1.f / (1.f - powf(b2, t));
+    }
     const float omb1 = 1.f - b1, omb2 = 1.f - b2;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     float* own = params.p[rank];
@@ -172,6 +223,25 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
         } else {
             reinterpret_cast<float4*>(own)[at] = pp;
         }
+    }
+    // last block done: every thread's stores are fenced before its block is counted
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int done = atomicAdd(done_counter, 1u);
+        s_last = (done == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if (threadIdx.x == 0) {
+        *done_counter = 0u;
+        if (advance) { adv[0] = t; adv[1] = ibc1; adv[2] = ibc2; }
+    }
+    const int o = threadIdx.x;
+    if (o < world && signal.p[o]) {
+        const unsigned int e = *step_counter;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.p[o]), "r"(e) : "memory");
     }
 }
 

@@ -34,6 +34,9 @@ struct tt_handle_s {
 namespace {
 
 constexpr size_t DEFAULT_WORKSPACE = 256ull << 20;
+// Device words owned by the handle: word 0 = status of the bounded waits; from word 64 on, one
+// stream-K flag per CTA (zero between launches).
+constexpr int STREAMK_FLAGS_WORD = 64, HANDLE_WORDS = 1024;
 constexpr long long TMA_MIN_FLOP_ELEMS = 1ll << 21;  // M*N*K below this -> any-stride kernel
 
 int fail(tt_handle_t h, int code, const char* fmt, const char* detail = "")
@@ -302,17 +305,17 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
                              (splits > 1 ? 2.0 / 0.70 : 0.0);
             if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps, false}; }
         }
-        // stream-K: no wave quantisation (work / SMs tile-times), one fix-up pass; needs two
-        // partial-tile slots per CTA and enough k-tiles for the ranges to be worth cutting
+        // stream-K: no wave quantisation (work / SMs tile-times); needs one partial-tile slot
+        // per CTA and enough k-tiles for the ranges to be worth cutting
         if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / 2) {
-            const size_t need = 2ull * h->num_sms * bm * simt::BN * sizeof(float);
+            const size_t need = static_cast<size_t>(h->num_sms) * bm * simt::BN * sizeof(float);
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
             if (need <= ws_avail && fill < 0.97) {
-                // measured: the partial-tile stores, the kernel boundary and the fix-up pass cost
-                // about 32 us (18 units) whatever the shape, and a fully busy chip clocks a little
-                // lower than one with idle SMs (5 %)
-                const double t = ((static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost + 18.0) * 1.05;
+                // measured: storing and re-reading the partial tiles costs about 20 us (11 units)
+                // whatever the shape, and a fully busy chip clocks a little lower than one with
+                // idle SMs (5 %)
+                const double t = ((static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost + 11.0) * 1.05;
                 if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true}; }
             }
         }
@@ -360,6 +363,7 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     p.epi = g.epi;
     p.c = g.c;
     p.status = h->status;
+    p.sk_flags = h->status + STREAMK_FLAGS_WORD;
     p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
     const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
     if (plan.splits > 1 || plan.streamk) h->stats.splitk++;
@@ -371,15 +375,7 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
-    if (plan.streamk && grid > 1) {
-        // one group of blocks per boundary between two CTAs' unit ranges
-        const unsigned int blocks = static_cast<unsigned int>(grid - 1) * (BM * simt::BN / 4 / 256);
-        simt::streamk_fixup_kernel<BM><<<blocks, 256, 0, st>>>(
-            p.partial, g.c, p.shape, g.epi, k_tiles, grid, p.c_vec_ok);
-        const cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return cuda_fail(h, e, "stream-K fix-up launch");
-        h->stats.launches++;
-    } else if (plan.splits > 1) {
+    if (plan.splits > 1) {
         const long long threads = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * (BM * simt::BN / 4);
         simt::splitk_reduce_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
             p.partial, g.c, p.shape, g.epi, plan.splits, p.c_vec_ok);
@@ -438,7 +434,7 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g_in)
     if (h->variant == 6 || g.epi.scatter_rows > 0) {
         // pinned: 256x128 tiles with stream-K (measurements; the scatter epilogue lives in this form)
         plan.tm = 16; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
-        if (2ull * h->num_sms * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
+        if (static_cast<size_t>(h->num_sms) * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
@@ -697,8 +693,8 @@ TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle
     h->num_sms = prop.multiProcessorCount;
     h->workspace_bytes = workspace_bytes ? workspace_bytes : DEFAULT_WORKSPACE;
     if (cudaMalloc(&h->workspace, h->workspace_bytes) != cudaSuccess) { delete h; return TT_ERR_CUDA; }
-    if (cudaMalloc(&h->status, 256) != cudaSuccess) { cudaFree(h->workspace); delete h; return TT_ERR_CUDA; }
-    cudaMemset(h->status, 0, 256);
+    if (cudaMalloc(&h->status, HANDLE_WORDS * sizeof(unsigned int)) != cudaSuccess) { cudaFree(h->workspace); delete h; return TT_ERR_CUDA; }
+    cudaMemset(h->status, 0, HANDLE_WORDS * sizeof(unsigned int));
     if (init_kernels() != cudaSuccess) { cudaFree(h->workspace); cudaFree(h->status); delete h; return TT_ERR_CUDA; }
     h->stats.workspace_bytes = static_cast<long long>(h->workspace_bytes);
     h->err[0] = 0;
@@ -966,7 +962,7 @@ TT_API int tt_check(tt_handle_t h, void* stream)
     if (e != cudaSuccess) return cuda_fail(h, e, "status read");
     if (word != 0) {
         snprintf(h->err, sizeof(h->err), "device-side bounded wait gave up (code %u)", word);
-        cudaMemset(h->status, 0, sizeof(word));
+        cudaMemset(h->status, 0, HANDLE_WORDS * sizeof(unsigned int));   // the status word and any flag left raised
         return TT_ERR_DEVICE_WAIT;
     }
     return TT_OK;

@@ -15,8 +15,8 @@ struct Epilogue {
     // Row-block scatter (gradient exchange between GPUs): with scatter_rows > 0, output row r
     // is stored at scatter[r / scatter_rows] + r * N + n instead of c + r * N + n; the bases may
     // be peer-GPU addresses.  scatter_rows is a multiple of every kernel's tile height, so a
-    // tile never straddles two bases.  Honoured by the stream-K form of the FMA kernel, its
-    // fix-up kernel and the tensor-core kernel; the host routes scatter calls to those only.
+    // tile never straddles two bases.  Honoured by the stream-K form of the FMA kernel and by
+    // the tensor-core kernel; the host routes scatter calls to those only.
     int scatter_rows;
     float* scatter[MAX_PEERS];
 };

@@ -15,6 +15,7 @@ enum : unsigned int {
     DEV_WAIT_MMA = 3,     // epilogue gave up waiting for tcgen05 completion
     DEV_WAIT_TMEM = 4,    // MMA issuer gave up waiting for a drained accumulator
     DEV_WAIT_PEER = 5,    // a wait for another GPU's flag (gradient / parameter exchange) gave up
+    DEV_WAIT_STREAMK = 6, // a stream-K CTA gave up waiting for a neighbour's partial tile
 };
 
 // Upper bound on one wait, in nanoseconds of %globaltimer.  The longest legitimate

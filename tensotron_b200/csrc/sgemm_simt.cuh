@@ -73,7 +73,7 @@ struct Cfg {
     static constexpr int OFF_TA = STAGES * STAGE_BYTES;
     static constexpr int OFF_TB = OFF_TA + 2 * TA_BYTES;
     static constexpr int OFF_BAR = (OFF_TB + 2 * TB_BYTES + 127) & ~127;
-    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // barriers @0, cursor @128, split-K flag @256
+    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // barriers @0, cursor @128, stream-K scratch @256
     static_assert(STAGES >= 2, "shared-memory budget");
 };
 
@@ -89,6 +89,9 @@ struct Params {
     // splitk_reduce_kernel adds them in split order and runs the epilogue.
     int splits, kps;
     float* partial;
+    // stream-K: one "partial tile stored" flag per CTA (zero outside a launch; set by the CTA
+    // whose range starts inside a tile, cleared by the CTA that adds that partial tile)
+    unsigned int* sk_flags;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act)
@@ -183,8 +186,13 @@ __device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst,
 //   MODE_TILES   whole output tiles, round-robin over the CTAs;
 //   MODE_SPLITK  every tile cut into `splits` equal k ranges (small M x N);
 //   MODE_STREAMK the tiles x k-tiles units are dealt to the CTAs as equal contiguous ranges,
-//                so no SM idles in a partial last wave; a range that ends inside a tile
-//                leaves a partial tile in the workspace for streamk_fixup_kernel.
+//                so no SM idles in a partial last wave.  A CTA whose range starts inside a tile
+//                computes that segment first, stores it as a partial tile and raises its flag;
+//                the CTA that holds the head of the tile (k from 0, the last segment of its
+//                range) adds the partial tiles of the following CTAs to its accumulators in
+//                ascending k and stores the finished tile.  The partial tiles it needs were
+//                stored about a tile's time earlier, so the wait is normally over before it
+//                starts (it is bounded like every other wait).
 constexpr int MODE_TILES = 0, MODE_SPLITK = 1, MODE_STREAMK = 2;
 
 template <int TM, bool A_KMAJ, bool B_KMAJ, int MODE>
@@ -434,6 +442,11 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             const float2 v = ((r & 1) == (c & 1)) ? d0[r >> 1][c >> 1] : d1[r >> 1][c >> 1];
             return (r & 1) ? v.y : v.x;
         };
+        const auto acc_ref = [&](int r, int c) -> float& {
+            float2& v = ((r & 1) == (c & 1)) ? d0[r >> 1][c >> 1] : d1[r >> 1][c >> 1];
+            return (r & 1) ? v.y : v.x;
+        };
+        (void)acc_ref;
         if constexpr (MODE == MODE_TILES) {
             // whole tiles only: store straight to C
             float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
@@ -481,8 +494,58 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 partial_tile = p.splits > 1;
                 slot = w;
             } else if (MODE == 2) {
-                partial_tile = !(kb == 0 && ke == k_tiles);
-                slot = 2ll * blockIdx.x + (w == w_begin ? 0 : 1);   // first / last segment of this CTA's range
+                partial_tile = kb != 0;      // the range starts inside the tile: hand the segment over
+                slot = blockIdx.x;
+                if (kb == 0 && ke != k_tiles) {
+                    // Head of a tile that the following CTAs finish: add their partial tiles
+                    // (ascending CTA = ascending k) to the accumulators, then store the tile.
+                    volatile int& s_hi = *reinterpret_cast<volatile int*>(smem + C::OFF_BAR + 256);
+                    if (tid == 0) {
+                        const long long u_hi = (unit + 1) * k_tiles;
+                        int hi = blockIdx.x;
+                        while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
+                        s_hi = hi;
+                    }
+                    __syncthreads();
+                    const int hi = s_hi;
+                    for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
+                        if (tid == 0) {
+                            const unsigned long long t0 = global_timer_ns();
+                            unsigned int spins = 0, v;
+                            for (;;) {
+                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sk_flags + cta) : "memory");
+                                if (v != 0u) break;
+                                if ((++spins & 63u) == 0 && global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                                    *cta_abort = 1u;
+                                    if (p.status) atomicCAS(p.status, 0u, static_cast<unsigned int>(DEV_WAIT_STREAMK));
+                                    break;
+                                }
+                            }
+                            p.sk_flags[cta] = 0u;   // consumed: the next launch starts from zero again
+                        }
+                        __syncthreads();
+                        if (*cta_abort) return;
+                        const float* src = p.partial + static_cast<long long>(cta) * (C::BM * BN);
+    #pragma unroll
+                        for (int h = 0; h < HALVES; h++)
+    #pragma unroll
+                            for (int ib = 0; ib < 2; ib++)
+    #pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
+                                    const int ai = h * 8 + ib * 4 + i;
+    #pragma unroll
+                                    for (int jb = 0; jb < 2; jb++) {
+                                        const int lc = wn * 64 + jb * 32 + tx * 4;
+                                        const float4 q = __ldcg(reinterpret_cast<const float4*>(src + lr * BN + lc));
+                                        acc_ref(ai, jb * 4 + 0) += q.x;
+                                        acc_ref(ai, jb * 4 + 1) += q.y;
+                                        acc_ref(ai, jb * 4 + 2) += q.z;
+                                        acc_ref(ai, jb * 4 + 3) += q.w;
+                                    }
+                                }
+                    }
+                }
             }
             float* base;
             int ld, row_lim, col_lim, vec_ok;
@@ -529,6 +592,14 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             }
                         }
                     }
+            if (MODE == 2 && partial_tile) {
+                // the partial tile is stored: fence, CTA barrier, flag (release)
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) {
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + blockIdx.x), "r"(1u) : "memory");
+                }
+            }
         }
         w = w_next;
     }
@@ -568,78 +639,6 @@ splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, G
         v[j] = apply_act(v[j], epi.act);
     }
     float* crow = c + static_cast<long long>(bidx) * shape.M * shape.N + static_cast<long long>(r) * shape.N;
-    if (c_vec_ok && cidx + 3 < shape.N) {
-        *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (cidx + j < shape.N) crow[cidx + j] = v[j];
-    }
-}
-
-// Fix-up for MODE_STREAMK.  CTA c of the GEMM owned the units [b(c), b(c+1)), b(c) =
-// work * c / grid.  A tile whose k-tiles were shared by several CTAs has one partial tile per
-// sharing CTA (slot 2c for a CTA's first segment, 2c + 1 for its last); they are added in
-// ascending CTA = ascending k order, then bias / activation, then C.  Tiles that one CTA
-// computed alone were written by the GEMM itself and are never visited: the grid is laid over
-// the grid - 1 range boundaries (BM * BN / 1024 blocks each), a boundary that falls strictly
-// inside a tile marks a shared tile, and the first such boundary of a tile handles it.  The
-// 64-bit divisions are done by one thread per block.
-template <int BM>
-__global__ void __launch_bounds__(256)
-streamk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ c, GemmShape shape,
-                     Epilogue epi, int k_tiles, int grid, int c_vec_ok)
-{
-    constexpr int BLOCKS_PER_TILE = BM * BN / 4 / 256;
-    __shared__ long long s_unit;
-    __shared__ int s_lo, s_hi;
-    const int boundary = blockIdx.x / BLOCKS_PER_TILE + 1;   // 1 .. grid - 1
-    const auto bound = [&](long long cta) { return (shape.work * cta) / grid; };
-    if (threadIdx.x == 0) {
-        const long long u = bound(boundary);
-        const long long unit = u / k_tiles;
-        const long long u_lo = unit * k_tiles, u_hi = u_lo + k_tiles;
-        int lo = -1, hi = -1;
-        // strictly inside the tile, and no earlier boundary inside the same tile
-        if (u != u_lo && bound(boundary - 1) <= u_lo) {
-            lo = boundary - 1;
-            hi = boundary;
-            while (hi + 1 < grid && bound(hi + 1) < u_hi) hi++;
-        }
-        s_unit = unit;
-        s_lo = lo;
-        s_hi = hi;
-    }
-    __syncthreads();
-    const int c_lo = s_lo, c_hi = s_hi;
-    if (c_lo < 0) return;
-    const long long unit = s_unit;
-    const long long u_lo = unit * k_tiles;
-    const int e = (blockIdx.x % BLOCKS_PER_TILE) * 256 + threadIdx.x;
-    const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
-    const int tiles_per_mat = shape.tiles_m * shape.tiles_n;
-    const int bidx = static_cast<int>(unit / tiles_per_mat);
-    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
-    int tm, tn;
-    raster_tile(t, shape.tiles_m, shape.tiles_n, RASTER_GROUP, tm, tn);
-    const int r = tm * BM + lr, cidx = tn * BN + lc;
-    if (r >= shape.M || cidx >= shape.N) return;
-    // the first sharer's segment is the tail of its range (slot 2c+1, or 2c when its range
-    // starts exactly at this tile); every later sharer's segment starts its range (slot 2c)
-    const long long first_slot = 2ll * c_lo + (bound(c_lo) == u_lo ? 0 : 1);
-    float4 sum = *reinterpret_cast<const float4*>(partial + first_slot * (BM * BN) + lr * BN + lc);
-    for (int cta = c_lo + 1; cta <= c_hi; cta++) {
-        const float4 q = *reinterpret_cast<const float4*>(partial + 2ll * cta * (BM * BN) + lr * BN + lc);
-        sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
-    }
-    float v[4] = {sum.x, sum.y, sum.z, sum.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        if (epi.bias && cidx + j < shape.N) v[j] += __ldg(epi.bias + cidx + j);
-        v[j] = apply_act(v[j], epi.act);
-    }
-    float* crow = scatter_base(epi, c, tm * BM) + static_cast<long long>(bidx) * shape.M * shape.N +
-                  static_cast<long long>(r) * shape.N;
     if (c_vec_ok && cidx + 3 < shape.N) {
         *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
     } else {

@@ -2,7 +2,7 @@
 
 Run in a checkout that has the reference mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the Tensotron checkout>
 
 Two sources go into tests/golden/*.json:
 
@@ -158,7 +158,9 @@ def linear_case():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to the Tensotron checkout>")
+    ref_root = sys.argv[1]
     ref = from_reference(ref_root)
     json.dump(ref, open(os.path.join(HERE, "reference_fixtures.json"), "w"), indent=1)
     # The seeded cases are ~0.4 M floats: stored as float32 binary (.npz) plus a small index.

@@ -56,7 +56,7 @@ struct Cfg {
     // chunks of row r stored at chunk index c ^ (r & 7), so both the row-wise writes and the
     // 4-rows-at-a-time reads are free of bank conflicts)
     static constexpr int OUT_WARP_BYTES = 32 * 128;
-    static constexpr int OFF_OUT = OFF_BAR + 256;
+    static constexpr int OFF_OUT = OFF_BAR + 1024;   // 1024-byte aligned: the blocks are TMA-store sources
     static constexpr int SMEM_BYTES = OFF_OUT + EPI_WARPS * OUT_WARP_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory budget");
     static_assert(STAGES >= 2, "shared-memory budget");
@@ -73,6 +73,9 @@ struct Params {
     // (32, rows / 32), so one TMA instruction brings all 32-column boxes of a k-tile
     // (coordinates {0, k, row / 32, batch...}) instead of one instruction per box.
     int a_grouped, b_grouped;
+    // C is written with TMA stores from the staging blocks (map_c: {N, M, batch}, box 32 x 32,
+    // 128-byte swizzle = the staging blocks' layout); 0: plain stores (scatter, N % 4 != 0).
+    int c_tma;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------
@@ -196,7 +199,8 @@ template <int MT, bool A_KMAJ, bool B_KMAJ, bool SPLIT>
 __global__ void __launch_bounds__(THREADS, 1)
 tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_alo,
-                 const __grid_constant__ CUtensorMap map_blo, const Params p)
+                 const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_c,
+                 const Params p)
 {
     using C = Cfg<MT, SPLIT>;
     constexpr int STAGES = C::STAGES;
@@ -372,6 +376,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // instruction writes 4 rows x 128 contiguous bytes: full sectors for L2, full-size
             // packets when the row block belongs to another GPU.)
             const auto emit = [&](const uint32_t (&r)[32], int row0, int c0) {
+                if (p.c_tma && lane == 0) bulk_wait_group_read0();   // the previous TMA store has read the block
                 __syncwarp();   // the previous block's reads of the staging block are done
 #pragma unroll
                 for (int v4 = 0; v4 < 8; v4++) {
@@ -385,6 +390,17 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     *reinterpret_cast<float4*>(out_stage + lane * 128 + ((v4 ^ (lane & 7)) << 4)) =
                         make_float4(v[0], v[1], v[2], v[3]);
+                }
+                if (p.c_tma) {
+                    // one asynchronous bulk store of the 32 x 32 block; rows >= M and columns >= N
+                    // are clipped by the tensor map
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_5d(&map_c, out_stage, n0 + c0, row0, tc.bidx, 0, 0);
+                        bulk_commit_group();
+                    }
+                    return;
                 }
                 __syncwarp();
                 const int col = n0 + c0 + (lane & 7) * 4;
@@ -431,6 +447,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
             if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
+        if (p.c_tma && lane == 0) bulk_wait_group0();   // this thread's bulk stores are complete
     }
 
     // ---- teardown: every role ends up here, also after a wait that gave up ----
@@ -565,10 +582,10 @@ template <int MT, bool SPLIT>
 int launch_cfg(bool ak, bool bk, int grid, cudaStream_t st, const CUtensorMap* maps, const Params& p)
 {
     constexpr int smem = Cfg<MT, SPLIT>::SMEM_BYTES;
-    if (ak && bk) tf32_gemm_kernel<MT, true, true, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
-    else if (ak && !bk) tf32_gemm_kernel<MT, true, false, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
-    else if (!ak && bk) tf32_gemm_kernel<MT, false, true, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
-    else tf32_gemm_kernel<MT, false, false, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    if (ak && bk) tf32_gemm_kernel<MT, true, true, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    else if (ak && !bk) tf32_gemm_kernel<MT, true, false, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    else if (!ak && bk) tf32_gemm_kernel<MT, false, true, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    else tf32_gemm_kernel<MT, false, false, SPLIT><<<grid, THREADS, smem, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
     return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -666,7 +683,7 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     };
     p.a_grouped = (!ak && can_group(va)) ? 1 : 0;
     p.b_grouped = (!bk && can_group(vb)) ? 1 : 0;
-    CUtensorMap maps[4];
+    CUtensorMap maps[5];
     for (int i = 0; i < (split ? 4 : 2); i++) {
         const bool is_a = (i % 2) == 0;
         const bool kmaj = is_a ? ak : bk;
@@ -679,6 +696,18 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
         if (r != 0) return 3;
     }
     if (!split) { maps[2] = maps[0]; maps[3] = maps[1]; }
+    // C through TMA stores when it is a plain (unscattered), 16-byte-aligned tensor
+    p.c_tma = 0;
+    maps[4] = maps[0];
+    if (epi.scatter_rows == 0 && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0) && N % 4 == 0) {
+        OperandView vc;
+        vc.base = c;
+        vc.rank = 3;
+        vc.dim[0] = static_cast<uint64_t>(N);           vc.stride_elems[0] = 1;
+        vc.dim[1] = static_cast<uint64_t>(M);           vc.stride_elems[1] = static_cast<uint64_t>(N);
+        vc.dim[2] = static_cast<uint64_t>(batch_count); vc.stride_elems[2] = static_cast<uint64_t>(M) * static_cast<uint64_t>(N);
+        if (tma_compatible(vc) && encode_tensor_map(&maps[4], vc, 32, 32, Swizzle::B128) == 0) p.c_tma = 1;
+    }
 
     p.shape.M = M; p.shape.N = N; p.shape.K = K;
     p.shape.tiles_m = (M + bm - 1) / bm;

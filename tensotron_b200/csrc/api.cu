@@ -449,11 +449,10 @@ int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     // (the tiny-N form only in strict FP32: in the TF32 modes the tensor-core kernel is faster)
     if (h->math_mode == TT_MATH_FP32 && g.N <= skinny::MAXD && g.M >= 64 && g.K >= 128 && g.aKs == 1 && g.bKs == 1 && g.K % 4 == 0 &&
         g.aMs % 4 == 0 && (g.N == 1 || g.bNs % 4 == 0) && aligned16(g.a) && aligned16(g.b)) {
-        // 8 rows per warp while the accumulators fit comfortably; 4 rows for N > 8 (8 x 16
-        // accumulators need 254 registers and run slower: 143 vs 91 us at 8192 x 10 x 4096)
+        // 8 rows per CTA while the accumulators fit comfortably; 4 rows for N > 8 (8 x 12 and
+        // 8 x 16 accumulators run slower: 105 vs 88 us at 8192 x 10 x 4096)
         const int rows = g.N <= 8 ? 8 : 4;
-        const long long warps = (g.M + rows - 1) / rows;
-        const unsigned int blocks = static_cast<unsigned int>((warps + 7) / 8);
+        const unsigned int blocks = static_cast<unsigned int>((g.M + rows - 1) / rows);   // one CTA per row group
         if (g.N <= 4)
             skinny::skinny_n_kernel<8, 4><<<blocks, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.bNs, g.epi);
         else if (g.N <= 8)

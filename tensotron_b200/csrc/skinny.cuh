@@ -25,37 +25,47 @@ __device__ __forceinline__ float act_apply(float v, int act)
 }
 
 // ---- small N ---------------------------------------------------------------------------------
-// One warp per ROWS rows of A (N <= NT).  Lanes stride over K in float4 steps; every lane keeps
-// ROWS x N partial sums; a fixed xor-shuffle tree adds the 32 lanes.  More rows per warp cut
-// the L1 traffic for the small operand (N x 16 bytes per lane and k step) relative to the large one.
+// One CTA per ROWS rows of A (N <= NT).  The 8 warps of the CTA cut K into 8 contiguous slices,
+// so a row's K elements are in flight from 8 warps at once (one warp walking a whole row is
+// latency-bound: 86 us for any M up to 8192 at K = 4096).  Lanes stride over their slice in
+// float4 steps; every lane keeps ROWS x N partial sums; a fixed xor-shuffle tree adds the 32
+// lanes, shared memory the 8 warps in warp order: the summation order is a function of the
+// shape only.  More rows per CTA cut the L1 traffic for the small operand relative to the large one.
 template <int ROWS, int NT>
 __global__ void __launch_bounds__(256)
 skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
                 int M, int N, int K, int aMs, int bNs, Epilogue epi)
 {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    __shared__ float part[8][ROWS][NT];
+    const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m0 = warp * ROWS;
-    if (m0 >= M) return;
+    const int m0 = blockIdx.x * ROWS;
     float acc[ROWS][NT];
 #pragma unroll
     for (int r = 0; r < ROWS; r++)
 #pragma unroll
         for (int n = 0; n < NT; n++) acc[r][n] = 0.f;
-    // Warps start at different k offsets (rotated by the warp index): rows are a power-of-two
-    // number of bytes apart, and thousands of warps walking them in lockstep from k = 0 would
-    // keep hitting the same memory channels.  The order is a function of the row only.
-    const int iters = (K + 127) / 128;
-    const int rot = (warp * 5) % iters;
-    for (int i = 0; i < iters; i++) {
-        int it = i + rot;
-        if (it >= iters) it -= iters;
+    // slice of this warp: a multiple of 128 k (one float4 per lane and step)
+    const int steps = (K + 127) / 128;
+    const int per_warp = (steps + 7) / 8;
+    const int s_begin = warp * per_warp;
+    const int s_end = min(steps, s_begin + per_warp);
+    // CTAs start at different steps of their slices (rotated by the CTA index): rows are a
+    // power-of-two number of bytes apart, and thousands of warps walking them in lockstep from the
+    // same offsets would keep hitting the same memory channels.  The order is a function of the
+    // row only.
+    const int span = s_end - s_begin;
+    const int rot = span > 0 ? static_cast<int>(blockIdx.x % span) : 0;
+    for (int i = 0; i < span; i++) {
+        int it = s_begin + i + rot;
+        if (it >= s_end) it -= span;
         const int k = it * 128 + lane * 4;
         if (k >= K) continue;
         float4 av[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; r++)
-            av[r] = (m0 + r < M) ? *reinterpret_cast<const float4*>(a + static_cast<long long>(m0 + r) * aMs + k)
+            // (streaming load: A is read once and must not push the small operand out of L1)
+            av[r] = (m0 + r < M) ? __ldcs(reinterpret_cast<const float4*>(a + static_cast<long long>(m0 + r) * aMs + k))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int n = 0; n < NT; n++) {
@@ -81,12 +91,20 @@ skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
                 float s = acc[r][n];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0 && m0 + r < M) {
-                    if (epi.bias) s += __ldg(epi.bias + n);
-                    c[static_cast<long long>(m0 + r) * N + n] = act_apply(s, epi.act);
-                }
+                if (lane == 0) part[warp][r][n] = s;
             }
         }
+    __syncthreads();
+    for (int e = threadIdx.x; e < ROWS * NT; e += blockDim.x) {
+        const int r = e / NT, n = e % NT;
+        if (n < N && m0 + r < M) {
+            float s = part[0][r][n];
+#pragma unroll
+            for (int w = 1; w < 8; w++) s += part[w][r][n];
+            if (epi.bias) s += __ldg(epi.bias + n);
+            c[static_cast<long long>(m0 + r) * N + n] = act_apply(s, epi.act);
+        }
+    }
 }
 
 // ---- small M ---------------------------------------------------------------------------------

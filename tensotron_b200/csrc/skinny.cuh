@@ -56,17 +56,20 @@ skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
     // row only.
     const int span = s_end - s_begin;
     const int rot = span > 0 ? static_cast<int>(blockIdx.x % span) : 0;
-    for (int i = 0; i < span; i++) {
+    const auto step_k = [&](int i) {
         int it = s_begin + i + rot;
         if (it >= s_end) it -= span;
-        const int k = it * 128 + lane * 4;
-        if (k >= K) continue;
-        float4 av[ROWS];
+        return it * 128 + lane * 4;
+    };
+    const auto load_a = [&](int k, float4 (&av)[ROWS]) {
 #pragma unroll
         for (int r = 0; r < ROWS; r++)
             // (streaming load: A is read once and must not push the small operand out of L1)
-            av[r] = (m0 + r < M) ? __ldcs(reinterpret_cast<const float4*>(a + static_cast<long long>(m0 + r) * aMs + k))
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            av[r] = (k < K && m0 + r < M) ? __ldcs(reinterpret_cast<const float4*>(a + static_cast<long long>(m0 + r) * aMs + k))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    const auto fma_step = [&](int k, const float4 (&av)[ROWS]) {
+        if (k >= K) return;
 #pragma unroll
         for (int n = 0; n < NT; n++) {
             if (n < N) {
@@ -82,6 +85,23 @@ skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
                 }
             }
         }
+    };
+    // two steps per iteration: the loads of both are issued before the first FMA, which doubles
+    // the bytes a warp keeps in flight
+    int i = 0;
+    for (; i + 1 < span; i += 2) {
+        const int k0 = step_k(i), k1 = step_k(i + 1);
+        float4 a0[ROWS], a1[ROWS];
+        load_a(k0, a0);
+        load_a(k1, a1);
+        fma_step(k0, a0);
+        fma_step(k1, a1);
+    }
+    if (i < span) {
+        const int k0 = step_k(i);
+        float4 a0[ROWS];
+        load_a(k0, a0);
+        fma_step(k0, a0);
     }
 #pragma unroll
     for (int r = 0; r < ROWS; r++)

@@ -42,6 +42,7 @@ typedef struct tt_handle_s* tt_handle_t;
 #define TT_ERR_WORKSPACE 4     /* handle workspace too small for the requested variant  */
 #define TT_ERR_DEVICE_WAIT 5   /* a bounded device-side wait ran out (see tt_check)     */
 #define TT_ERR_STATIC_LIMIT 6  /* size beyond what a *_static entry's built-in scratch holds */
+#define TT_ERR_BAD_LABEL 7     /* tt_check: a cross-entropy label was outside [0, classes)   */
 
 /* math modes: 0 and 3 carry the meaning of SetCuBlasMathMode
  * (src/Tensotron/TensorRuntime.cs:332-338: 0 = FP32, 3 = TF32); 4 is new. */

@@ -179,13 +179,14 @@ class MlpOracle:
             zs.append(z)
             acts.append(y)
         loss, g = cross_entropy(acts[-1], labels)
-        dws, dbs = [None] * L, [None] * L
+        dws, dbs, gs = [None] * L, [None] * L, [None] * L
         for i in reversed(range(L)):
-            dx, dw, db, _ = linear_bwd(acts[i], self.w[i], zs[i], acts[i + 1], g,
-                                       1 if i < L - 1 else 0, need_dx=i > 0)
-            dws[i], dbs[i] = dw, db
+            dx, dw, db, gm = linear_bwd(acts[i], self.w[i], zs[i], acts[i + 1], g,
+                                        1 if i < L - 1 else 0, need_dx=i > 0)
+            dws[i], dbs[i], gs[i] = dw, db, gm
             g = dx
         self.grads = dws + dbs
+        self.acts, self.gs = acts, gs      # layer inputs and masked upstream gradients, for error bounds
         if apply_update:
             for t, gr, (m, v, adv) in zip(self.w + self.b, self.grads, self.state):
                 adam_step(t, gr, m, v, adv, lr=self.lr)

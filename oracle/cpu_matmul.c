@@ -205,18 +205,62 @@ void oracle_matmul_batched_fast(const float *a, const float *b, float *c, int ba
     }
 }
 
-/* float64 accumulation of the same contract: the error-budget yardstick. */
+/* float64 accumulation of the same contract: the error-budget yardstick (not a restatement
+ * of reference code).  Rows are independent; with B contiguous along N the k loop is outermost
+ * per row so that B is walked along its rows (the row-slab checks of 8192- and 16384-wide
+ * products would otherwise take a cache miss per term).  Row-parallel like oracle_matmul2d. */
+typedef struct {
+    const float *a, *b; double *c;
+    int N, K, aMs, aKs, bKs, bNs, s, e;
+} row_job64;
+
+static void *row_worker64(void *p)
+{
+    row_job64 *j = (row_job64 *)p;
+    const int N = j->N, K = j->K;
+    for (int m = j->s; m < j->e; m++) {
+        double *cr = j->c + (long long)m * N;
+        if (j->bNs == 1) {
+            for (int n = 0; n < N; n++) cr[n] = 0.0;
+            for (int k = 0; k < K; k++) {
+                const double av = (double)j->a[(long long)m * j->aMs + (long long)k * j->aKs];
+                const float *br = j->b + (long long)k * j->bKs;
+                for (int n = 0; n < N; n++) cr[n] += av * (double)br[n];
+            }
+        } else {
+            for (int n = 0; n < N; n++) {
+                double acc = 0.0;
+                for (int k = 0; k < K; k++)
+                    acc += (double)j->a[(long long)m * j->aMs + (long long)k * j->aKs] *
+                           (double)j->b[(long long)n * j->bNs + (long long)k * j->bKs];
+                cr[n] = acc;
+            }
+        }
+    }
+    return NULL;
+}
+
 void oracle_matmul2d_f64(const float *a, const float *b, double *c, int M, int N, int K,
                          int aMs, int aKs, int bKs, int bNs)
 {
-    for (int m = 0; m < M; m++)
-        for (int n = 0; n < N; n++) {
-            double acc = 0.0;
-            for (int k = 0; k < K; k++)
-                acc += (double)a[(long long)m * aMs + (long long)k * aKs] *
-                       (double)b[(long long)n * bNs + (long long)k * bKs];
-            c[(long long)m * N + n] = acc;
-        }
+    int chunks = g_threads < M ? g_threads : M;
+    if (chunks < 1 || 2LL * M * N * K < g_min_flops) chunks = 1;
+    const int per = (M + chunks - 1) / chunks;
+    pthread_t tid[256];
+    row_job64 jobs[256];
+    if (chunks > 256) chunks = 256;
+    int started = 0;
+    for (int ci = 0; ci < chunks; ci++) {
+        const int s = ci * per;
+        if (s >= M) break;
+        const int e = (ci == chunks - 1 || s + per > M) ? M : s + per;
+        row_job64 j = {a, b, c, N, K, aMs, aKs, bKs, bNs, s, e};
+        jobs[started] = j;
+        if (chunks == 1) { row_worker64(&jobs[0]); return; }
+        pthread_create(&tid[started], NULL, row_worker64, &jobs[started]);
+        started++;
+    }
+    for (int i = 0; i < started; i++) pthread_join(tid[i], NULL);
 }
 
 /* ---- Linear support ops -------------------------------------------------- */

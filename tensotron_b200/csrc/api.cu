@@ -4,7 +4,9 @@
 // can be recorded into a CUDA graph.
 #include "../../include/tensotron_gemm.h"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
+#include <cudaTypedefs.h>
 #include <stdio.h>
 #include <string.h>
 
@@ -20,6 +22,7 @@
 using namespace tt;
 
 struct tt_handle_s {
+    CUcontext ctx;   // the CUDA context the handle's memory and kernels live in (see tt_create)
     int device;
     int num_sms;
     int math_mode;
@@ -591,14 +594,64 @@ int check_common(tt_handle_t h, const void* a, const void* b, const void* c, int
     return TT_OK;
 }
 
-int bind(tt_handle_t h)
+// Driver entry points, resolved through the runtime so the library does not link libcuda.
+struct DriverApi {
+    PFN_cuCtxGetCurrent_v4000 get_current = nullptr;
+    PFN_cuCtxPushCurrent_v4000 push_current = nullptr;
+    PFN_cuCtxPopCurrent_v4000 pop_current = nullptr;
+    PFN_cuCtxGetDevice_v2000 get_device = nullptr;
+    bool ok = false;
+};
+
+const DriverApi& driver_api()
 {
-    int cur = -1;
-    if (cudaGetDevice(&cur) == cudaSuccess && cur == h->device) return TT_OK;
-    const cudaError_t e = cudaSetDevice(h->device);
-    if (e != cudaSuccess) return cuda_fail(h, e, "cudaSetDevice");
-    return TT_OK;
+    static DriverApi api = [] {
+        DriverApi d;
+        const auto get = [](const char* name) -> void* {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+                return nullptr;
+            return fn;
+        };
+        d.get_current = reinterpret_cast<PFN_cuCtxGetCurrent_v4000>(get("cuCtxGetCurrent"));
+        d.push_current = reinterpret_cast<PFN_cuCtxPushCurrent_v4000>(get("cuCtxPushCurrent"));
+        d.pop_current = reinterpret_cast<PFN_cuCtxPopCurrent_v4000>(get("cuCtxPopCurrent"));
+        d.get_device = reinterpret_cast<PFN_cuCtxGetDevice_v2000>(get("cuCtxGetDevice"));
+        d.ok = d.get_current && d.push_current && d.pop_current && d.get_device;
+        return d;
+    }();
+    return api;
 }
+
+// Every entry runs in the handle's context.  Normally that context is already current on the
+// calling thread (the host made it current before tt_create and keeps it so) and the scope does
+// nothing.  When another context, or none, is current, the handle's context is pushed for the
+// duration of the call and popped again: the caller's current context is never replaced.
+struct CtxScope {
+    bool pushed = false;
+    int rc = TT_OK;
+    explicit CtxScope(tt_handle_t h)
+    {
+        const DriverApi& d = driver_api();
+        CUcontext cur = nullptr;
+        if (!d.ok || d.get_current(&cur) != CUDA_SUCCESS) { rc = cuda_fail(h, cudaErrorUnknown, "cuCtxGetCurrent"); return; }
+        if (cur == h->ctx) return;
+        if (d.push_current(h->ctx) != CUDA_SUCCESS) { rc = cuda_fail(h, cudaErrorUnknown, "cuCtxPushCurrent"); return; }
+        pushed = true;
+    }
+    ~CtxScope()
+    {
+        if (pushed) { CUcontext out = nullptr; driver_api().pop_current(&out); }
+    }
+    CtxScope(const CtxScope&) = delete;
+    CtxScope& operator=(const CtxScope&) = delete;
+};
+
+// First statement of every entry after its argument checks: declares the scope object for the rest of the function.
+#define TT_BIND(h)                  \
+    CtxScope tt_ctx_scope_(h);      \
+    if (tt_ctx_scope_.rc) return tt_ctx_scope_.rc
 
 // Linear backward (activation backward + bias gradient, dX, dW).  With `scatter` the weight
 // gradient is first offered to the kernels whose epilogue stores through the scatter table;
@@ -613,8 +666,9 @@ int linear_bwd_impl(tt_handle_t h, cudaStream_t st, const float* x, const float*
     if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
     if (!dy || !x || !w || !dw || (act != TT_ACT_NONE && !y))
         return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
 
     const float* g = dy;
@@ -681,9 +735,24 @@ TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle
     *out_handle = nullptr;
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return TT_ERR_CUDA;
-    if (cudaSetDevice(device) != cudaSuccess) return TT_ERR_CUDA;
+    // Context: the one that is current on the calling thread when it belongs to `device` (a host
+    // with a driver-API context of its own makes it current before this call, the way it does
+    // for its cuBLAS handle); only when none is current, or the current one is on another
+    // device, the device's primary context is made current (cudaSetDevice).
+    const DriverApi& d = driver_api();
+    if (!d.ok) return TT_ERR_CUDA;
+    CUcontext ctx = nullptr;
+    CUdevice ctx_dev = -1;
+    if (d.get_current(&ctx) != CUDA_SUCCESS) return TT_ERR_CUDA;
+    if (ctx && (d.get_device(&ctx_dev) != CUDA_SUCCESS || static_cast<int>(ctx_dev) != device)) ctx = nullptr;
+    if (!ctx) {
+        if (cudaSetDevice(device) != cudaSuccess) return TT_ERR_CUDA;
+        if (cudaFree(nullptr) != cudaSuccess) return TT_ERR_CUDA;   // brings the primary context up
+        if (d.get_current(&ctx) != CUDA_SUCCESS || !ctx) return TT_ERR_CUDA;
+    }
     tt_handle_s* h = new tt_handle_s();
     memset(h, 0, sizeof(*h));
+    h->ctx = ctx;
     h->device = device;
     h->math_mode = TT_MATH_FP32;
     cudaDeviceProp prop;
@@ -694,6 +763,7 @@ TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle
     if (cudaMalloc(&h->workspace, h->workspace_bytes) != cudaSuccess) { delete h; return TT_ERR_CUDA; }
     if (cudaMalloc(&h->status, HANDLE_WORDS * sizeof(unsigned int)) != cudaSuccess) { cudaFree(h->workspace); delete h; return TT_ERR_CUDA; }
     cudaMemset(h->status, 0, HANDLE_WORDS * sizeof(unsigned int));
+    // kernel attributes are per context: set them in this one
     if (init_kernels() != cudaSuccess) { cudaFree(h->workspace); cudaFree(h->status); delete h; return TT_ERR_CUDA; }
     h->stats.workspace_bytes = static_cast<long long>(h->workspace_bytes);
     h->err[0] = 0;
@@ -704,9 +774,13 @@ TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle
 TT_API int tt_destroy(tt_handle_t h)
 {
     if (!h) return TT_ERR_INVALID_ARG;
-    cudaSetDevice(h->device);
-    cudaFree(h->workspace);
-    cudaFree(h->status);
+    {
+        CtxScope scope(h);
+        if (scope.rc == TT_OK) {
+            cudaFree(h->workspace);
+            cudaFree(h->status);
+        }
+    }
     delete h;
     return TT_OK;
 }
@@ -716,6 +790,10 @@ TT_API const char* tt_last_error(tt_handle_t h) { return h ? h->err : "null hand
 TT_API int tt_set_math_mode(tt_handle_t h, int mode)
 {
     if (!h) return TT_ERR_INVALID_ARG;
+    // 1 is cuBLAS's legacy tensor-op math, which SetCuBlasMathMode also accepts
+    // (src/Tensotron/TensorRuntime.cs:332-338): served by the TF32 kernel, the nearest mode here
+    // (and more accurate than the FP16-class arithmetic that value selects in cuBLAS).
+    if (mode == 1) mode = TT_MATH_TF32;
     if (mode != TT_MATH_FP32 && mode != TT_MATH_TF32 && mode != TT_MATH_3XTF32)
         return fail(h, TT_ERR_INVALID_ARG, "unknown math mode");
     h->math_mode = mode;
@@ -741,7 +819,7 @@ TT_API int tt_matmul(tt_handle_t h, void* stream, const float* a, const float* b
 {
     int rc = check_common(h, a, b, c, M, N, K);
     if (rc) return rc;
-    if ((rc = bind(h))) return rc;
+    TT_BIND(h);
     h->stats.calls++;
     GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
@@ -763,7 +841,7 @@ TT_API int tt_matmul_batched(tt_handle_t h, void* stream, const float* a, const 
         prod *= batchDims[i];
     }
     if (prod != batchCount) return fail(h, TT_ERR_INVALID_ARG, "batchCount != product(batchDims)");
-    if ((rc = bind(h))) return rc;
+    TT_BIND(h);
     h->stats.calls++;
     GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, HostBatch(), batchCount,
                Epilogue{nullptr, TT_ACT_NONE}};
@@ -806,7 +884,7 @@ TT_API int tt_matmul_batched_reduce(tt_handle_t h, void* stream, const float* a,
             nk++;
         }
     }
-    if ((rc = bind(h))) return rc;
+    TT_BIND(h);
     h->stats.calls++;
     const int rc_n = hb.red_count, rc_a = hb.red_as, rc_b = hb.red_bs;
     if (!collapse_batch(nk, kd, ka, kb, hb))
@@ -822,7 +900,7 @@ TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const floa
     int rc = check_common(h, x, w, y, M, N, K);
     if (rc) return rc;
     if (act < TT_ACT_NONE || act > TT_ACT_TANH) return fail(h, TT_ERR_INVALID_ARG, "unknown activation");
-    if ((rc = bind(h))) return rc;
+    TT_BIND(h);
     h->stats.calls++;
     // y[m,n] = sum_k x[m*K + k] * w[n*K + k]   (src/Tensotron/TensorOps.LinearNT.cs:24)
     GemmCall g{x, w, y, M, N, K, K, 1, 1, K, HostBatch(), 1, Epilogue{bias, act}};
@@ -841,8 +919,9 @@ TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* lo
 {
     if (!h) return TT_ERR_INVALID_ARG;
     if (rows < 0 || classes <= 0 || !logits || !labels) return fail(h, TT_ERR_INVALID_ARG, "bad cross-entropy arguments");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     if (rows == 0) return TT_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -851,7 +930,7 @@ TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* lo
     float* row_loss = loss ? reinterpret_cast<float*>(h->workspace) : nullptr;
     const int warps_per_block = 8;
     ew::softmax_ce_rows_kernel<<<(rows + warps_per_block - 1) / warps_per_block, 256, 0, st>>>(
-        logits, labels, dlogits, row_loss, rows, classes, scale);
+        logits, labels, dlogits, row_loss, rows, classes, scale, h->status);
     h->stats.launches++;
     if (loss) {
         ew::sum_fixed_kernel<<<1, 1024, 0, st>>>(row_loss, loss, rows, scale);
@@ -868,8 +947,9 @@ TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, f
 {
     if (!h) return TT_ERR_INVALID_ARG;
     if (n < 0 || !adv || (n > 0 && (!p || !g || !m || !v))) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (advance) {
@@ -895,8 +975,9 @@ TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* 
 {
     if (!h) return TT_ERR_INVALID_ARG;
     if (n < 0 || (n > 0 && (!target || !source))) return fail(h, TT_ERR_INVALID_ARG, "bad AddInto arguments");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     if (n == 0) return TT_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -951,8 +1032,9 @@ TT_API int tt_reset_stats(tt_handle_t h)
 TT_API int tt_check(tt_handle_t h, void* stream)
 {
     if (!h) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(h, e, "stream synchronize");
@@ -960,8 +1042,12 @@ TT_API int tt_check(tt_handle_t h, void* stream)
     e = cudaMemcpy(&word, h->status, sizeof(word), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(h, e, "status read");
     if (word != 0) {
-        snprintf(h->err, sizeof(h->err), "device-side bounded wait gave up (code %u)", word);
         cudaMemset(h->status, 0, HANDLE_WORDS * sizeof(unsigned int));   // the status word and any flag left raised
+        if (word == DEV_BAD_LABEL) {
+            snprintf(h->err, sizeof(h->err), "cross-entropy label outside [0, classes): that row's loss is NaN");
+            return TT_ERR_BAD_LABEL;
+        }
+        snprintf(h->err, sizeof(h->err), "device-side bounded wait gave up (code %u)", word);
         return TT_ERR_DEVICE_WAIT;
     }
     return TT_OK;
@@ -987,8 +1073,9 @@ static_assert(TT_MAX_PEERS == MAX_PEERS && TT_MAX_SEGMENTS == peer::MAX_SEGS && 
 TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr)
 {
     if (!h || !out_ptr || bytes == 0) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer allocation");
@@ -1001,8 +1088,9 @@ TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr)
 TT_API int tt_peer_free(tt_handle_t h, void* ptr)
 {
     if (!h) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     const cudaError_t e = cudaFree(ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer free");
     return TT_OK;
@@ -1011,8 +1099,9 @@ TT_API int tt_peer_free(tt_handle_t h, void* ptr)
 TT_API int tt_peer_export(tt_handle_t h, void* ptr, unsigned char* handle_out)
 {
     if (!h || !ptr || !handle_out) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     cudaIpcMemHandle_t hd;
     const cudaError_t e = cudaIpcGetMemHandle(&hd, ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcGetMemHandle");
@@ -1023,8 +1112,9 @@ TT_API int tt_peer_export(tt_handle_t h, void* ptr, unsigned char* handle_out)
 TT_API int tt_peer_open(tt_handle_t h, const unsigned char* handle, void** out_ptr)
 {
     if (!h || !handle || !out_ptr) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     cudaIpcMemHandle_t hd;
     memcpy(&hd, handle, sizeof(hd));
     void* p = nullptr;
@@ -1037,8 +1127,9 @@ TT_API int tt_peer_open(tt_handle_t h, const unsigned char* handle, void** out_p
 TT_API int tt_peer_close(tt_handle_t h, void* ptr)
 {
     if (!h || !ptr) return TT_ERR_INVALID_ARG;
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     const cudaError_t e = cudaIpcCloseMemHandle(ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcCloseMemHandle");
     return TT_OK;
@@ -1154,8 +1245,9 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int chan
 {
     if (!h || !g) return TT_ERR_INVALID_ARG;
     if (channel < 0 || channel >= peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad exchange channel");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     peer::SegList segs;
@@ -1195,8 +1287,9 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     if (!h || !g) return TT_ERR_INVALID_ARG;
     if (channel < 0 || channel >= peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad exchange channel");
     if (!m || !v || !adv || !aligned16(m) || !aligned16(v)) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     peer::SegList owned, repl;
@@ -1228,8 +1321,9 @@ TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g, int n_ch
 {
     if (!h || !g) return TT_ERR_INVALID_ARG;
     if (n_channels < 1 || n_channels > peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad channel count");
-    int rc = bind(h);
-    if (rc) return rc;
+    TT_BIND(h);
+    int rc = TT_OK;
+    (void)rc;
     h->stats.calls++;
     peer::wait_kernel<<<1, 32 * n_channels, 0, static_cast<cudaStream_t>(stream)>>>(
         g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, h->status,

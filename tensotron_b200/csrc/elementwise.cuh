@@ -14,7 +14,7 @@ constexpr int COLSUM_COLS = 128;      // columns per CTA
 constexpr int COLSUM_ROW_LANES = 8;   // row lanes per CTA (256 threads = 32 col groups x 8)
 constexpr int COLSUM_MAX_CHUNKS = 64;
 
-inline int colsum_chunks(int M)
+static inline int colsum_chunks(int M)
 {
     int c = M / 64;
     if (c < 1) c = 1;
@@ -98,7 +98,7 @@ act_bwd_colsum_kernel(const float* __restrict__ y, const float* __restrict__ dy,
 }
 
 // out[n] = sum over chunks (ascending) of partial[chunk][n].
-__global__ void colsum_finish_kernel(const float* __restrict__ partial, float* __restrict__ out,
+static __global__ void colsum_finish_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                      int N, int chunks)
 {
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
@@ -110,10 +110,14 @@ __global__ void colsum_finish_kernel(const float* __restrict__ partial, float* _
 
 // One warp per row: lse = log(sum exp(x - max)) + max; row_loss = -(x[label] - lse);
 // dlogits = (exp(x - lse) - onehot) * scale.  Warp shuffles reduce in a fixed tree.
-__global__ void __launch_bounds__(256)
+// A label outside [0, classes) is never used as an index: that row's loss becomes NaN (so the
+// summed loss is NaN), its gradient is the plain softmax, and code 7 (DEV_BAD_LABEL of ptx.cuh) is
+// recorded in *status when status is not null.  (static: this header is compiled into more than
+// one translation unit of the library.)
+static __global__ void __launch_bounds__(256)
 softmax_ce_rows_kernel(const float* __restrict__ logits, const int* __restrict__ labels,
                        float* __restrict__ dlogits, float* __restrict__ row_loss, int rows,
-                       int classes, float scale)
+                       int classes, float scale, unsigned int* status)
 {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -129,7 +133,11 @@ softmax_ce_rows_kernel(const float* __restrict__ logits, const int* __restrict__
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float lse = logf(s) + mx;
     const int label = labels[warp];
-    if (row_loss && lane == 0) row_loss[warp] = -(x[label] - lse);
+    const bool label_ok = label >= 0 && label < classes;
+    if (lane == 0) {
+        if (row_loss) row_loss[warp] = label_ok ? -(x[label] - lse) : __int_as_float(0x7fc00000);
+        if (!label_ok && status) atomicCAS(status, 0u, 7u);
+    }
     if (dlogits) {
         float* d = dlogits + static_cast<long long>(warp) * classes;
         for (int j = lane; j < classes; j += 32)
@@ -139,7 +147,7 @@ softmax_ce_rows_kernel(const float* __restrict__ logits, const int* __restrict__
 
 // Single-CTA fixed-order sum: each thread adds a strided slice in ascending order,
 // then a shared-memory tree with a fixed shape.  out = scale * sum(v[0..n)).
-__global__ void __launch_bounds__(1024)
+static __global__ void __launch_bounds__(1024)
 sum_fixed_kernel(const float* __restrict__ v, float* __restrict__ out, int n, float scale)
 {
     __shared__ float red[1024];
@@ -155,7 +163,7 @@ sum_fixed_kernel(const float* __restrict__ v, float* __restrict__ out, int n, fl
 }
 
 // adv = [t, 1/(1-b1^t), 1/(1-b2^t)]; one thread.
-__global__ void adam_advance_kernel(float* adv, float b1, float b2)
+static __global__ void adam_advance_kernel(float* adv, float b1, float b2)
 {
     const float t = adv[0] + 1.f;
     adv[0] = t;
@@ -215,7 +223,7 @@ adam_step_kernel(float* __restrict__ p, const float* __restrict__ g, float* __re
 // multiples of 4, both bases 16-byte aligned).  64 x 64 tiles through shared memory, 128-bit
 // accesses on both sides.  Used to bring a large K-major GEMM operand into the MN-major form the
 // FMA kernel reads without a shared-memory transposition.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int R, int C, long long ld_src,
                  long long ld_dst)
 {

@@ -96,8 +96,9 @@ copy_to_peer_kernel(const float* __restrict__ src, float* __restrict__ dst, long
         reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
 }
 
-// Polls flags[s] until it has reached `epoch` (wrap-safe), at most limit_ns.
-__device__ __forceinline__ void wait_flag(const unsigned int* flags, int s, unsigned int epoch,
+// Polls flags[s] until it has reached `epoch` (wrap-safe), at most limit_ns.  Returns false
+// (after recording DEV_WAIT_PEER in *status) when the limit ran out.
+__device__ __forceinline__ bool wait_flag(const unsigned int* flags, int s, unsigned int epoch,
                                           unsigned int* status, unsigned long long limit_ns)
 {
     const unsigned long long t0 = global_timer_ns();
@@ -105,10 +106,10 @@ __device__ __forceinline__ void wait_flag(const unsigned int* flags, int s, unsi
     for (;;) {
         unsigned int v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
-        if (static_cast<int>(v - epoch) >= 0) break;
+        if (static_cast<int>(v - epoch) >= 0) return true;
         if ((++spins & 255u) == 0 && global_timer_ns() - t0 > limit_ns) {
             atomicCAS(status, 0u, static_cast<unsigned int>(DEV_WAIT_PEER));
-            break;
+            return false;
         }
         __nanosleep(200);
     }
@@ -166,7 +167,7 @@ __global__ void wait_kernel(const unsigned int* flags, int world, const unsigned
     const int s = threadIdx.x & 31;
     if (s >= world) return;
     flags += (threadIdx.x >> 5) * CHANNEL_WORDS;
-    wait_flag(flags, s, *step_counter, status, limit_ns);
+    (void)wait_flag(flags, s, *step_counter, status, limit_ns);
     __threadfence_system();
 }
 
@@ -189,9 +190,18 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
                    const unsigned int* step_counter, unsigned int* status, unsigned long long limit_ns,
                    FlagPtrs signal, unsigned int* done_counter)
 {
-    __shared__ unsigned int s_last;
-    if (threadIdx.x < world) wait_flag(wait_flags, threadIdx.x, *step_counter, status, limit_ns);
+    __shared__ unsigned int s_last, s_bad;
+    if (threadIdx.x == 0) s_bad = 0u;
     __syncthreads();
+    if (threadIdx.x < world && !wait_flag(wait_flags, threadIdx.x, *step_counter, status, limit_ns)) atomicOr(&s_bad, 1u);
+    __syncthreads();
+    // A rank that never signalled (or any error already recorded on this handle: another block of
+    // this launch may be the one whose wait ran out) ends the step here: no sum over slots that
+    // may be stale, no Adam, nothing stored to any rank, no "rows updated" signal.  The block is
+    // still counted, so that the last one resets the counter for the next launch.
+    if (threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(status) != 0u) s_bad = 1u;
+    __syncthreads();
+    const bool bad = s_bad != 0u;
     float t = adv[0], ibc1 = adv[1], ibc2 = adv[2];
     if (advance) {
         t += 1.f;
@@ -201,7 +211,7 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
     const float omb1 = 1.f - b1, omb2 = 1.f - b2;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     float* own = params.p[rank];
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < owned4 + repl4; i += stride) {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; !bad && i < owned4 + repl4; i += stride) {
         const bool is_owned = i < owned4;
         const long long at = is_owned ? seg_locate(owned, i) : seg_locate(repl, i - owned4);
         float4 g = reinterpret_cast<const float4*>(stage)[at];
@@ -234,12 +244,14 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
     __syncthreads();
     if (!s_last) return;
     __threadfence_system();
+    // (a block that gave up recorded its code before it was counted: the last block sees it)
+    const bool failed = *reinterpret_cast<volatile unsigned int*>(status) != 0u;
     if (threadIdx.x == 0) {
         *done_counter = 0u;
-        if (advance) { adv[0] = t; adv[1] = ibc1; adv[2] = ibc2; }
+        if (advance && !failed) { adv[0] = t; adv[1] = ibc1; adv[2] = ibc2; }
     }
     const int o = threadIdx.x;
-    if (o < world && signal.p[o]) {
+    if (!failed && o < world && signal.p[o]) {
         const unsigned int e = *step_counter;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.p[o]), "r"(e) : "memory");
     }

@@ -16,6 +16,7 @@ enum : unsigned int {
     DEV_WAIT_TMEM = 4,    // MMA issuer gave up waiting for a drained accumulator
     DEV_WAIT_PEER = 5,    // a wait for another GPU's flag (gradient / parameter exchange) gave up
     DEV_WAIT_STREAMK = 6, // a stream-K CTA gave up waiting for a neighbour's partial tile
+    DEV_BAD_LABEL = 7,    // cross-entropy met a label outside [0, classes)
 };
 
 // Upper bound on one wait, in nanoseconds of %globaltimer.  The longest legitimate

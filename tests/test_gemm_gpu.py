@@ -498,6 +498,33 @@ def test_cross_entropy_large_matches_oracle(rt):
     np.testing.assert_allclose(d.cpu().numpy(), do, atol=1e-9, rtol=2e-5)
 
 
+def test_cross_entropy_label_outside_the_classes_is_an_error_code_not_a_stray_read(rt):
+    """The reference indexes with host int[] targets and throws on a bad one; here labels are on
+    the device, so a label outside [0, classes) is never used as an index: the loss turns NaN
+    and tt_check reports status 7."""
+    from tensotron_b200 import runtime
+    rng = np.random.default_rng(10)
+    x = dev(rng.standard_normal((64, 10)) * 2)
+    for bad in (10, -1, 2 ** 30):
+        y = rng.integers(0, 10, 64).astype(np.int32)
+        y[17] = bad
+        yd = torch.from_numpy(y).cuda()
+        d = torch.empty((64, 10), device="cuda")
+        loss = torch.zeros(1, device="cuda")
+        rt.LaunchSoftmaxCrossEntropy(x, yd, d, loss, 64, 10, 1.0 / 64)
+        with pytest.raises(TensotronGemmError) as e:
+            rt.Check()
+        assert e.value.status == 7
+        rt.Check()                                  # reported once, then cleared
+        assert np.isnan(loss.item())
+        assert torch.isfinite(d).all()              # the gradient is the plain softmax on that row
+        # the allocation-free entry has no handle to report through: NaN loss only
+        l2 = torch.zeros(1, device="cuda")
+        runtime.softmax_cross_entropy_static(x, yd, None, l2, 64, 10, 1.0 / 64)
+        torch.cuda.synchronize()
+        assert np.isnan(l2.item())
+
+
 def test_add_into(rt):
     a = torch.arange(1003, dtype=torch.float32, device="cuda")
     b = torch.ones(1003, device="cuda")

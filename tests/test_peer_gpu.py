@@ -137,11 +137,18 @@ def test_a_wait_for_a_rank_that_never_signals_gives_up_with_an_error_code():
         top = trs[0].L - 1
         trs[0].peer_backward_layer(x[:128], top)
         trs[0].peer_push(top)
+        torch.cuda.synchronize()
+        before = [t.clone() for t in (trs[0].params, trs[1].params, trs[0].m, trs[0].v, trs[0].adv)]
         trs[0].peer_update(top)               # rank 1 never pushed: the wait for its flag runs out
         with pytest.raises(TensotronGemmError) as e:
             trs[0].rt.Check()
         assert e.value.status == 5
         trs[0].rt.Check()                     # the status word was cleared; the context is still usable
+        # the step that timed out touched nothing: no sum over a slot that never arrived, no Adam,
+        # no store into any rank's parameters, no advance of the bias corrections
+        after = (trs[0].params, trs[1].params, trs[0].m, trs[0].v, trs[0].adv)
+        for b, a in zip(before, after):
+            assert torch.equal(b, a)
     finally:
         for t in trs:
             t.close()

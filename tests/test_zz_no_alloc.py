@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from tensotron_b200 import runtime
 
 pytestmark = pytest.mark.gpu
@@ -34,6 +35,10 @@ def test_static_cross_entropy_matches_handle_entry_twice(rt):
         assert torch.equal(d_new, d_ref)
         assert torch.equal(l_new, l_ref)
         assert abs(l_new.item() - l_ref.item()) <= 1e-5 * max(1.0, abs(l_ref.item()))
+        # and against the CPU oracle, like the handle-based entry's own parity test
+        lo, do = oracle.cross_entropy(x.cpu().numpy(), y.cpu().numpy())
+        assert abs(l_new.item() - lo) <= 1e-5 * max(1.0, abs(lo))
+        np.testing.assert_allclose(d_new.cpu().numpy(), do, atol=1e-9, rtol=2e-5)
 
 
 def test_static_cross_entropy_refuses_oversize_and_bad_arguments(rt):

@@ -27,9 +27,9 @@ N_TOTAL = int(os.environ.get("TT_BENCH_N", "16384"))
 METRIC = "sgemm_fp32_tflops"
 UNIT = "TFLOP/s"
 
-# DRAM bytes (read + write) per launch of sgemm_simt_kernel from ncu, keyed by problem edge.
-# 8192 is captured (profiles/sgemm_simt_kernel_nn_8192_dram_traffic.md); 16384 is that capture
-# scaled (reads x 8, writes x 4), because a 3 GB / 157 ms launch is too large to capture.
+# DRAM bytes (read + write) per launch of sgemm_simt_kernel from one ncu capture, keyed by problem
+# edge.  8192 is captured; 16384 is that capture scaled (reads x 8, writes x 4), because a
+# 3 GB / 157 ms launch is too large to capture.
 NCU_TRAFFIC_BYTES = {8192: 3366821376 + 254345472, 16384: 8 * 3366821376 + 4 * 254345472}
 
 
@@ -337,6 +337,90 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
     return res
 
 
+def cublas_ms(a, b, M, N, K, lay, mode, iters):
+    """Comparator, never on the product path: the same product through torch.matmul (cuBLAS),
+    strict FP32 (allow_tf32 off) for math mode 0, TF32 math otherwise.  a / b are flat operands in
+    the storage LAYOUT names."""
+    import torch
+    a2 = a.view(M, K) if lay[0] == "N" else a.view(K, M).t()
+    b2 = b.view(K, N) if lay[1] == "N" else b.view(N, K).t()
+    out = torch.empty(M, N, device=a.device)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = mode != 0
+    try:
+        return time_calls(lambda: torch.matmul(a2, b2, out=out), iters)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def run_one(spec):
+    """--one MxNxK LAYOUT VARIANT MODE ITERS [graph] [cublas]: times one GEMM shape through the C-ABI
+    library (the command the ncu captures summarised under profiles/ run).  LAYOUT is NN / NT /
+    TN (N = the operand is stored row-major as given, T = stored transposed and read through
+    swapped strides); VARIANT as in tt_set_variant (0 = automatic); MODE is the math mode
+    (0 strict FP32, 3 TF32, 4 3xTF32).  With the trailing word `graph` the ITERS launches are
+    also captured into one CUDA graph and replayed: device time without per-call host cost."""
+    import torch
+
+    from tensotron_b200.runtime import TensorRuntime
+    M, N, K = (int(x) for x in spec[0].split("x"))
+    lay, variant, mode, iters = spec[1], int(spec[2]), int(spec[3]), int(spec[4])
+    rt = TensorRuntime(0, 2048 << 20)
+    rt.SetCuBlasMathMode(mode)
+    rt.SetVariant(variant)
+    a = torch.rand(M * K, device="cuda") * 2 - 1
+    b = torch.rand(K * N, device="cuda") * 2 - 1
+    c = torch.empty(M, N, device="cuda")
+    aMs, aKs = (K, 1) if lay[0] == "N" else (1, M)
+    bKs, bNs = (N, 1) if lay[1] == "N" else (1, K)
+    call = lambda: rt.LaunchMatMul(a, b, c, M, N, K, aMs, aKs, bKs, bNs)
+    ms = time_calls(call, iters)
+    rt.Check()
+    print("ok %dx%dx%d %s v%d m%d: %.4f ms %.2f TF/s" % (M, N, K, lay, variant, mode, ms, 2.0 * M * N * K / ms / 1e9))
+    if "cublas" in spec[5:]:
+        # comparator only: the library GEMM (cuBLAS through torch.matmul) on the same operands
+        ms_lib = cublas_ms(a, b, M, N, K, lay, mode, iters)
+        print("   cuBLAS (torch.matmul, allow_tf32=%s): %.4f ms %.2f TF/s  -> ours / cuBLAS = %.3f"
+              % (mode != 0, ms_lib, 2.0 * M * N * K / ms_lib / 1e9, ms_lib / ms))
+    if "graph" in spec[5:]:
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            call()
+        host_us = (time.perf_counter() - t0) / iters * 1e6
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                call()
+        us = time_calls(g.replay, 5, warmup=1) / iters * 1e3
+        print("   graph replay: %.2f us per launch (%.2f TF/s); host call cost %.2f us"
+              % (us, 2.0 * M * N * K / us / 1e6, host_us))
+
+
+def run_one_bmm(spec):
+    """--one-bmm MODE ITERS [transposed_b]: times benchmark config 3, A [32,1,384,256] x
+    B [1,16,256,192] -> [32,16,384,192], as one LaunchMatMulBatched call.  With `transposed_b` B is
+    stored [1,16,192,256] and read through bKs = 1, bNs = 256."""
+    import torch
+
+    from tensotron_b200 import runtime
+    from tensotron_b200.runtime import TensorRuntime
+    mode, iters = int(spec[0]), int(spec[1])
+    tb = len(spec) > 2 and spec[2] == "transposed_b"
+    rt = TensorRuntime(0, 1 << 30)
+    rt.SetCuBlasMathMode(mode)
+    a = torch.rand((32, 1, 384, 256), device="cuda") * 2 - 1
+    b = torch.rand((1, 16, 192, 256) if tb else (1, 16, 256, 192), device="cuda") * 2 - 1
+    c = torch.empty((32, 16, 384, 192), device="cuda")
+    dims, aBs, bBs = runtime.broadcast_batch([32, 1], [98304, 98304], [1, 16], [786432, 49152])
+    bKs, bNs = (1, 256) if tb else (192, 1)
+    ms = time_calls(lambda: rt.LaunchMatMulBatched(a, b, c, 512, 384, 192, 256, 256, 1, bKs, bNs, dims, aBs, bBs), iters)
+    rt.Check()
+    nbytes = 4.0 * (a.numel() + b.numel() + c.numel())
+    print("ok bmm config 3 m%d%s: %.1f us %.2f TF/s %.0f GB/s of algorithmic bytes" % (
+        mode, " (B transposed)" if tb else "", ms * 1e3, 512 * 2.0 * 384 * 192 * 256 / ms / 1e9, nbytes / ms / 1e6))
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
     if rank != 0:
@@ -365,7 +449,13 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--one", nargs="+", metavar="ARG", help="MxNxK LAYOUT VARIANT MODE ITERS [graph]: time one GEMM shape and exit")
+    ap.add_argument("--one-bmm", nargs="+", metavar="ARG", help="MODE ITERS [transposed_b]: time benchmark config 3 and exit")
     args = ap.parse_args()
+    if args.one:
+        return run_one(args.one)
+    if args.one_bmm:
+        return run_one_bmm(args.one_bmm)
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     rank = env_int("RANK", 0)

@@ -127,6 +127,20 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
 TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
                              float* dlogits, float* loss, int rows, int classes, float scale);
 
+/* MseLoss (mean reduction) forward + backward in one pass
+ * (src/Tensotron/TensorOps.Losses.cs:29-61): *loss = sum((input - target)^2) / count and
+ * dinput = (2 / count) * (input - target); sums in a fixed two-level order.  `loss` and
+ * `dinput` may each be NULL.  Needs 8 KiB of the handle workspace. */
+TT_API int tt_mse_loss(tt_handle_t h, void* stream, const float* input, const float* target, float* dinput,
+                       float* loss, long long count);
+
+/* GradUtils.ClipGradNorm over one flat gradient span (src/Tensotron/Optimizers.cs:383-422):
+ * norm = sqrt(sum g^2) (fixed-order sum), every g scaled by clamp(max_norm / (norm + eps), 0, 1)
+ * unconditionally; *norm_out (device float, optional) receives the pre-clip norm, so nothing
+ * synchronises.  Needs 8 KiB of the handle workspace. */
+TT_API int tt_clip_grad_norm(tt_handle_t h, void* stream, float* grads, long long n, float max_norm, float eps,
+                             float* norm_out);
+
 /* Same result as tt_softmax_cross_entropy, for callers that may not allocate device
  * memory.  No counterpart in the reference: there the per-row losses live in tensors from
  * its own allocator.  It takes no handle (tt_create allocates) and keeps the per-row losses
@@ -146,6 +160,40 @@ TT_API int tt_softmax_cross_entropy_static(void* stream, const float* logits, co
 TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, float* m, float* v,
                  float* adv, long long n, float beta1, float beta2, float lr, float eps,
                  float coupled_wd, float decoupled_factor, int advance);
+
+/* The whole training step of a small MLP -- forward, loss, backward, gradient-norm clip, Adam --
+ * as ONE launch (a thread-block cluster; everything stays in shared memory).  It replaces the
+ * op-by-op step the reference captures for its control / PPO-sized networks
+ * (examples/Tensotron.Examples/BenchExample.cs:140-193: Sequential(Linear, Tanh, Linear, Tanh,
+ * Linear) + MseLoss + ZeroGrad + Backward + ClipGradNorm + Adam.Step; nets of
+ * showcase/Tensotron.Showcase/Rl/ActorCritic.cs:21-32), which is launch-bound there.
+ *   net      n_layers Linear layers (1..TT_MLP_MAX_LAYERS) of widths dims[0] -> ... -> dims[n_layers],
+ *            every width 1..64; `act` after every layer but the last; loss TT_LOSS_MSE (mean over
+ *            batch x outputs, src/Tensotron/TensorOps.Losses.cs:29-61; target = float (batch, out))
+ *            or TT_LOSS_CE (softmax cross-entropy, mean over the batch; target = int32 labels)
+ *   params, m, v   flat buffers, layer by layer: W_l (out, in) row-major, then b_l, each layer padded
+ *            to a multiple of 4 floats (16-byte aligned bases)
+ *   adv      [t, 1/(1-b1^t), 1/(1-b2^t)] as in tt_adam_step; always advanced on the device
+ *   grads_out  optional: receives the (clipped) gradients in the flat layout
+ *   loss_out   optional: device float, the loss before the update
+ *   max_grad_norm > 0: ClipGradNorm (src/Tensotron/Optimizers.cs:394-416): every gradient is
+ *            scaled by clamp(max_grad_norm / (norm + clip_eps), 0, 1); <= 0: no clipping
+ * batch up to 1024 rows.  All sums run in a fixed order that depends on the batch size only, so
+ * results are bit-stable from run to run.  TT_ERR_UNSUPPORTED when the network or the batch does
+ * not fit (the caller then runs the step layer by layer with the entries above). */
+#define TT_MLP_MAX_LAYERS 4
+#define TT_LOSS_MSE 0
+#define TT_LOSS_CE 1
+typedef struct tt_mlp_desc {
+    int n_layers;
+    int dims[TT_MLP_MAX_LAYERS + 1];
+    int act;   /* TT_ACT_* */
+    int loss;  /* TT_LOSS_* */
+} tt_mlp_desc;
+TT_API int tt_mlp_train_step(tt_handle_t h, void* stream, const tt_mlp_desc* net, float* params, float* m,
+                             float* v, float* adv, float* grads_out, const float* x, const void* target,
+                             float* loss_out, int batch, float lr, float beta1, float beta2, float eps,
+                             float max_grad_norm, float clip_eps);
 
 /* target[i] += source[i]  (Kernels.AddInto, src/Tensotron/Kernels.cs:111-114). */
 TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* source, long long n);
@@ -167,6 +215,8 @@ typedef struct tt_stats {
     long long splitk;          /* calls that used the split-K workspace                   */
     long long skinny;          /* calls served by the tiny-dimension streaming kernels    */
     long long workspace_bytes; /* size of the handle workspace                            */
+    long long tensor_map_hits;   /* TMA descriptors served from the calling thread's cache  */
+    long long tensor_map_misses; /* TMA descriptors encoded (cuTensorMapEncodeTiled)        */
 } tt_stats;
 TT_API int tt_get_stats(tt_handle_t h, tt_stats* out);
 TT_API int tt_reset_stats(tt_handle_t h);

@@ -154,6 +154,34 @@ def cross_entropy(logits, labels, scale=None):
     return float(loss), d.reshape(rows, classes)
 
 
+def mse_loss(pred, target):
+    """MseLoss, mean reduction (src/Tensotron/TensorOps.Losses.cs:29-61): per = (in - tgt)^2,
+    loss = Sum(per) * (1 / count); backward with upstream gradient 1: (2 / count) * (in - tgt)."""
+    pred = np.ascontiguousarray(pred, dtype=np.float32)
+    target = np.ascontiguousarray(target, dtype=np.float32)
+    diff = pred - target
+    count = diff.size
+    loss = np.float32(np.sum(diff * diff, dtype=np.float32) * np.float32(1.0 / count))
+    return float(loss), (np.float32(2.0 / count) * diff).astype(np.float32)
+
+
+def clip_grad_norm(grads, max_norm, eps=1e-6):
+    """GradUtils.ClipGradNorm (src/Tensotron/Optimizers.cs:394-422), in place on a list of float32
+    arrays: sumSq = sum over tensors of Sum(Square(g)); total = sqrt(sumSq);
+    coef = clamp(maxNorm / (total + eps), 0, 1); every g *= coef (unconditionally).  Returns total."""
+    sum_sq = None
+    for g in grads:
+        s = np.sum(np.square(g, dtype=np.float32), dtype=np.float32)
+        sum_sq = s if sum_sq is None else np.float32(sum_sq + s)
+    if sum_sq is None:
+        return 0.0
+    total = np.float32(np.sqrt(sum_sq))
+    coef = np.float32(min(max(np.float32(max_norm) / (total + np.float32(eps)), np.float32(0.0)), np.float32(1.0)))
+    for g in grads:
+        g *= coef
+    return float(total)
+
+
 def adam_step(p, g, m, v, adv, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.0):
     """In place on float32 numpy arrays (all contiguous); adv = [t, ibc1, ibc2]."""
     lib().oracle_adam_step(_p(p.reshape(-1)), _p(_flat(g)), _p(m.reshape(-1)), _p(v.reshape(-1)),
@@ -164,7 +192,12 @@ class MlpOracle:
     """The reference's op sequence for a Sequential of Linear+ReLU layers with a
     final Linear, CrossEntropy(mean) and Adam: one training step on the CPU."""
 
-    def __init__(self, weights, biases, lr=1e-3):
+    def __init__(self, weights, biases, lr=1e-3, act=1, loss="ce", max_grad_norm=0.0, clip_eps=1e-6):
+        """act: 1 ReLU / 2 Tanh between the layers; loss "ce" (int labels) or "mse" (float
+        target, the reference's captured step: examples/Tensotron.Examples/BenchExample.cs:163-176);
+        max_grad_norm > 0: ClipGradNorm before the Adam step."""
+        self.act, self.loss_kind = act, loss
+        self.max_grad_norm, self.clip_eps = max_grad_norm, clip_eps
         self.w = [np.array(w, dtype=np.float32, copy=True) for w in weights]
         self.b = [np.array(b, dtype=np.float32, copy=True) for b in biases]
         self.lr = lr
@@ -175,18 +208,19 @@ class MlpOracle:
         L = len(self.w)
         acts, zs = [np.ascontiguousarray(x, dtype=np.float32)], []
         for i in range(L):
-            z, y = linear_fwd(acts[-1], self.w[i], self.b[i], 1 if i < L - 1 else 0)
+            z, y = linear_fwd(acts[-1], self.w[i], self.b[i], self.act if i < L - 1 else 0)
             zs.append(z)
             acts.append(y)
-        loss, g = cross_entropy(acts[-1], labels)
+        loss, g = cross_entropy(acts[-1], labels) if self.loss_kind == "ce" else mse_loss(acts[-1], labels)
         dws, dbs, gs = [None] * L, [None] * L, [None] * L
         for i in reversed(range(L)):
             dx, dw, db, gm = linear_bwd(acts[i], self.w[i], zs[i], acts[i + 1], g,
-                                        1 if i < L - 1 else 0, need_dx=i > 0)
+                                        self.act if i < L - 1 else 0, need_dx=i > 0)
             dws[i], dbs[i], gs[i] = dw, db, gm
             g = dx
         self.grads = dws + dbs
         self.acts, self.gs = acts, gs      # layer inputs and masked upstream gradients, for error bounds
+        self.grad_norm = clip_grad_norm(self.grads, self.max_grad_norm, self.clip_eps) if self.max_grad_norm > 0 else None
         if apply_update:
             for t, gr, (m, v, adv) in zip(self.w + self.b, self.grads, self.state):
                 adam_step(t, gr, m, v, adv, lr=self.lr)

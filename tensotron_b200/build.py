@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtensotron_gemm.so")
-SOURCES = ["api.cu", "tensor_map.cu", "tf32_gemm.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "tensor_map.cu", "tf32_gemm.cu", "static_scratch.cu", "mlp_step.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -37,17 +37,12 @@ def _newest_dep():
     return t
 
 
-def build(force=False, verbose=False, defines=(), out=None):
-    """defines / out: build an experimental variant (extra -D flags) to another file."""
-    global LIB, OBJ
-    if out:
-        LIB = out
-        OBJ = out + ".build"
+def build(force=False, verbose=False):
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
-    extra = (["-Xptxas", "-v"] if verbose else []) + ["-D" + d for d in defines]
+    extra = ["-Xptxas", "-v"] if verbose else []
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

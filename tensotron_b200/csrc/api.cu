@@ -13,6 +13,7 @@
 #include "elementwise.cuh"
 #include "gemm_common.h"
 #include "gemm_generic.cuh"
+#include "mlp_step.h"
 #include "peer.cuh"
 #include "sgemm_simt.cuh"
 #include "skinny.cuh"
@@ -31,6 +32,7 @@ struct tt_handle_s {
     size_t workspace_bytes;
     unsigned int* status;  // device status word
     tt_stats stats;
+    long long map_hits0, map_misses0;   // descriptor-cache totals at the last tt_reset_stats
     char err[256];
 };
 
@@ -582,6 +584,7 @@ cudaError_t init_kernels()
     if (e != cudaSuccess) return e;
     e = init_simt_tm<16>();
     if (e != cudaSuccess) return e;
+    if (mlp_step::init_device() != 0) return cudaErrorUnknown;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
 
@@ -668,7 +671,6 @@ int linear_bwd_impl(tt_handle_t h, cudaStream_t st, const float* x, const float*
         return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
     TT_BIND(h);
     int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
 
     const float* g = dy;
@@ -920,8 +922,6 @@ TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* lo
     if (!h) return TT_ERR_INVALID_ARG;
     if (rows < 0 || classes <= 0 || !logits || !labels) return fail(h, TT_ERR_INVALID_ARG, "bad cross-entropy arguments");
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     if (rows == 0) return TT_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -941,6 +941,55 @@ TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* lo
     return TT_OK;
 }
 
+TT_API int tt_mse_loss(tt_handle_t h, void* stream, const float* input, const float* target, float* dinput,
+                       float* loss, long long count)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (count < 0 || (count > 0 && (!input || !target))) return fail(h, TT_ERR_INVALID_ARG, "bad MSE arguments");
+    TT_BIND(h);
+    h->stats.calls++;
+    if (count == 0) return TT_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int blocks = ew::reduce_blocks(count);
+    if (sizeof(float) * 1024 > h->workspace_bytes) return fail(h, TT_ERR_WORKSPACE, "workspace too small for the loss");
+    float* partial = reinterpret_cast<float*>(h->workspace);
+    ew::reduce_partial_kernel<0><<<blocks, 256, 0, st>>>(input, target, dinput, partial, count,
+                                                        2.f / static_cast<float>(count));
+    h->stats.launches++;
+    if (loss) {
+        ew::sum_fixed_kernel<<<1, 1024, 0, st>>>(partial, loss, blocks, 1.f / static_cast<float>(count));
+        h->stats.launches++;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "MSE launch");
+    return TT_OK;
+}
+
+TT_API int tt_clip_grad_norm(tt_handle_t h, void* stream, float* grads, long long n, float max_norm, float eps,
+                             float* norm_out)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (n < 0 || (n > 0 && !grads)) return fail(h, TT_ERR_INVALID_ARG, "bad clip arguments");
+    TT_BIND(h);
+    h->stats.calls++;
+    if (n == 0) return TT_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int blocks = ew::reduce_blocks(n);
+    if (sizeof(float) * 1028 > h->workspace_bytes) return fail(h, TT_ERR_WORKSPACE, "workspace too small for the clip");
+    float* partial = reinterpret_cast<float*>(h->workspace);
+    float* sumsq = partial + 1024;
+    ew::reduce_partial_kernel<1><<<blocks, 256, 0, st>>>(grads, nullptr, nullptr, partial, n, 0.f);
+    ew::sum_fixed_kernel<<<1, 1024, 0, st>>>(partial, sumsq, blocks, 1.f);
+    long long sblocks = (n + 255) / 256;
+    const long long cap = static_cast<long long>(h->num_sms) * 16;
+    if (sblocks > cap) sblocks = cap;
+    ew::clip_scale_kernel<<<static_cast<int>(sblocks), 256, 0, st>>>(grads, sumsq, n, max_norm, eps, norm_out);
+    h->stats.launches += 3;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "clip launch");
+    return TT_OK;
+}
+
 TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, float* m, float* v,
                  float* adv, long long n, float beta1, float beta2, float lr, float eps,
                  float coupled_wd, float decoupled_factor, int advance)
@@ -948,8 +997,6 @@ TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, f
     if (!h) return TT_ERR_INVALID_ARG;
     if (n < 0 || !adv || (n > 0 && (!p || !g || !m || !v))) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (advance) {
@@ -971,13 +1018,34 @@ TT_API int tt_adam_step(tt_handle_t h, void* stream, float* p, const float* g, f
     return TT_OK;
 }
 
+TT_API int tt_mlp_train_step(tt_handle_t h, void* stream, const tt_mlp_desc* net, float* params, float* m,
+                             float* v, float* adv, float* grads_out, const float* x, const void* target,
+                             float* loss_out, int batch, float lr, float beta1, float beta2, float eps,
+                             float max_grad_norm, float clip_eps)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (!net || !params || !m || !v || !adv || !x || !target || batch < 1)
+        return fail(h, TT_ERR_INVALID_ARG, "bad MLP step arguments");
+    if (net->act < TT_ACT_NONE || net->act > TT_ACT_TANH || (net->loss != TT_LOSS_MSE && net->loss != TT_LOSS_CE))
+        return fail(h, TT_ERR_INVALID_ARG, "unknown activation or loss");
+    if (!aligned16(params) || !aligned16(m) || !aligned16(v) || (grads_out && !aligned16(grads_out)))
+        return fail(h, TT_ERR_INVALID_ARG, "flat parameter buffers must be 16-byte aligned");
+    TT_BIND(h);
+    h->stats.calls++;
+    int ctas = 0;
+    const int rc = mlp_step::launch(static_cast<cudaStream_t>(stream), net, params, m, v, adv, grads_out, x, target,
+                                    loss_out, h->status, batch, lr, beta1, beta2, eps, max_grad_norm, clip_eps, 1, &ctas);
+    if (rc == TT_ERR_UNSUPPORTED) return fail(h, rc, "network or batch outside what the one-launch MLP step holds");
+    if (rc != TT_OK) return fail(h, rc, "MLP step launch failed");
+    h->stats.launches++;
+    return TT_OK;
+}
+
 TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* source, long long n)
 {
     if (!h) return TT_ERR_INVALID_ARG;
     if (n < 0 || (n > 0 && (!target || !source))) return fail(h, TT_ERR_INVALID_ARG, "bad AddInto arguments");
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     if (n == 0) return TT_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1017,6 +1085,12 @@ TT_API int tt_get_stats(tt_handle_t h, tt_stats* out)
 {
     if (!h || !out) return TT_ERR_INVALID_ARG;
     *out = h->stats;
+    // the descriptor cache belongs to the calling thread, not to the handle: totals since the
+    // thread's first call minus what tt_reset_stats recorded
+    unsigned long long hits = 0, misses = 0;
+    tensor_map_cache_stats(&hits, &misses);
+    out->tensor_map_hits = static_cast<long long>(hits) - h->map_hits0;
+    out->tensor_map_misses = static_cast<long long>(misses) - h->map_misses0;
     return TT_OK;
 }
 
@@ -1026,6 +1100,10 @@ TT_API int tt_reset_stats(tt_handle_t h)
     const long long ws = h->stats.workspace_bytes;
     memset(&h->stats, 0, sizeof(h->stats));
     h->stats.workspace_bytes = ws;
+    unsigned long long hits = 0, misses = 0;
+    tensor_map_cache_stats(&hits, &misses);
+    h->map_hits0 = static_cast<long long>(hits);
+    h->map_misses0 = static_cast<long long>(misses);
     return TT_OK;
 }
 
@@ -1033,8 +1111,6 @@ TT_API int tt_check(tt_handle_t h, void* stream)
 {
     if (!h) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(h, e, "stream synchronize");
@@ -1074,8 +1150,6 @@ TT_API int tt_peer_alloc(tt_handle_t h, size_t bytes, void** out_ptr)
 {
     if (!h || !out_ptr || bytes == 0) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer allocation");
@@ -1089,8 +1163,6 @@ TT_API int tt_peer_free(tt_handle_t h, void* ptr)
 {
     if (!h) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     const cudaError_t e = cudaFree(ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "peer buffer free");
     return TT_OK;
@@ -1100,8 +1172,6 @@ TT_API int tt_peer_export(tt_handle_t h, void* ptr, unsigned char* handle_out)
 {
     if (!h || !ptr || !handle_out) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     cudaIpcMemHandle_t hd;
     const cudaError_t e = cudaIpcGetMemHandle(&hd, ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcGetMemHandle");
@@ -1113,8 +1183,6 @@ TT_API int tt_peer_open(tt_handle_t h, const unsigned char* handle, void** out_p
 {
     if (!h || !handle || !out_ptr) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     cudaIpcMemHandle_t hd;
     memcpy(&hd, handle, sizeof(hd));
     void* p = nullptr;
@@ -1128,8 +1196,6 @@ TT_API int tt_peer_close(tt_handle_t h, void* ptr)
 {
     if (!h || !ptr) return TT_ERR_INVALID_ARG;
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     const cudaError_t e = cudaIpcCloseMemHandle(ptr);
     if (e != cudaSuccess) return cuda_fail(h, e, "cudaIpcCloseMemHandle");
     return TT_OK;
@@ -1247,7 +1313,6 @@ TT_API int tt_peer_push(tt_handle_t h, void* stream, tt_peer_group_t g, int chan
     if (channel < 0 || channel >= peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad exchange channel");
     TT_BIND(h);
     int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     peer::SegList segs;
@@ -1289,7 +1354,6 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     if (!m || !v || !adv || !aligned16(m) || !aligned16(v)) return fail(h, TT_ERR_INVALID_ARG, "bad Adam arguments");
     TT_BIND(h);
     int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     peer::SegList owned, repl;
@@ -1322,8 +1386,6 @@ TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g, int n_ch
     if (!h || !g) return TT_ERR_INVALID_ARG;
     if (n_channels < 1 || n_channels > peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad channel count");
     TT_BIND(h);
-    int rc = TT_OK;
-    (void)rc;
     h->stats.calls++;
     peer::wait_kernel<<<1, 32 * n_channels, 0, static_cast<cudaStream_t>(stream)>>>(
         g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, h->status,

@@ -162,6 +162,62 @@ sum_fixed_kernel(const float* __restrict__ v, float* __restrict__ out, int n, fl
     if (threadIdx.x == 0) *out = red[0] * scale;
 }
 
+// Fixed-order two-level sums for the losses and the gradient norm.  Level 1: block b adds the
+// contiguous chunk [b * chunk, (b + 1) * chunk) -- each thread a strided slice in ascending order,
+// then a shared-memory tree of fixed shape -- and writes partial[b]; the number of blocks is a
+// function of n alone (reduce_blocks), never of the SM count.  Level 2: sum_fixed_kernel over the
+// partials.  MODE 0: sum of (a[i] - b[i])^2, and d[i] = dscale * (a[i] - b[i]) when d is not
+// null (MseLoss forward + backward, src/Tensotron/TensorOps.Losses.cs:29-61).  MODE 1: sum of
+// a[i]^2 (ClipGradNorm's sum of squares, src/Tensotron/Optimizers.cs:399-406).
+constexpr int REDUCE_CHUNK = 4096;
+static inline int reduce_blocks(long long n)
+{
+    long long b = (n + REDUCE_CHUNK - 1) / REDUCE_CHUNK;
+    return static_cast<int>(b < 1 ? 1 : (b > 1024 ? 1024 : b));
+}
+
+template <int MODE>
+static __global__ void __launch_bounds__(256)
+reduce_partial_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
+                      float* __restrict__ partial, long long n, float dscale)
+{
+    __shared__ float red[256];
+    const long long per = (n + gridDim.x - 1) / gridDim.x;
+    const long long lo = per * blockIdx.x;
+    const long long hi = lo + per < n ? lo + per : n;
+    float t = 0.f;
+    for (long long i = lo + threadIdx.x; i < hi; i += 256) {
+        if (MODE == 0) {
+            const float diff = a[i] - b[i];
+            t += diff * diff;
+            if (d) d[i] = dscale * diff;
+        } else {
+            t += a[i] * a[i];
+        }
+    }
+    red[threadIdx.x] = t;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = red[0];
+}
+
+// g[i] *= clamp(max_norm / (sqrt(*sumsq) + eps), 0, 1); *norm_out = sqrt(*sumsq) when not null
+// (ClipGradNorm, src/Tensotron/Optimizers.cs:409-416: applied unconditionally, so nothing
+// branches on the host).
+static __global__ void __launch_bounds__(256)
+clip_scale_kernel(float* __restrict__ g, const float* __restrict__ sumsq, long long n, float max_norm, float eps,
+                  float* __restrict__ norm_out)
+{
+    const float total = sqrtf(*sumsq);
+    const float coef = fminf(fmaxf(max_norm / (total + eps), 0.f), 1.f);
+    if (norm_out && blockIdx.x == 0 && threadIdx.x == 0) *norm_out = total;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) g[i] *= coef;
+}
+
 // adv = [t, 1/(1-b1^t), 1/(1-b2^t)]; one thread.
 static __global__ void adam_advance_kernel(float* adv, float b1, float b2)
 {

@@ -1,21 +1,26 @@
 // Strict-FP32 SGEMM for sm_100a: SIMT FMA tiles fed by TMA.
 //
-// One persistent CTA per SM (8 warps) walks a grouped raster of (16*TM)x128 output
-// tiles, TM = 16 (256x128 tile, 16x8 accumulators per thread) or TM = 8 (128x128, 8x8).
-// Thread 0 streams (16*TM)x32 (A) and 32x128 (B) float tiles into a shared-memory ring
-// with TMA, a few k-steps ahead of the consumers; all warps read the tiles with 128-bit
-// shared loads and issue packed two-wide FP32 FMAs (fma.rn.f32x2).  Stages are handed
-// over with mbarriers (full: TMA transaction bytes; empty: one arrival per warp), and
-// the ring keeps filling across tile boundaries while the previous tile's epilogue
-// stores.
+// One persistent CTA per SM walks a grouped raster of (16*TM)x128 output tiles, TM = 16
+// (256x128 tile, 16x8 accumulators per thread) or TM = 8 (128x128, 8x8).  The CTA is three
+// warpgroups: two of consumers (8 warps) and one producer warpgroup, of which a single thread
+// works.  The producer streams (16*TM)x32 (A) and 32x128 (B) float tiles into a shared-memory
+// ring with TMA, as far ahead of the consumers as the ring allows; the consumer warps read the
+// tiles with 128-bit shared loads and issue packed two-wide FP32 FMAs (fma.rn.f32x2).  Stages
+// are handed over with mbarriers (full: TMA transaction bytes; empty: one arrival per consumer
+// warp), and the ring keeps filling across tile boundaries while the previous tile's epilogue
+// stores.  The producer warpgroup gives its registers back (setmaxnreg.dec) and the consumers
+// take them (setmaxnreg.inc), so the consumers keep the 232 registers their 128 accumulators
+// plus fragments need.  (With the loads issued by thread 0 of consumer warp 0, that warp was
+// the CTA's critical path: its producer work, serialised with its own FMAs, paced the ring and
+// the other seven warps waited on the full barriers for about 4 % of their cycles.)
 //
 // Why 16x8 per thread and packed FMAs: on this SM the FP32 pipe retires 128 FMAs per
 // clock, one warp instruction per scheduler per clock, and shared memory returns
 // 128 B/clk.  With scalar FFMA every non-FMA instruction steals an FMA issue slot and an
 // 8x8 register tile needs the whole shared-memory return bandwidth.  A 16x8 tile needs
 // 75 % of it, and the two-wide FMA halves the FMA issue slots, leaving room for the
-// loads.  128 accumulators plus fragments need > 170 registers, hence exactly 8 warps
-// (2 per scheduler partition) and no separate producer warp.
+// loads.  128 accumulators plus fragments need > 170 registers, hence exactly 8 consumer
+// warps (2 per scheduler partition).
 //
 // Operand layouts.  The main loop wants both operands "MN-major" in shared memory:
 // [32 k][rows] with the M (or N) index contiguous, so that a float4 holds 4 adjacent
@@ -38,17 +43,19 @@ namespace tt {
 namespace simt {
 
 constexpr int BN = 128, BK = 32;
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
+constexpr int WARPS = 8;                        // consumer warps (two warpgroups)
+constexpr int CONSUMER_THREADS = WARPS * 32;
+constexpr int THREADS = CONSUMER_THREADS + 128; // + the producer warpgroup
+constexpr int PRODUCER_REGS = 24, CONSUMER_REGS = 240;   // 128 x 24 + 256 x 240 <= 64 K registers
 constexpr int RASTER_GROUP = 8;
-#ifndef TT_G_UNROLL
-#define TT_G_UNROLL 4
-#endif
-#ifndef TT_KG
-#define TT_KG 4
-#endif
-constexpr int KG = TT_KG;              // k-steps whose fragments are loaded together
-constexpr int G_UNROLL = TT_G_UNROLL;  // k groups unrolled in the main loop; bounds code size
+constexpr int KG = 4;        // k-steps whose fragments are loaded together
+constexpr int G_UNROLL = 4;  // k groups unrolled in the main loop; bounds code size
+
+// CTA barrier over the consumer warps only (the producer warpgroup never joins it).
+__device__ __forceinline__ void consumer_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
+}
 
 template <int TM, bool A_KMAJ, bool B_KMAJ>
 struct Cfg {
@@ -67,9 +74,6 @@ struct Cfg {
     static constexpr int BUDGET = 227 * 1024 - 1024 /*align slack*/ - 512 /*barriers, cursor*/;
     static constexpr int FIT = (BUDGET - 2 * (TA_BYTES + TB_BYTES)) / STAGE_BYTES;
     static constexpr int STAGES = FIT > 4 ? 4 : FIT;
-    // How many k-tiles ahead of the consumers the producer runs.  A stage whose tiles
-    // are all transposed is released one k-tile earlier than one the main loop reads.
-    static constexpr int DIST = ALL_T ? STAGES : STAGES - 1;
     static constexpr int OFF_TA = STAGES * STAGE_BYTES;
     static constexpr int OFF_TB = OFF_TA + 2 * TA_BYTES;
     static constexpr int OFF_BAR = (OFF_TB + 2 * TB_BYTES + 127) & ~127;
@@ -101,59 +105,30 @@ __device__ __forceinline__ float apply_act(float v, int act)
     return v;
 }
 
-// Cursor over this CTA's (tile, k-tile) sequence; used by the producer thread, which
-// runs DIST steps ahead of the consumers.  Lives in shared memory.
-struct LoadCursor {
-    long long w;
-    int kt, ke;   // next k-tile to load, end of this work item's k range
-    int kb, r;    // start of the k range; index along the reduced batch axis
-    int fresh;    // 1: the next load starts a new work item
-    int m0, n0;
-    int ca0, ca1, ca2, cb0, cb1, cb2;
-    uint32_t stage, use;  // stage to fill next; how many times the ring has wrapped
-    int ok;
+// Batch coordinates (TMA coordinate slots 0..2 per operand) of batch entry bidx.
+struct BatchCoords {
+    int a[3], b[3];
 };
 
-template <int BM, int MODE>
-__device__ __forceinline__ void cursor_set_tile(LoadCursor& cur, const Params& p, int tiles_per_mat, int k_tiles,
-                                                long long w_end)
+__device__ __forceinline__ BatchCoords batch_coords(const BatchDesc& batch, int bidx)
 {
-    long long unit;
-    if (MODE == 2) {
-        unit = cur.w / k_tiles;
-        cur.kt = static_cast<int>(cur.w - unit * k_tiles);
-        const long long left = w_end - cur.w;
-        cur.ke = static_cast<int>(min(static_cast<long long>(k_tiles), cur.kt + left));
-    } else {
-        unit = cur.w / p.splits;
-        const int split = static_cast<int>(cur.w - unit * p.splits);
-        cur.kt = split * p.kps;
-        cur.ke = min(k_tiles, cur.kt + p.kps);
-    }
-    cur.kb = cur.kt;
-    cur.r = 0;
-    cur.fresh = 0;
-    const int bidx = static_cast<int>(unit / tiles_per_mat);
-    const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
-    int tm, tn;
-    raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
-    cur.m0 = tm * BM;
-    cur.n0 = tn * BN;
-    cur.ca0 = cur.ca1 = cur.ca2 = 0;
-    cur.cb0 = cur.cb1 = cur.cb2 = 0;
+    BatchCoords c;
+    c.a[0] = c.a[1] = c.a[2] = 0;
+    c.b[0] = c.b[1] = c.b[2] = 0;
     int br = bidx;
-    for (int ax = p.batch.rank - 1; ax >= 0; ax--) {
-        const int d = p.batch.dims[ax];
+    for (int ax = batch.rank - 1; ax >= 0; ax--) {
+        const int d = batch.dims[ax];
         const int bi = br % d;
         br /= d;
-        const int sa = p.batch.a_slot[ax], sb = p.batch.b_slot[ax];
-        if (sa == 0) cur.ca0 += bi * p.batch.a_mult[ax];
-        else if (sa == 1) cur.ca1 += bi * p.batch.a_mult[ax];
-        else if (sa == 2) cur.ca2 += bi * p.batch.a_mult[ax];
-        if (sb == 0) cur.cb0 += bi * p.batch.b_mult[ax];
-        else if (sb == 1) cur.cb1 += bi * p.batch.b_mult[ax];
-        else if (sb == 2) cur.cb2 += bi * p.batch.b_mult[ax];
+        const int sa = batch.a_slot[ax], sb = batch.b_slot[ax];
+        if (sa == 0) c.a[0] += bi * batch.a_mult[ax];
+        else if (sa == 1) c.a[1] += bi * batch.a_mult[ax];
+        else if (sa == 2) c.a[2] += bi * batch.a_mult[ax];
+        if (sb == 0) c.b[0] += bi * batch.b_mult[ax];
+        else if (sb == 1) c.b[1] += bi * batch.b_mult[ax];
+        else if (sb == 2) c.b[2] += bi * batch.b_mult[ax];
     }
+    return c;
 }
 
 // Transposes one K-major TMA tile ([ROWS][32 k], 128B-swizzled) into an MN-major tile
@@ -211,7 +186,6 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
     uint64_t* empty_bar = full_bar + STAGES;
     volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
-    LoadCursor& cur = *reinterpret_cast<LoadCursor*>(smem + C::OFF_BAR + 128);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -231,58 +205,71 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         *cta_abort = 0u;
         fence_mbar_init();
-        prefetch_tensormap(&map_a);
-        prefetch_tensormap(&map_b);
-        cur.w = w_begin;
-        cur.kt = 0;
-        cur.ke = 0;
-        cur.fresh = 1;
-        cur.stage = 0;
-        cur.use = 0;
-        cur.ok = 1;
     }
     __syncthreads();
 
-    // Issues the TMA loads of the cursor's (tile, k-tile) into cur.stage and advances
-    // (thread 0 only; its state lives in shared memory so it costs no registers).
-    auto produce_one = [&]() {
-        if (cur.w >= w_end || !cur.ok) return;
-        if (cur.fresh) cursor_set_tile<C::BM, MODE>(cur, p, tiles_per_mat, k_tiles, w_end);
-        const uint32_t ps = cur.stage;
-        if (cur.use > 0) {
-            // the stage was used before: wait until all warps released that use
-            if (!mbar_wait_bounded(&empty_bar[ps], (cur.use - 1) & 1u, cta_abort, p.status,
-                                   DEV_WAIT_EMPTY)) {
-                cur.ok = 0;
-                return;
-            }
-        }
-        uint8_t* sa = smem + ps * C::STAGE_BYTES;
-        uint8_t* sb = sa + C::RAW_A;
-        mbar_arrive_expect_tx(&full_bar[ps], C::STAGE_BYTES);
-        const int k0 = cur.kt * BK;
-        // the reduced batch axis has a coordinate slot of its own (or none when the operand
-        // is broadcast along it)
+    if (warp >= WARPS) {
+        // ------------------------- producer warpgroup -------------------------
+        // Walks the same (work item, reduced-axis entry, k-tile) sequence as the consumers and
+        // fills the ring as far ahead as the empty barriers allow.  One thread; its cursor
+        // lives in registers.
+        setmaxnreg_dec<PRODUCER_REGS>();
+        if (warp != WARPS || lane != 0) return;
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        uint32_t ps = 0, use = 0;   // stage to fill next; how many times the ring has wrapped
         const int sra = p.batch.red_a_slot, srb = p.batch.red_b_slot;
-        const int ca0 = cur.ca0 + (sra == 0 ? cur.r : 0), ca1 = cur.ca1 + (sra == 1 ? cur.r : 0),
-                  ca2 = cur.ca2 + (sra == 2 ? cur.r : 0);
-        const int cb0 = cur.cb0 + (srb == 0 ? cur.r : 0), cb1 = cur.cb1 + (srb == 1 ? cur.r : 0),
-                  cb2 = cur.cb2 + (srb == 2 ? cur.r : 0);
-        if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[ps], k0, cur.m0, ca0, ca1, ca2);
-        else        tma_load_5d(sa, &map_a, &full_bar[ps], cur.m0, k0, ca0, ca1, ca2);
-        if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, cur.n0, cb0, cb1, cb2);
-        else        tma_load_5d(sb, &map_b, &full_bar[ps], cur.n0, k0, cb0, cb1, cb2);
-        if (ps + 1 == STAGES) { cur.stage = 0; cur.use++; } else { cur.stage = ps + 1; }
-        if (++cur.kt == cur.ke) {
-            if (++cur.r < p.batch.red_count) cur.kt = cur.kb;   // same k range, next reduced entry
-            else { cur.fresh = 1; cur.w += (MODE == 2) ? (cur.ke - cur.kb) : static_cast<int>(gridDim.x); }
+        for (long long w = w_begin; w < w_end;) {
+            long long unit, w_next;
+            int kb, ke;
+            if (MODE == 2) {
+                unit = w / k_tiles;
+                kb = static_cast<int>(w - unit * k_tiles);
+                ke = static_cast<int>(min(static_cast<long long>(k_tiles), kb + (w_end - w)));
+                w_next = w + (ke - kb);
+            } else {
+                unit = w / p.splits;
+                const int split = static_cast<int>(w - unit * p.splits);
+                kb = split * p.kps;
+                ke = min(k_tiles, kb + p.kps);
+                w_next = w + gridDim.x;
+            }
+            const int bidx = static_cast<int>(unit / tiles_per_mat);
+            const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
+            int tm, tn;
+            raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
+            const int m0 = tm * C::BM, n0 = tn * BN;
+            const BatchCoords bc = batch_coords(p.batch, bidx);
+            for (int r = 0; r < p.batch.red_count; r++) {
+                // the reduced batch axis has a coordinate slot of its own (or none when the
+                // operand is broadcast along it)
+                const int ca0 = bc.a[0] + (sra == 0 ? r : 0), ca1 = bc.a[1] + (sra == 1 ? r : 0),
+                          ca2 = bc.a[2] + (sra == 2 ? r : 0);
+                const int cb0 = bc.b[0] + (srb == 0 ? r : 0), cb1 = bc.b[1] + (srb == 1 ? r : 0),
+                          cb2 = bc.b[2] + (srb == 2 ? r : 0);
+                for (int kt = kb; kt < ke; kt++) {
+                    if (use > 0) {
+                        // the stage was used before: wait until all warps released that use
+                        if (!mbar_wait_bounded(&empty_bar[ps], (use - 1) & 1u, cta_abort, p.status, DEV_WAIT_EMPTY))
+                            return;
+                    }
+                    uint8_t* sa = smem + ps * C::STAGE_BYTES;
+                    uint8_t* sb = sa + C::RAW_A;
+                    mbar_arrive_expect_tx(&full_bar[ps], C::STAGE_BYTES);
+                    const int k0 = kt * BK;
+                    if (A_KMAJ) tma_load_5d(sa, &map_a, &full_bar[ps], k0, m0, ca0, ca1, ca2);
+                    else        tma_load_5d(sa, &map_a, &full_bar[ps], m0, k0, ca0, ca1, ca2);
+                    if (B_KMAJ) tma_load_5d(sb, &map_b, &full_bar[ps], k0, n0, cb0, cb1, cb2);
+                    else        tma_load_5d(sb, &map_b, &full_bar[ps], n0, k0, cb0, cb1, cb2);
+                    if (++ps == STAGES) { ps = 0; use++; }
+                }
+            }
+            w = w_next;
         }
-    };
-
-    if (tid == 0) {
-#pragma unroll 1
-        for (int i = 0; i < C::DIST; i++) produce_one();
+        return;
     }
+    // ------------------------------ consumer warps ------------------------------
+    setmaxnreg_inc<CONSUMER_REGS>();
 
     // Transposes the K-major tiles of TMA stage `s` into transposed buffer `tb`.
     auto transpose_stage = [&](uint32_t s, uint32_t tb) {
@@ -303,7 +290,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (lane == 0) mbar_arrive(&empty_bar[0]);
             }
         }
-        __syncthreads();
+        consumer_sync();
         if (*cta_abort) return;
     }
 
@@ -351,10 +338,9 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
             for (int j = 0; j < 4; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
 
-#pragma unroll 1
         const int iters = (ke - kb) * p.batch.red_count;  // k-tiles x entries of the reduced axis
+#pragma unroll 1
         for (int it = 0; it < iters; it++) {
-            if (tid == 0) produce_one();
             bool ok = true;
             if (!C::HAS_T)
                 ok = mbar_wait_bounded(&full_bar[stage], phase, cta_abort, p.status, DEV_WAIT_FULL);
@@ -428,7 +414,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                     }
                 }
                 // writers of buffer tb^1 | readers of buffer tb: one barrier orders both
-                __syncthreads();
+                consumer_sync();
                 if (*cta_abort) return;  // uniform: every thread sees the flag after the barrier
                 tb ^= 1u;
             }
@@ -506,7 +492,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                         while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
                         s_hi = hi;
                     }
-                    __syncthreads();
+                    consumer_sync();
                     const int hi = s_hi;
                     for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
                         if (tid == 0) {
@@ -523,7 +509,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             }
                             p.sk_flags[cta] = 0u;   // consumed: the next launch starts from zero again
                         }
-                        __syncthreads();
+                        consumer_sync();
                         if (*cta_abort) return;
                         const float* src = p.partial + static_cast<long long>(cta) * (C::BM * BN);
     #pragma unroll
@@ -595,7 +581,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             if (MODE == 2 && partial_tile) {
                 // the partial tile is stored: fence, CTA barrier, flag (release)
                 __threadfence();
-                __syncthreads();
+                consumer_sync();
                 if (tid == 0) {
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + blockIdx.x), "r"(1u) : "memory");
                 }

@@ -1,6 +1,7 @@
 #include "tensor_map.h"
 
 #include <cudaTypedefs.h>
+#include <string.h>
 
 namespace tt {
 
@@ -38,9 +39,64 @@ bool tma_compatible(const OperandView& v)
     return true;
 }
 
+namespace {
+// Descriptor cache.  A training loop calls the same products on the same buffers step after
+// step, and one cuTensorMapEncodeTiled costs about a microsecond of host time (2 to 5 per
+// call), the same order as a kernel launch.  A descriptor is a pure function of (base, dims,
+// strides, box, swizzle) -- it does not depend on the context or on what the memory holds -- so
+// the encoded 128 bytes are kept in a small direct-mapped table per host thread, keyed by
+// exactly those inputs.
+struct MapKey {
+    const void* base;
+    uint64_t dim[5];
+    uint64_t stride[5];
+    uint32_t box[3];
+    int32_t rank;
+    int32_t swz;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapSlot {
+    bool used = false;
+    MapKey key;
+    CUtensorMap map;
+};
+constexpr int CACHE_SLOTS = 256;
+thread_local MapSlot t_cache[CACHE_SLOTS];
+thread_local unsigned long long t_hits = 0, t_misses = 0;
+
+uint64_t hash_key(const MapKey& k)
+{
+    uint64_t h = 1469598103934665603ull;   // FNV-1a over the key's words
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    for (size_t i = 0; i < sizeof(MapKey) / sizeof(uint64_t); i++) { h ^= w[i]; h *= 1099511628211ull; }
+    return h ^ (h >> 29);
+}
+static_assert(sizeof(MapKey) % sizeof(uint64_t) == 0, "key is hashed word by word");
+}  // namespace
+
+void tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses)
+{
+    if (hits) *hits = t_hits;
+    if (misses) *misses = t_misses;
+}
+
 int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uint32_t box1,
                       Swizzle swz, uint32_t box2)
 {
+    MapKey key;
+    memset(&key, 0, sizeof(key));   // padding bytes too: the key is compared and hashed as raw bytes
+    key.base = v.base;
+    key.rank = v.rank;
+    key.swz = static_cast<int32_t>(swz);
+    for (int i = 0; i < v.rank && i < 5; i++) { key.dim[i] = v.dim[i]; key.stride[i] = v.stride_elems[i]; }
+    key.box[0] = box0; key.box[1] = box1; key.box[2] = box2;
+    MapSlot& slot = t_cache[hash_key(key) % CACHE_SLOTS];
+    if (slot.used && slot.key == key) {
+        *out = slot.map;
+        t_hits++;
+        return 0;
+    }
+    t_misses++;
     PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
     if (!enc) return 999;
     cuuint64_t dims[5];
@@ -65,6 +121,11 @@ int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uin
                            : swz == Swizzle::B128_A32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                       : CU_TENSOR_MAP_SWIZZLE_NONE,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        slot.used = true;
+        slot.key = key;
+        slot.map = *out;
+    }
     return static_cast<int>(r);
 }
 

@@ -1,7 +1,8 @@
 // Host-side construction of TMA descriptors (CUtensorMap) for float32 operands.
 // The driver entry point is resolved at run time so the library does not link
-// libcuda directly.  Descriptors are built per call and passed to kernels as
-// __grid_constant__ parameters, so they are baked into captured graph nodes.
+// libcuda directly.  Descriptors are built (or fetched from a per-thread cache keyed by base,
+// dims, strides, box and swizzle) per call and passed to kernels as __grid_constant__
+// parameters, so they are baked into captured graph nodes.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -28,5 +29,8 @@ bool tma_compatible(const OperandView& v);
 // Returns cudaSuccess-like 0 on success, non-zero CUresult otherwise.
 int encode_tensor_map(CUtensorMap* out, const OperandView& v, uint32_t box0, uint32_t box1,
                       Swizzle swz, uint32_t box2 = 1);
+
+// Hits / misses of the calling thread's descriptor cache (diagnostics, tests).
+void tensor_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
 
 }  // namespace tt

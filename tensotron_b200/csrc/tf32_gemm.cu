@@ -14,6 +14,9 @@
 // MT = 1: 128x256 tiles with two accumulator buffers (the epilogue of tile i overlaps
 // the MMAs of tile i+1).  MT = 2: 256x256 tiles (two M = 128 MMAs share every B tile,
 // halving L2->SM traffic per flop) with a single accumulator set.
+// The tile WIDTH is a launch parameter (bn = 64, 128, 192 or 256: the N of the MMA instruction,
+// the rows of the B box, the columns the epilogue reads out), so that e.g. N = 192 is one
+// 192-wide tile and no MMA, operand byte or TMEM read-out is spent on padding columns.
 //
 // Operands keep their global layout: a K-major tile is one TMA box of [rows][32 k]
 // (128-byte rows, 128B swizzle, K-major UMMA descriptor); an MN-major tile is a row of
@@ -46,18 +49,26 @@ template <int MT, bool SPLIT>
 struct Cfg {
     static constexpr int BM = 128 * MT;
     static constexpr int A_BYTES = BM * BK * 4;
-    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int B_BYTES = BN * BK * 4;   // room for the widest tile; bn * BK * 4 bytes are filled
     static constexpr int PLANES = SPLIT ? 2 : 1;  // hi (+ lo)
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * PLANES;
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
     static constexpr int ACC_BUFS = MT == 1 ? 2 : 1;
+    // epilogue staging: per epilogue warp EPI_BUFS blocks of 32 rows x 32 columns (128-byte rows,
+    // the 16-byte chunks of row r stored at chunk index c ^ (r & 7), so both the row-wise writes
+    // and the 4-rows-at-a-time reads are free of bank conflicts).  Two blocks per warp where the
+    // ring can spare the room (128-row tiles, one operand plane): the TMA store of one block is
+    // still reading it while the next block is staged, so a warp keeps two stores in flight.
+    // With one block a warp's read-out is a chain of store latencies, which is what bounds
+    // short-K products (their epilogue is longer than their MMAs).
+    static constexpr int EPI_BUFS = (MT == 1 && !SPLIT) ? 2 : 1;
+    static constexpr int OUT_BLOCK_BYTES = 32 * 128;
+    static constexpr int OUT_WARP_BYTES = EPI_BUFS * OUT_BLOCK_BYTES;
+    static constexpr int OUT_BYTES = EPI_WARPS * OUT_WARP_BYTES;
+    static constexpr int BUDGET = 227 * 1024 - 1024 /*alignment slack*/ - 1024 /*barriers*/ - OUT_BYTES;
+    static constexpr int STAGES = BUDGET / STAGE_BYTES;
     static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
-    // epilogue staging: per epilogue warp 32 rows x 32 columns (128-byte rows, the 16-byte
-    // chunks of row r stored at chunk index c ^ (r & 7), so both the row-wise writes and the
-    // 4-rows-at-a-time reads are free of bank conflicts)
-    static constexpr int OUT_WARP_BYTES = 32 * 128;
     static constexpr int OFF_OUT = OFF_BAR + 1024;   // 1024-byte aligned: the blocks are TMA-store sources
-    static constexpr int SMEM_BYTES = OFF_OUT + EPI_WARPS * OUT_WARP_BYTES + 1024;
+    static constexpr int SMEM_BYTES = OFF_OUT + OUT_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory budget");
     static_assert(STAGES >= 2, "shared-memory budget");
 };
@@ -76,6 +87,8 @@ struct Params {
     // C is written with TMA stores from the staging blocks (map_c: {N, M, batch}, box 32 x 32,
     // 128-byte swizzle = the staging blocks' layout); 0: plain stores (scatter, N % 4 != 0).
     int c_tma;
+    // tile width: 64, 128, 192 or 256 columns (tiles_n = ceil(N / bn))
+    int bn;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------
@@ -166,11 +179,12 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
     return d;
 }
 
-// Instruction descriptor: D = F32, A = B = TF32, M = 128, N = BN, per-operand major-ness.
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn)
+// Instruction descriptor: D = F32, A = B = TF32, M = 128, N = n (a multiple of 16, at most 256),
+// per-operand major-ness.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n)
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
 __device__ __forceinline__ float act_apply(float v, int act)
@@ -263,14 +277,14 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (p.batch.a_slot[ax] >= 0) ca[p.batch.a_slot[ax]] += bi * p.batch.a_mult[ax];
                     if (p.batch.b_slot[ax] >= 0) cb[p.batch.b_slot[ax]] += bi * p.batch.b_mult[ax];
                 }
-                const int m0 = tc.tm * C::BM, n0 = tc.tn * BN;
+                const int m0 = tc.tm * C::BM, n0 = tc.tn * p.bn;
                 for (int kt = 0; kt < k_tiles; kt++) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, cta_abort, p.status, DEV_WAIT_EMPTY)) {
                         ok = false;
                         break;
                     }
                     uint8_t* st = smem + stage * C::STAGE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+                    mbar_arrive_expect_tx(&full_bar[stage], (C::A_BYTES + p.bn * BK * 4) * C::PLANES);
                     const int k0 = kt * BK;
 #pragma unroll
                     for (int pl = 0; pl < C::PLANES; pl++) {
@@ -292,8 +306,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         } else if (p.b_grouped) {
                             tma_load_5d(sb, mb, &full_bar[stage], 0, k0, n0 >> 5, cb[0], cb[1]);
                         } else {
-#pragma unroll
-                            for (int i = 0; i < BN / 32; i++)
+                            for (int i = 0; i < p.bn / 32; i++)
                                 tma_load_5d(sb + i * 4096, mb, &full_bar[stage], n0 + i * 32, k0, cb[0], cb[1], cb[2]);
                         }
                     }
@@ -304,7 +317,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // -------------------------------- MMA issuer --------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(!A_KMAJ, !B_KMAJ);
+            const uint32_t idesc = make_idesc(!A_KMAJ, !B_KMAJ, p.bn);
             // K-major: 16-byte-chunk swizzle, 8-row groups 1024 bytes apart.  MN-major (32-bit
             // operands): 32-byte-chunk swizzle, 4-k groups 512 bytes apart inside a box of
             // 32 columns, boxes 4096 bytes apart.
@@ -359,25 +372,32 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // --------------------------------- epilogue ---------------------------------
         const int ew = warp - 2;   // 0 .. 7
         const int q = warp & 3;    // TMEM sub-partition a warp may read: lanes 32q .. 32q+31
-        const int cbeg = (ew >> 2) * (BN / 2), cend = cbeg + BN / 2;   // this warp's half of the columns
+        const int cbeg = (ew >> 2) * (p.bn / 2), cend = cbeg + p.bn / 2;   // this warp's half of the tile's columns
         uint32_t acc = 0, acc_phase = 0;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
-        uint8_t* out_stage = smem + C::OFF_OUT + ew * C::OUT_WARP_BYTES;
+        uint8_t* const out_blocks = smem + C::OFF_OUT + ew * C::OUT_WARP_BYTES;
+        uint32_t out_buf = 0;   // staging block of the next 32 x 32 block (alternates when there are two)
         for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
             const TileCoord tc = decode_tile(w, p.shape);
             if (!mbar_wait_bounded(&acc_full[acc], acc_phase, cta_abort, p.status, DEV_WAIT_MMA)) break;
             tc_fence_after();
             float* cmat = scatter_base(p.epi, p.c, tc.tm * C::BM) + static_cast<long long>(tc.bidx) * p.shape.M * p.shape.N;
-            const int n0 = tc.tn * BN;
+            const int n0 = tc.tn * p.bn;
             // One 32 x 32 block: bias / activation, through the staging block, out with 8 lanes per
             // row.  (The TMEM load gives lane l the 32 columns of row l; stored that way one
             // instruction would touch 32 rows with 16 bytes each.  After the exchange an
             // instruction writes 4 rows x 128 contiguous bytes: full sectors for L2, full-size
             // packets when the row block belongs to another GPU.)
             const auto emit = [&](const uint32_t (&r)[32], int row0, int c0) {
-                if (p.c_tma && lane == 0) bulk_wait_group_read0();   // the previous TMA store has read the block
-                __syncwarp();   // the previous block's reads of the staging block are done
+                uint8_t* const out_stage = out_blocks + out_buf * C::OUT_BLOCK_BYTES;
+                if (C::EPI_BUFS == 2) out_buf ^= 1u;
+                // the TMA store that last used this block has read it (with two blocks: all but
+                // the most recent store)
+                if (p.c_tma && lane == 0) {
+                    if (C::EPI_BUFS == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+                }
+                __syncwarp();   // the previous reads of this staging block are done
 #pragma unroll
                 for (int v4 = 0; v4 < 8; v4++) {
                     const int col = n0 + c0 + v4 * 4;
@@ -626,6 +646,15 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     if (!plan_batch(hb, b_bs, p.batch.b_slot, p.batch.b_mult, vb)) return 3;
     if (!tma_compatible(va) || !tma_compatible(vb)) return 3;
 
+    // Tile width: 256 columns unless a narrower tile (192 or 128, 64 for N <= 64) cuts the padded
+    // width by more than 8 % (N = 192: one 192-wide tile instead of a 256-wide one that is a
+    // quarter padding).  Wide tiles move fewer operand bytes per flop, so they stay the rule.
+    int bn = 256;
+    {
+        const auto padded = [&](int w) { return static_cast<long long>((N + w - 1) / w) * w; };
+        for (int w : {192, 128, 64})
+            if (padded(w) * 108 < padded(bn) * 100) bn = w;
+    }
     // Tile height.  Measured per k-tile (32 k) and SM: about 980 clk with 128x256 tiles and
     // about 1545 clk with 256x256 tiles, which do twice the work (two MMAs share each B tile,
     // so less L2 -> SM traffic per flop).  The 128-row form has two accumulator sets, so its
@@ -637,7 +666,7 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     if (!split) {
         const double k_tiles = (K + BK - 1) / BK;
         const auto waves = [&](int bm) {
-            const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
+            const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
             return static_cast<double>((work + num_sms - 1) / num_sms);
         };
         const double mma1 = k_tiles * 980.0;
@@ -687,7 +716,7 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     for (int i = 0; i < (split ? 4 : 2); i++) {
         const bool is_a = (i % 2) == 0;
         const bool kmaj = is_a ? ak : bk;
-        const int rows_box = is_a ? bm : BN;
+        const int rows_box = is_a ? bm : bn;
         int r;
         if (kmaj) r = encode_tensor_map(&maps[i], views[i], BK, rows_box, Swizzle::B128);
         else if (is_a ? p.a_grouped : p.b_grouped)
@@ -711,7 +740,8 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
 
     p.shape.M = M; p.shape.N = N; p.shape.K = K;
     p.shape.tiles_m = (M + bm - 1) / bm;
-    p.shape.tiles_n = (N + BN - 1) / BN;
+    p.shape.tiles_n = (N + bn - 1) / bn;
+    p.bn = bn;
     p.shape.batch = batch_count;
     p.shape.work = static_cast<long long>(batch_count) * p.shape.tiles_m * p.shape.tiles_n;
     p.epi = epi;

@@ -27,7 +27,7 @@ import math
 
 import torch
 
-from .runtime import TT_MATH_FP32, TensorRuntime
+from .runtime import ACT, LOSS, TT_LOSS_CE, TT_MATH_FP32, TensorRuntime, TensotronGemmError
 
 
 def shard_rows(total, world, rank):
@@ -52,9 +52,23 @@ def layer_layout(dims):
 
 
 class MlpTrainer:
+    """act: activation between the layers ("relu" as in benchmark config 4, "tanh" as in the
+    reference's control / PPO networks); loss: "ce" (cross-entropy on int32 labels) or "mse"
+    (mean squared error against a float target, examples/Tensotron.Examples/BenchExample.cs:171);
+    max_grad_norm > 0 adds ClipGradNorm before the optimizer step (:174).  fused: True runs the
+    whole step as one launch (tt_mlp_train_step, single GPU, small networks), "auto" does so when
+    the network and the batch fit and otherwise runs it layer by layer, False never does."""
+
     def __init__(self, dims, rt=None, device=0, lr=1e-3, seed=2, process_group=None, math_mode=TT_MATH_FP32,
-                 exchange="nccl", peer_group=None):
+                 exchange="nccl", peer_group=None, act="relu", loss="ce", max_grad_norm=0.0, clip_eps=1e-6,
+                 fused=False):
         self.dims = list(dims)
+        self.act = ACT[act]
+        self.loss_kind = LOSS[loss]
+        self.max_grad_norm = float(max_grad_norm)
+        self.clip_eps = float(clip_eps)
+        self.fused = fused
+        self.last_step_fused = False
         self.L = len(dims) - 1
         self.device = device
         self.rt = rt or TensorRuntime(device)
@@ -67,6 +81,8 @@ class MlpTrainer:
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.exchange = exchange
         self.peer = None
+        if exchange == "peer" and self.max_grad_norm > 0:
+            raise ValueError("gradient clipping needs the whole gradient on one rank: use exchange='nccl'")
         if exchange == "peer":
             from .peer import CHANNELS, PeerGroup, exchange_plan, merge_segments
             self.peer = peer_group or PeerGroup(self.rt, total, process_group)
@@ -134,18 +150,35 @@ class MlpTrainer:
         L = self.L
         inp = x
         for i in range(L):
-            act = 1 if i < L - 1 else 0
+            act = self.act if i < L - 1 else 0
             rt.LaunchLinearForward(inp, self.weight(i), self.bias(i), self._acts[i], rows,
                                    self.dims[i + 1], self.dims[i], act)
             inp = self._acts[i]
-        rt.LaunchSoftmaxCrossEntropy(self._acts[L - 1], labels, self._dacts[L - 1], self.loss, rows,
-                                     self.dims[L], 1.0 / gb)
+        if self.loss_kind == TT_LOSS_CE:
+            rt.LaunchSoftmaxCrossEntropy(self._acts[L - 1], labels, self._dacts[L - 1], self.loss, rows,
+                                         self.dims[L], 1.0 / gb)
+        else:
+            if gb != rows:
+                raise ValueError("the MSE loss is single-GPU only (its mean runs over this rank's rows)")
+            rt.LaunchMseLoss(self._acts[L - 1], labels, self._dacts[L - 1], self.loss, rows * self.dims[L])
 
     # ---- one training step ----
     def step(self, x, labels, global_batch=None, apply_update=True):
         """x: (rows, dims[0]) float32 CUDA, labels: (rows,) int32 CUDA.  Returns the device
         scalar holding this rank's share of the mean loss (sum over ranks = global mean)."""
         rt, L, rows = self.rt, self.L, x.shape[0]
+        self.last_step_fused = False
+        if self.fused and self.peer is None and self.pg is None and apply_update and (global_batch or rows) == rows:
+            try:
+                rt.SetCuBlasMathMode(self.math_mode)
+                rt.LaunchMlpTrainStep(self.dims, self.act, self.loss_kind, self.params, self.m, self.v, self.adv,
+                                      self.grads, x, labels, self.loss, rows, lr=self.lr,
+                                      max_grad_norm=self.max_grad_norm, clip_eps=self.clip_eps)
+                self.last_step_fused = True
+                return self.loss
+            except TensotronGemmError as e:
+                if e.status != 3 or self.fused is True:
+                    raise
         self.forward(x, labels, global_batch)
         if self.peer is not None:
             if not apply_update:
@@ -166,7 +199,7 @@ class MlpTrainer:
             return self.loss
         handles = []
         for i in reversed(range(L)):
-            act = 1 if i < L - 1 else 0
+            act = self.act if i < L - 1 else 0
             layer_in = x if i == 0 else self._acts[i - 1]
             dx = self._dacts[i - 1] if i > 0 else None
             rt.LaunchLinearBackward(layer_in, self.weight(i), self._acts[i], self._dacts[i], dx,
@@ -177,6 +210,8 @@ class MlpTrainer:
                 handles.append(dist.all_reduce(self.layer_slice(i, self.grads), group=self.pg, async_op=True))
         for h in handles:
             h.wait()
+        if self.max_grad_norm > 0:
+            rt.LaunchClipGradNorm(self.grads, self.n_params, self.max_grad_norm, self.clip_eps)
         if apply_update:
             rt.LaunchAdam(self.params, self.grads, self.m, self.v, self.adv, self.n_params, lr=self.lr)
         return self.loss
@@ -187,7 +222,7 @@ class MlpTrainer:
     # channel = the layer (0 when the exchange is not pipelined).
     def peer_backward_layer(self, x, i):
         L, pr, rows = self.L, self.peer, x.shape[0]
-        act = 1 if i < L - 1 else 0
+        act = self.act if i < L - 1 else 0
         layer_in = x if i == 0 else self._acts[i - 1]
         dx = self._dacts[i - 1] if i > 0 else None
         w_off, b_off = self.offs[i]

@@ -20,7 +20,7 @@ EXPORTS = [
     "tt_version", "tt_create", "tt_destroy", "tt_last_error", "tt_set_math_mode", "tt_get_math_mode",
     "tt_matmul", "tt_matmul_batched", "tt_matmul_batched_reduce", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
-    "tt_set_variant", "tt_softmax_cross_entropy_static",
+    "tt_set_variant", "tt_softmax_cross_entropy_static", "tt_mse_loss", "tt_clip_grad_norm", "tt_mlp_train_step",
     "tt_peer_alloc", "tt_peer_free", "tt_peer_export", "tt_peer_open", "tt_peer_close", "tt_peer_group_create",
     "tt_peer_group_destroy", "tt_peer_linear_bwd", "tt_peer_push", "tt_peer_adam_step", "tt_peer_sync",
     "tt_peer_set_wait_limit",
@@ -33,9 +33,21 @@ class TensotronGemmError(RuntimeError):
         self.status = status
 
 
+TT_LOSS_MSE, TT_LOSS_CE = 0, 1
+LOSS = {"mse": 0, "ce": 1, 0: 0, 1: 1}
+MLP_MAX_LAYERS = 4
+
+
+class MlpDesc(ctypes.Structure):
+    """tt_mlp_desc: a small MLP for tt_mlp_train_step."""
+    _fields_ = [("n_layers", ctypes.c_int), ("dims", ctypes.c_int * (MLP_MAX_LAYERS + 1)),
+                ("act", ctypes.c_int), ("loss", ctypes.c_int)]
+
+
 class Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_longlong) for n in
-                ("launches", "calls", "simt_tma", "tcgen05", "generic", "splitk", "skinny", "workspace_bytes")]
+                ("launches", "calls", "simt_tma", "tcgen05", "generic", "splitk", "skinny", "workspace_bytes",
+                 "tensor_map_hits", "tensor_map_misses")]
 
 
 _lib = None
@@ -69,6 +81,9 @@ def load_library(path=None):
     L.tt_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, vp, i, i, f]
     L.tt_softmax_cross_entropy_static.argtypes = [vp, vp, vp, vp, vp, i, i, f]
     L.tt_adam_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, i]
+    L.tt_mse_loss.argtypes = [vp, vp, vp, vp, vp, vp, ll]
+    L.tt_clip_grad_norm.argtypes = [vp, vp, vp, ll, f, f, vp]
+    L.tt_mlp_train_step.argtypes = [vp, vp, ctypes.POINTER(MlpDesc), vp, vp, vp, vp, vp, vp, vp, vp, i, f, f, f, f, f, f]
     L.tt_add_into.argtypes = [vp, vp, vp, vp, ll]
     L.tt_broadcast_batch.argtypes = [i, ip, ip, i, ip, ip, ip, ip, ip, ip]
     L.tt_get_stats.argtypes = [vp, ctypes.POINTER(Stats)]
@@ -224,6 +239,30 @@ class TensorRuntime:
         self._ck(self._L.tt_adam_step(self._h, self._st(stream), _ptr(p), _ptr(g), _ptr(m), _ptr(v),
                                       _ptr(adv), n, b1, b2, lr, eps, coupledWd, decoupledFactor,
                                       1 if advance else 0))
+
+    def LaunchMseLoss(self, input, target, dinput, loss, count, stream=None):
+        """MseLoss(mean) forward + backward (src/Tensotron/TensorOps.Losses.cs:29-61)."""
+        self._ck(self._L.tt_mse_loss(self._h, self._st(stream), _ptr(input), _ptr(target), _ptr(dinput),
+                                     _ptr(loss), count))
+
+    def LaunchClipGradNorm(self, grads, n, max_norm, eps=1e-6, norm_out=None, stream=None):
+        """GradUtils.ClipGradNorm over a flat gradient span (src/Tensotron/Optimizers.cs:383-422)."""
+        self._ck(self._L.tt_clip_grad_norm(self._h, self._st(stream), _ptr(grads), n, max_norm, eps, _ptr(norm_out)))
+
+    def LaunchMlpTrainStep(self, dims, act, loss_kind, params, m, v, adv, grads_out, x, target, loss, batch,
+                           lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, max_grad_norm=0.0, clip_eps=1e-6, stream=None):
+        """tt_mlp_train_step: forward + loss + backward + clip + Adam of a small MLP as one launch.
+        Raises status 3 when the network or the batch does not fit one cluster."""
+        d = MlpDesc()
+        d.n_layers = len(dims) - 1
+        if not 1 <= d.n_layers <= MLP_MAX_LAYERS:
+            raise TensotronGemmError(3, "the one-launch MLP step takes 1..%d layers" % MLP_MAX_LAYERS)
+        for i, w in enumerate(dims):
+            d.dims[i] = int(w)
+        d.act, d.loss = ACT[act], LOSS[loss_kind]
+        self._ck(self._L.tt_mlp_train_step(self._h, self._st(stream), ctypes.byref(d), _ptr(params), _ptr(m), _ptr(v),
+                                           _ptr(adv), _ptr(grads_out), _ptr(x), _ptr(target), _ptr(loss), batch,
+                                           lr, b1, b2, eps, max_grad_norm, clip_eps))
 
     def LaunchAddInto(self, target, source, n, stream=None):
         self._ck(self._L.tt_add_into(self._h, self._st(stream), _ptr(target), _ptr(source), n))

@@ -532,6 +532,26 @@ def test_add_into(rt):
     assert torch.equal(a, torch.arange(1003, dtype=torch.float32, device="cuda") + 1)
 
 
+def test_tensor_map_descriptors_are_cached_per_buffer_and_shape(rt):
+    """The TMA descriptors of a call are a function of (pointer, dims, strides, box): the second
+    call on the same buffers re-encodes nothing, another buffer or shape does."""
+    a = torch.randn(512, 256, device="cuda")
+    b = torch.randn(256, 384, device="cuda")
+    c = torch.empty(512, 384, device="cuda")
+    rt.LaunchMatMul(a, b, c, 512, 384, 256, 256, 1, 384, 1)
+    rt.ResetCounters()
+    rt.LaunchMatMul(a, b, c, 512, 384, 256, 256, 1, 384, 1)
+    s = rt.Stats()
+    assert s["simt_tma"] == 1 and s["tensor_map_misses"] == 0 and s["tensor_map_hits"] == 2, s
+    a2 = torch.randn(512, 256, device="cuda")
+    rt.LaunchMatMul(a2, b, c, 512, 384, 256, 256, 1, 384, 1)
+    s = rt.Stats()
+    assert s["tensor_map_misses"] == 1 and s["tensor_map_hits"] == 3, s
+    rt.Check()
+    exp = oracle.matmul2d(a2.cpu().numpy(), b.cpu().numpy(), 512, 384, 256, 256, 1, 384, 1)
+    assert np.abs(c.cpu().numpy() - exp).max() <= fp32_bound(256, a2.cpu().numpy(), b.cpu().numpy())
+
+
 # ---- stream capture (the reference's native-graph contract) --------------------------------
 
 def test_graph_capture_replays_with_new_inputs(rt):

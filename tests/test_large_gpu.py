@@ -238,20 +238,29 @@ def test_mlp_step_at_full_width_1024_rows(big_rt):
     rt.Check()
     lo = ref.step(x, y)
     assert abs(loss - lo) <= 2e-5 * max(1.0, abs(lo)), (loss, lo)
+    # Yardstick for the gradients: the oracle against itself with another SIMD width (4 lanes
+    # instead of 8), i.e. the same arithmetic in another summation order.  At initialisation the
+    # gradients nearly cancel, rounding differences are handed down through three 4096-wide
+    # layers, and a pre-activation within an ulp of zero may pass the ReLU on one side and not on
+    # the other (one g element then changes by its full value), so the strict-FP32 bound of a
+    # single product does not apply to the deep layers.  The CUDA path must differ from the
+    # oracle by no more than a small multiple of what the oracle differs from itself.
+    alt = oracle.MlpOracle(ws, bs, lr=1e-3)
+    oracle.lib().oracle_set_vector_width(4)
+    try:
+        alt.step(x, y, apply_update=False)
+    finally:
+        oracle.lib().oracle_set_vector_width(8)
     for i in range(tr.L):
-        # dW_i = g_i^T . act_i over K = batch rows.  Strict-FP32 bound on that contraction (x4 for
-        # the rounding differences the upstream layers hand down).  A pre-activation within an
-        # ulp of zero may pass the ReLU on one side and not on the other, which changes one
-        # g element by its full value: a handful of elements may therefore differ by up to
-        # max|g|.max|act|, nothing more.
         g_i, a_i = ref.gs[i], ref.acts[i]
-        tight = 4 * fp32_bound(batch, g_i, a_i) + 1e-9
-        loose = 2 * float(np.abs(g_i).max() * np.abs(a_i).max())
-        for got, want in ((tr.weight(i, tr.grads).cpu().numpy(), ref.grads[i]),
-                          (tr.bias(i, tr.grads).cpu().numpy(), ref.grads[tr.L + i])):
+        loose = 2 * float(np.abs(g_i).max() * np.abs(a_i).max())       # one flipped ReLU
+        for got, want, other in ((tr.weight(i, tr.grads).cpu().numpy(), ref.grads[i], alt.grads[i]),
+                                 (tr.bias(i, tr.grads).cpu().numpy(), ref.grads[tr.L + i], alt.grads[tr.L + i])):
             d = np.abs(got - want)
+            noise = float(np.abs(other - want).mean())
+            single = fp32_bound(batch, g_i, a_i)                        # bound of this one product
             assert d.max() <= loose, (i, d.max(), loose)
-            assert np.mean(d > tight) <= 1e-4, (i, float(np.mean(d > tight)), tight)
+            assert d.mean() <= 4 * noise + single, (i, float(d.mean()), noise, single)
         for got, want in ((tr.weight(i).cpu().numpy(), ref.w[i]), (tr.bias(i).cpu().numpy(), ref.b[i])):
             d = np.abs(got - want)
             # Adam normalises each element: one whose gradient is at rounding-noise level may step

@@ -145,39 +145,112 @@ def time_calls(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
-def sgemm_modes_8192(rt, sms, max_mhz):
-    """North-star sizes: 8192^3 in strict FP32, TF32 and 3xTF32 (single GPU)."""
+def peaks(sms, max_mhz):
+    """Roofline denominators: FP32 FMA peak derived from the device (the measured-peaks file has no
+    FP32 SIMT figure), TF32 dense peak = half the measured BF16 burst figure (same tensor pipe,
+    twice the operand width), HBM bandwidth as measured."""
+    out = {"fp32_ffma_tflops": sms * 128 * 2 * max_mhz * 1e6 / 1e12}
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        out["tf32_tflops"] = pk["bf16_tflops"] / 2.0
+        out["hbm_gbs"] = pk["hbm_gbs"]
+        out["source"] = "of measured (MEASURED_PEAKS.json); TF32 = half the BF16 burst figure, derived"
+    except (OSError, KeyError, ValueError):
+        out["tf32_tflops"] = 1590.0 / 2.0
+        out["hbm_gbs"] = 6650.0
+        out["source"] = "of fallback (1.59 PFLOP/s BF16, 6.65 TB/s)"
+    return out
+
+
+def sgemm_sweep(rt, sms, max_mhz):
+    """Benchmark config 5 on one GPU: M = N = K in {512 ... 8192} x {strict FP32, TF32, 3xTF32},
+    TFLOP/s and fraction of the pipe's peak per entry (the north-star fractions are quoted at
+    8192^3), with cuBLAS through torch.matmul on the same box, same operands, same event timing as
+    the stated comparator (`cublas_same_box`, `vs_cublas` = cuBLAS time / our time; never on the
+    product path).  3xTF32 has no cuBLAS counterpart and is compared with cuBLAS strict FP32."""
     import torch
 
     from tensotron_b200.runtime import TT_MATH_3XTF32, TT_MATH_FP32, TT_MATH_TF32
-    n = 8192
-    a = torch.rand((n, n), device="cuda") * 2 - 1
-    b = torch.rand((n, n), device="cuda") * 2 - 1
-    c = torch.empty((n, n), device="cuda")
-    flop = 2.0 * n ** 3
-    fp32_peak = sms * 128 * 2 * max_mhz * 1e6 / 1e12
-    tf32_peak = None
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        tf32_peak = peaks["bf16_tflops"] / 2.0
-        src = "derived: half of the measured BF16 burst peak (MEASURED_PEAKS.json)"
-    except (OSError, KeyError, ValueError):
-        tf32_peak = 1590.0 / 2.0
-        src = "derived: half of the fallback BF16 peak (1.59 PFLOP/s)"
-    out = {}
-    for name, mode, iters in (("fp32", TT_MATH_FP32, 5), ("tf32", TT_MATH_TF32, 20), ("3xtf32", TT_MATH_3XTF32, 10)):
-        rt.SetCuBlasMathMode(mode)
-        ms = time_calls(lambda: rt.LaunchMatMul(a, b, c, n, n, n, n, 1, n, 1), iters)
-        tf = flop / ms / 1e9
-        if name == "fp32":
-            out[name] = {"tflops": tf, "ms": ms, "frac_of_fp32_ffma_peak": tf / fp32_peak}
-        else:
-            pipe = tf * (3 if name == "3xtf32" else 1)
-            out[name] = {"tflops": tf, "ms": ms, "tensor_pipe_tflops": pipe,
-                         "frac_of_tf32_peak": pipe / tf32_peak}
+    pk = peaks(sms, max_mhz)
+    out = {"peaks": pk, "sizes": {}}
+    for n in (512, 1024, 2048, 4096, 8192):
+        a = torch.rand(n * n, device="cuda") * 2 - 1
+        b = torch.rand(n * n, device="cuda") * 2 - 1
+        c = torch.empty((n, n), device="cuda")
+        flop = 2.0 * n ** 3
+        iters = {512: 200, 1024: 100, 2048: 50, 4096: 20, 8192: 5}[n]
+        entry = {}
+        lib = {}
+        for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32)):
+            ms_lib = cublas_ms(a, b, n, n, n, "NN", mode, iters)
+            lib[name] = {"ms": ms_lib, "tflops": flop / ms_lib / 1e9}
+        for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32), ("3xtf32", TT_MATH_3XTF32)):
+            rt.SetCuBlasMathMode(mode)
+            it = iters if name != "fp32" or n < 8192 else 5
+            ms = time_calls(lambda: rt.LaunchMatMul(a, b, c, n, n, n, n, 1, n, 1), it)
+            tf = flop / ms / 1e9
+            e = {"tflops": tf, "ms": ms}
+            if name == "fp32":
+                e["frac_of_fp32_ffma_peak"] = tf / pk["fp32_ffma_tflops"]
+                e["vs_cublas"] = lib["fp32"]["ms"] / ms
+            else:
+                pipe = tf * (3 if name == "3xtf32" else 1)
+                e["tensor_pipe_tflops"] = pipe
+                e["frac_of_tf32_peak"] = pipe / pk["tf32_tflops"]
+                e["vs_cublas"] = lib["tf32" if name == "tf32" else "fp32"]["ms"] / ms
+            entry[name] = e
+        entry["cublas_same_box"] = lib
+        out["sizes"][str(n)] = entry
+        del a, b, c
     rt.SetCuBlasMathMode(TT_MATH_FP32)
-    out["tf32_peak_tflops"] = tf32_peak
-    out["tf32_peak_source"] = src
+    return out
+
+
+def timed_max_ms(fn, iters, world, warmup=3):
+    """CUDA-event time per call after warm-up, bracketed by a barrier, max over the ranks."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def sgemm_16384_tensor_modes(rt, rank, world, sms, max_mhz):
+    """The headline product (16384^3, rows of A and C sharded over the ranks, B replicated, no
+    collective) in the tensor-core modes: whole-job TFLOP/s at this N, max-over-ranks time."""
+    import torch
+
+    from tensotron_b200.runtime import TT_MATH_3XTF32, TT_MATH_FP32, TT_MATH_TF32
+    n = N_TOTAL
+    rows = n // world
+    gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
+    a = torch.rand((rows, n), generator=gen, device="cuda") * 2 - 1
+    gen.manual_seed(98)
+    b = torch.rand((n, n), generator=gen, device="cuda") * 2 - 1
+    c = torch.empty((rows, n), device="cuda")
+    pk = peaks(sms, max_mhz)
+    out = {"rows_per_gpu": rows}
+    for name, mode, iters in (("tf32", TT_MATH_TF32, 10), ("3xtf32", TT_MATH_3XTF32, 5)):
+        rt.SetCuBlasMathMode(mode)
+        ms = timed_max_ms(lambda: rt.LaunchMatMul(a, b, c, rows, n, n, n, 1, n, 1), iters, world)
+        tf = 2.0 * n ** 3 / ms / 1e9
+        pipe = tf * (3 if name == "3xtf32" else 1)
+        out[name] = {"tflops": tf, "ms": ms, "tensor_pipe_tflops_per_gpu": pipe / world,
+                     "frac_of_tf32_peak": pipe / world / pk["tf32_tflops"]}
+    rt.SetCuBlasMathMode(TT_MATH_FP32)
+    rt.Check()
     return out
 
 
@@ -236,44 +309,60 @@ def small_configs(rt):
     us, host = replay_us(fwd_bwd)
     out["linear_relu_64x128x64_fwd_bwd"] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches}
 
-    # RL-policy shape: 8-64-64-2 MLP, batch 64, whole training step (forward, cross-entropy,
-    # backward, Adam) as one replayed graph
+    # The reference's replay sweep (examples/Tensotron.Examples/BenchExample.cs:140-176): Tanh MLPs,
+    # MSE loss, ClipGradNorm(0.5), Adam(1e-3); whole training step per replayed graph node set.
+    # The control / PPO sized networks run as ONE launch (tt_mlp_train_step); the 128-256-256-10
+    # entry is too wide for one cluster and runs layer by layer.
     from tensotron_b200.mlp import MlpTrainer
-    tr = MlpTrainer([8, 64, 64, 2], rt=rt, lr=1e-3, seed=3)
-    xs = torch.randn((64, 8), device="cuda")
-    ys = torch.randint(0, 2, (64,), device="cuda", dtype=torch.int32)
-    l0 = rt.Stats()["launches"]
-    tr.step(xs, ys)
-    launches = rt.Stats()["launches"] - l0
-    us, host = replay_us(lambda: tr.step(xs, ys), iters=10)
-    out["mlp_8_64_64_2_batch64_train_step"] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches}
+    for name, dims, batch in (("ctrl_net_b1", [8, 64, 64, 2], 1), ("ppo_b64", [8, 64, 64, 2], 64),
+                              ("ppo_b512", [8, 64, 64, 2], 512), ("critic_4_32_32_1_b64", [4, 32, 32, 1], 64),
+                              ("mlp_b256_128_256_256_10", [128, 256, 256, 10], 256)):
+        tr = MlpTrainer(dims, rt=rt, lr=1e-3, seed=3, act="tanh", loss="mse", max_grad_norm=0.5, fused="auto")
+        xs = torch.rand((batch, dims[0]), device="cuda") - 0.5
+        ts = torch.zeros((batch, dims[-1]), device="cuda")
+        l0 = rt.Stats()["launches"]
+        tr.step(xs, ts)
+        launches = rt.Stats()["launches"] - l0
+        us, host = replay_us(lambda: tr.step(xs, ts), iters=10)
+        out["train_step_" + name] = {"graph_replay_us": us, "eager_host_us": host, "launches": launches,
+                                     "one_launch": bool(tr.last_step_fused), "batch": batch, "dims": dims}
     return out
 
 
-def bmm_config3(rt):
-    """Config 3: A [32,1,384,256] x B [1,16,256,192] -> [32,16,384,192], one launch through
-    LaunchMatMulBatched (the reference issues 512 cuBLAS calls); FP32 and TF32.  In TF32 the
-    151 MB output write makes it HBM-bound, so achieved GB/s is reported too."""
+def bmm_config3(rt, rank=0, world=1):
+    """Config 3: A [32,1,384,256] x B [1,16,256,192] -> [32,16,384,192] through LaunchMatMulBatched
+    (the reference issues 512 cuBLAS calls), the outer batch axis (32) split over the ranks --
+    each rank one launch over its 32 / world entries of A, B replicated, no collective.  FP32, TF32
+    and 3xTF32; whole-job numbers with the max-over-ranks time.  In TF32 the 151 MB output write
+    makes it HBM-bound, so achieved GB/s of algorithmic bytes (per GPU) is reported too."""
     import torch
 
     from tensotron_b200 import runtime
-    from tensotron_b200.runtime import TT_MATH_FP32, TT_MATH_TF32
-    a = torch.rand((32, 1, 384, 256), device="cuda") * 2 - 1
-    b = torch.rand((1, 16, 256, 192), device="cuda") * 2 - 1
-    c = torch.empty((32, 16, 384, 192), device="cuda")
-    dims, aBs, bBs = runtime.broadcast_batch([32, 1], [98304, 98304], [1, 16], [786432, 49152])
+    from tensotron_b200.mlp import shard_rows
+    from tensotron_b200.runtime import TT_MATH_3XTF32, TT_MATH_FP32, TT_MATH_TF32
+    i0, i1 = shard_rows(32, world, rank)
+    nb = i1 - i0
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    a = (torch.rand((32, 1, 384, 256), generator=gen, device="cuda") * 2 - 1)[i0:i1].contiguous()
+    gen.manual_seed(8)
+    b = torch.rand((1, 16, 256, 192), generator=gen, device="cuda") * 2 - 1
+    c = torch.empty((max(nb, 1), 16, 384, 192), device="cuda")
+    dims, aBs, bBs = runtime.broadcast_batch([nb, 1], [98304, 98304], [1, 16], [786432, 49152])
     flop = 512 * 2.0 * 384 * 192 * 256
-    nbytes = 4.0 * (a.numel() + b.numel() + c.numel())
-    out = {"algorithmic_bytes": nbytes, "flop": flop}
-    for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32)):
+    nbytes = 4.0 * (32 * 384 * 256 + b.numel() * world + 32 * 16 * 384 * 192)   # whole job; B once per GPU
+    out = {"algorithmic_bytes": nbytes, "flop": flop, "batch_entries_per_gpu": nb, "hbm_peak_gbs": peaks(148, 1965.0)["hbm_gbs"]}
+
+    def call():
+        if nb > 0:
+            rt.LaunchMatMulBatched(a, b, c, nb * 16, 384, 192, 256, 256, 1, 192, 1, dims, aBs, bBs)
+
+    for name, mode in (("fp32", TT_MATH_FP32), ("tf32", TT_MATH_TF32), ("3xtf32", TT_MATH_3XTF32)):
         rt.SetCuBlasMathMode(mode)
-        ms = time_calls(lambda: rt.LaunchMatMulBatched(a, b, c, 512, 384, 192, 256, 256, 1, 192, 1, dims, aBs, bBs), 20)
-        out[name] = {"ms": ms, "tflops": flop / ms / 1e9, "hbm_gbs": nbytes / ms / 1e6}
+        ms = timed_max_ms(call, 20, world)
+        out[name] = {"ms": ms, "tflops": flop / ms / 1e9, "hbm_gbs_per_gpu": nbytes / world / ms / 1e6,
+                     "frac_of_hbm": nbytes / world / ms / 1e6 / out["hbm_peak_gbs"]}
     rt.SetCuBlasMathMode(TT_MATH_FP32)
-    try:
-        out["hbm_peak_gbs"] = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]
-    except (OSError, KeyError, ValueError):
-        out["hbm_peak_gbs"] = 6650.0
+    rt.Check()
     return out
 
 
@@ -333,6 +422,28 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
         rt.Check()
         tr.close()
         del tr
+    if world > 1:
+        # run-to-run bit stability of the NCCL form (algorithm and protocol pinned): two runs of
+        # three steps from the same initial state must end in identical parameters on every rank
+        s, e = shard_rows(8192, world, rank)
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        xs = torch.randn((8192, 784), generator=gen, device="cuda")[s:e].contiguous()
+        gen.manual_seed(1)
+        ys = torch.randint(0, 10, (8192,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
+        finals = []
+        for _ in range(2):
+            tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
+                            process_group=pg, math_mode=TT_MATH_FP32, exchange="nccl")
+            for _ in range(3):
+                tr.step(xs, ys, global_batch=8192)
+            torch.cuda.synchronize()
+            finals.append(tr.params.clone())
+            tr.close()
+            del tr
+        same = torch.tensor([1.0 if torch.equal(finals[0], finals[1]) else 0.0], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        res["nccl_bitwise_repeatable"] = bool(same.item() == 1.0)
+        res["nccl_pinned"] = {"NCCL_ALGO": os.environ.get("NCCL_ALGO"), "NCCL_PROTO": os.environ.get("NCCL_PROTO")}
     rt.SetCuBlasMathMode(TT_MATH_FP32)
     return res
 
@@ -351,6 +462,27 @@ def cublas_ms(a, b, M, N, K, lay, mode, iters):
         return time_calls(lambda: torch.matmul(a2, b2, out=out), iters)
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def check_row_slab(a, b, c, n, count=16):
+    """`count` rows of C = A.B (spread over the shard, all columns) against the CPU oracle:
+    max |err| and the strict-FP32 acceptance bound 1e-5 * sqrt(K) * max|A| * max|B|."""
+    import numpy as np
+    import torch
+
+    import oracle
+    rows = a.shape[0]
+    idx = sorted(set([0, rows - 1] + [int(v) for v in np.random.default_rng(5).choice(rows, size=min(rows, count) - 2, replace=False)]))
+    sel = torch.tensor(idx, device=a.device)
+    a_rows = a.index_select(0, sel).cpu().numpy()
+    b_host = b.cpu().numpy()
+    got = c.index_select(0, sel).cpu().numpy()
+    oracle.set_threads("auto")
+    exp = oracle.matmul2d(a_rows, b_host, len(idx), n, n, n, 1, n, 1)
+    err = float(np.abs(got - exp).max())
+    bound = float(1e-5 * np.sqrt(n) * np.abs(a_rows).max() * np.abs(b_host).max())
+    return {"max_err": err, "bound": bound, "ok": bool(err <= bound), "rows_checked": len(idx),
+            "against": "CPU oracle (C restatement of CpuKernels.MatMul2D) on the same operands"}
 
 
 def run_one(spec):
@@ -474,6 +606,11 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # One algorithm and one protocol for every NCCL all-reduce of the gradient exchange's
+        # "nccl" form: the order in which the ranks' contributions are added is then fixed, and the
+        # step is bit-stable from run to run (checked below, `nccl_bitwise_repeatable`).
+        os.environ.setdefault("NCCL_ALGO", "Ring")
+        os.environ.setdefault("NCCL_PROTO", "Simple")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     # raises if the CUDA library is missing: no fallback.  2.5 GiB workspace: 3xTF32 keeps
@@ -519,9 +656,19 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     rt.Check()
 
+    # ---- correctness of the very call that was timed (outside the timed region): a sample of rows
+    # of this rank's C against the CPU oracle at the strict-FP32 bound ----
+    check = None
+    if rank == 0:
+        check = check_row_slab(a, b, c, n)
+
     # ---- end to end: pinned host operands, copies inside the timed region ----
+    # B: the job's inputs cross PCIe once.  Each rank copies a 1 / world row slice of B from its
+    # host buffer and one NCCL all-gather lands the whole B in every rank's local HBM (the GEMM's
+    # operands and tensor maps are local memory only).
+    brow = n // world
     ha = torch.empty((rows, n), pin_memory=True).copy_(a)
-    hb = torch.empty((n, n), pin_memory=True).copy_(b)
+    hb = torch.empty((brow, n), pin_memory=True).copy_(b[rank * brow:(rank + 1) * brow])
     hc = torch.empty((rows, n), pin_memory=True)
     e2e_steps = max(1, min(args.steps, 5))
 
@@ -541,7 +688,9 @@ def main():
         with torch.cuda.stream(s_h2d):
             if comp_done[j % 2] is not None:
                 s_h2d.wait_event(comp_done[j % 2])       # the set's previous GEMMs are done reading
-            db.copy_(hb, non_blocking=True)
+            db[rank * brow:(rank + 1) * brow].copy_(hb, non_blocking=True)
+            if world > 1:
+                dist.all_gather_into_tensor(db, db[rank * brow:(rank + 1) * brow])   # in place, on s_h2d
             ev_b = torch.cuda.Event()
             ev_b.record(s_h2d)
             ev_a = []
@@ -600,13 +749,21 @@ def main():
             except Exception as ex:
                 extras[name] = {"error": "%s: %s" % (type(ex).__name__, ex)}
 
+        props0 = torch.cuda.get_device_properties(local_rank)
+        sms0 = props0.multi_processor_count
+        mhz0 = 1965.0
+        if world > 1:
+            mt = torch.tensor([(clocks or {}).get("sm_max_mhz") or 0.0], device="cuda", dtype=torch.float64)
+            dist.broadcast(mt, 0)
+            mhz0 = mt.item() or 1965.0
+        else:
+            mhz0 = (clocks or {}).get("sm_max_mhz") or 1965.0
         guarded("mlp_784_4096x3_10_batch8192", lambda: mlp_steps_per_s(rt, rank, world, local_rank, pg))
+        guarded("sgemm_16384_tensor_modes", lambda: sgemm_16384_tensor_modes(rt, rank, world, sms0, mhz0))
+        guarded("bmm_32x16_384x256x192", lambda: bmm_config3(rt, rank, world))
         if world == 1:
-            props0 = torch.cuda.get_device_properties(local_rank)
-            guarded("bmm_32x16_384x256x192", lambda: bmm_config3(rt))
             guarded("small_configs", lambda: small_configs(rt))
-            guarded("sgemm_8192", lambda: sgemm_modes_8192(rt, props0.multi_processor_count,
-                                                           (clocks or {}).get("sm_max_mhz") or 1965.0))
+            guarded("sgemm_sweep", lambda: sgemm_sweep(rt, sms0, mhz0))
 
     t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
     if world > 1:
@@ -626,6 +783,7 @@ def main():
         roof = {
             "bound": "fp32_ffma", "achieved": per_gpu, "peak": peak, "unit": UNIT,
             "frac": per_gpu / peak, "traffic": NCU_TRAFFIC_BYTES.get(n) if world == 1 else None,
+            "traffic_is_scaled": n != 8192,
             "traffic_note": "ncu DRAM bytes per launch; 16384 is the 8192^3 capture scaled (reads x 8, writes x 4)",
             "peak_source": "derived: %d SMs x 128 FP32 lanes x 2 x %.0f MHz (max SM clock); the "
                            "measured-peaks file has no FP32 SIMT figure" % (sms, max_mhz),
@@ -644,10 +802,14 @@ def main():
                        "rows_per_gpu": rows, "l2": "operands (%.0f MiB A-shard + %.0f MiB B) exceed the 126 MB L2"
                        % (rows * n * 4 / 2 ** 20, n * n * 4 / 2 ** 20)},
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (rows * n + n * n) * 4,
-                    "d2h_bytes_per_step": rows * n * 4, "steps": e2e_steps,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (rows * n + brow * n) * 4 * world,
+                    "d2h_bytes_per_step": rows * n * 4 * world, "steps": e2e_steps,
+                    "per_rank": "H2D %d rows of A + %d rows of B, D2H %d rows of C" % (rows, brow, rows),
+                    "b_placement": "local" if world == 1 else "each rank copies 1/%d of B from the host, one NCCL all-gather "
+                                   "lands the whole B in every rank's HBM" % world,
                     "pipeline": "%d row chunks per step on H2D / compute / D2H streams, two buffer sets" % n_chunks},
             "gpu_launches": launches,
+            "check": check,
             "roofline": roof,
         }
         if extras:

@@ -101,6 +101,14 @@ TT_API int tt_matmul_batched_reduce(tt_handle_t h, void* stream, const float* a,
                              const int* batchDims, const int* aBatchStrides,
                              const int* bBatchStrides, const int* reduceAxis);
 
+/* ReduceGradToShape (src/Tensotron/TensorOps.cs:76-100): sums a contiguous row-major tensor of
+ * `rank` axes (<= 8) over the axes with reduceAxis[ax] != 0; dst is contiguous over the remaining
+ * axes in order.  One thread per output walks the summed axes in ascending row-major order (fixed
+ * order, no atomics).  The unfused companion of tt_matmul_batched_reduce, for broadcast axes that do
+ * not merge into one. */
+TT_API int tt_reduce_sum_axes(tt_handle_t h, void* stream, const float* src, float* dst, int rank,
+                              const int* dims, const int* reduceAxis);
+
 /* Linear.Forward (+ the Activation module that follows it) as one launch
  * (src/Tensotron/Module.cs:100-105, src/Tensotron/TensorOps.LinearNT.cs:13-25):
  *   y = act(x (M,K) . w (N,K)^T + bias (N)),  bias may be NULL. */
@@ -228,7 +236,8 @@ TT_API int tt_check(tt_handle_t h, void* stream);
 /* Forces a kernel variant for A/B measurements: 0 auto, 1 any-stride kernel,
  * 2 TMA-fed FFMA kernel with 256x128 tiles, 3 the same with 128x128 tiles,
  * 4 / 5 tcgen05 kernel (TF32 modes only) with 128- / 256-row tiles,
- * 6 FFMA kernel with 256x128 tiles and stream-K work distribution. */
+ * 6 FFMA kernel with 256x128 tiles and stream-K work distribution,
+ * 7 FFMA kernel with 128x192 tiles (B contiguous along N only). */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 /* ---- Data-parallel gradient exchange over peer memory ---------------------------------

@@ -253,17 +253,17 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     return TT_OK;
 }
 
-template <int TM, bool AK, bool BK_>
+template <int TM, bool AK, bool BK_, int NJ = 2>
 int launch_simt_t(tt_handle_t h, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb,
                   const simt::Params& p, int grid, int mode)
 {
-    constexpr int smem = simt::Cfg<TM, AK, BK_>::SMEM_BYTES;
+    constexpr int smem = simt::Cfg<TM, AK, BK_, NJ>::SMEM_BYTES;
     if (mode == simt::MODE_STREAMK)
-        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_STREAMK><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
-    else if (TM == 8 && mode == simt::MODE_SPLITK)   // split-K exists for the 128x128 tile only
+        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_STREAMK, NJ><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+    else if (TM == 8 && NJ == 2 && mode == simt::MODE_SPLITK)   // split-K exists for the 128x128 tile only
         simt::sgemm_simt_kernel<8, AK, BK_, simt::MODE_SPLITK><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
     else
-        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_TILES><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
+        simt::sgemm_simt_kernel<TM, AK, BK_, simt::MODE_TILES, NJ><<<grid, simt::THREADS, smem, st>>>(ma, mb, p);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "simt gemm launch");
     return TT_OK;
@@ -280,26 +280,32 @@ struct SimtPlan {
     int splits;
     int kps;
     bool streamk = false;   // deal tiles x k-tiles units evenly to the CTAs (partial last wave)
+    int nj = 2;             // tile width / 64: 2 = 128 columns, 3 = 192 columns (128-row tiles, MN-major B)
 };
 
-SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail, int red_count)
+SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t ws_avail, int red_count, bool b_kmajor)
 {
     const int k_tiles = (K + simt::BK - 1) / simt::BK;
     if (red_count > 1) ws_avail = 0;  // a reduced batch axis already lengthens the k loop: no split-K
     SimtPlan best{16, 1, k_tiles};
     double best_t = 1e300;
-    for (int tm : {16, 8}) {
-        const int bm = 16 * tm;
-        const long long tiles = static_cast<long long>(batch) * ((M + bm - 1) / bm) * ((N + simt::BN - 1) / simt::BN);
-        const double tile_cost = tm == 16 ? 2.0 / 0.76 : 1.0 / 0.70;
+    // (rows per thread, tile width / 64): cost per tile relative to a 128x128 tile at full FMA rate,
+    // over the fraction of that rate the shape reaches (16x8 per thread 0.80, 8x12 0.76, 8x8 0.73)
+    struct Shape { int tm, nj; double cost; };
+    const Shape shapes[3] = {{16, 2, 2.0 / 0.80}, {8, 2, 1.0 / 0.73}, {8, 3, 1.5 / 0.76}};
+    for (const Shape& sh : shapes) {
+        const int tm = sh.tm, bm = 16 * tm, bn = 64 * sh.nj;
+        if (sh.nj == 3 && b_kmajor) continue;          // the 192-column tile reads MN-major B only
+        const long long tiles = static_cast<long long>(batch) * ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+        const double tile_cost = sh.cost;
         for (int splits = 1; splits <= 32; splits++) {
             const int kps = (k_tiles + splits - 1) / splits;
             const int real = (k_tiles + kps - 1) / kps;
             if (real != splits) continue;              // skip counts that leave empty ranges
             if (splits > 1) {
-                if (tm != 8) break;                    // split-K exists for the 128x128 tile only
+                if (tm != 8 || sh.nj != 2) break;      // split-K exists for the 128x128 tile only
                 if (kps < 1) break;
-                const size_t need = static_cast<size_t>(tiles) * splits * bm * simt::BN * sizeof(float);
+                const size_t need = static_cast<size_t>(tiles) * splits * bm * bn * sizeof(float);
                 if (need > ws_avail) break;
             }
             const long long work = tiles * splits;
@@ -308,12 +314,12 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             // reduction kernel costs about as much as two more k-tiles of a 128x128 tile
             const double t = static_cast<double>(waves) * (static_cast<double>(kps) * red_count + 2.0) * tile_cost +
                              (splits > 1 ? 2.0 / 0.70 : 0.0);
-            if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps, false}; }
+            if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps, false, sh.nj}; }
         }
         // stream-K: no wave quantisation (work / SMs tile-times); needs one partial-tile slot
         // per CTA and enough k-tiles for the ranges to be worth cutting
         if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / 2) {
-            const size_t need = static_cast<size_t>(h->num_sms) * bm * simt::BN * sizeof(float);
+            const size_t need = static_cast<size_t>(h->num_sms) * bm * bn * sizeof(float);
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
             if (need <= ws_avail && fill < 0.97) {
@@ -321,7 +327,7 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
                 // whatever the shape, and a fully busy chip clocks a little lower than one with
                 // idle SMs (5 %)
                 const double t = ((static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost + 11.0) * 1.05;
-                if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true}; }
+                if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true, sh.nj}; }
             }
         }
     }
@@ -330,10 +336,10 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
 
 // Returns TT_ERR_UNSUPPORTED (without touching h->err) when the operands cannot be
 // expressed as TMA descriptors; the caller then uses the any-stride kernel.
-template <int TM>
+template <int TM, int NJ = 2>
 int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const SimtPlan& plan)
 {
-    constexpr int BM = 16 * TM;
+    constexpr int BM = 16 * TM, BN = 64 * NJ;
     OperandView va, vb;
     const int ak = operand_view(g.a, g.M, g.K, g.aMs, g.aKs, va);
     const int bk = operand_view(g.b, g.N, g.K, g.bNs, g.bKs, vb);
@@ -349,13 +355,13 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     int r = ak ? encode_tensor_map(&ma, va, simt::BK, BM, Swizzle::B128)
                : encode_tensor_map(&ma, va, BM, simt::BK, Swizzle::None);
     if (r != 0) return TT_ERR_UNSUPPORTED;
-    r = bk ? encode_tensor_map(&mb, vb, simt::BK, simt::BN, Swizzle::B128)
-           : encode_tensor_map(&mb, vb, simt::BN, simt::BK, Swizzle::None);
+    r = bk ? encode_tensor_map(&mb, vb, simt::BK, BN, Swizzle::B128)
+           : encode_tensor_map(&mb, vb, BN, simt::BK, Swizzle::None);
     if (r != 0) return TT_ERR_UNSUPPORTED;
 
     p.shape.M = g.M; p.shape.N = g.N; p.shape.K = g.K;
     p.shape.tiles_m = (g.M + BM - 1) / BM;
-    p.shape.tiles_n = (g.N + simt::BN - 1) / simt::BN;
+    p.shape.tiles_n = (g.N + BN - 1) / BN;
     p.shape.batch = g.batch_count;
     p.splits = plan.splits;
     p.kps = plan.kps;
@@ -373,15 +379,21 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
     if (plan.splits > 1 || plan.streamk) h->stats.splitk++;
     int rc;
-    if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid, mode);
-    else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid, mode);
-    else if (!ak && !bk) rc = launch_simt_t<TM, false, false>(h, st, ma, mb, p, grid, mode);
-    else rc = launch_simt_t<TM, false, true>(h, st, ma, mb, p, grid, mode);
+    if constexpr (NJ == 3) {
+        if (bk) return TT_ERR_UNSUPPORTED;             // planned for MN-major B only
+        if (ak) rc = launch_simt_t<8, true, false, 3>(h, st, ma, mb, p, grid, mode);
+        else rc = launch_simt_t<8, false, false, 3>(h, st, ma, mb, p, grid, mode);
+    } else {
+        if (ak && bk) rc = launch_simt_t<TM, true, true>(h, st, ma, mb, p, grid, mode);
+        else if (ak && !bk) rc = launch_simt_t<TM, true, false>(h, st, ma, mb, p, grid, mode);
+        else if (!ak && !bk) rc = launch_simt_t<TM, false, false>(h, st, ma, mb, p, grid, mode);
+        else rc = launch_simt_t<TM, false, true>(h, st, ma, mb, p, grid, mode);
+    }
     if (rc != TT_OK) return rc;
     h->stats.launches++;
     h->stats.simt_tma++;
     if (plan.splits > 1) {
-        const long long threads = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * (BM * simt::BN / 4);
+        const long long threads = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n * (BM * BN / 4);
         simt::splitk_reduce_kernel<BM><<<static_cast<unsigned int>((threads + 255) / 256), 256, 0, st>>>(
             p.partial, g.c, p.shape, g.epi, plan.splits, p.c_vec_ok);
         const cudaError_t e = cudaGetLastError();
@@ -392,13 +404,15 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
 }
 
 // Pre-transposition of large K-major operands.  The FMA kernel reads MN-major tiles straight
-// from the TMA stage but has to transpose K-major tiles through shared memory on every k-tile
-// (5.4 % of the run time for A, 3.3 % for B at 8192^3).  One streaming transposition into the
-// workspace costs 8 bytes of traffic per operand element, which is far less once the other
-// dimension is large: A (M x K) pays off for N >= 1536, B (N x K) for M >= 2560.  The sums
-// are the same sums in the same order, so the bits of C do not change.
-constexpr int PRE_T_MIN_N_FOR_A = 1536, PRE_T_MIN_M_FOR_B = 2560;
-constexpr long long PRE_T_MIN_ELEMS = 1ll << 20;
+// from the TMA stage but has to transpose K-major tiles through shared memory on every k-tile:
+// that costs a CTA barrier per k-tile and the shared memory of a ring stage (3 stages instead of
+// 4), 5 to 18 % of the run time depending on the shape (1024 x 4096 x 4096 with K-major B: 669 us
+// against 566 us with MN-major B).  One streaming transposition into the workspace costs 8 bytes
+// of traffic per operand element, which is far less once the other dimension reaches a few
+// hundred: gain / cost is about N / 440 for A (M x K) and M / 440 for B (N x K).  The sums are the
+// same sums in the same order, so the bits of C do not change.
+constexpr int PRE_T_MIN_N_FOR_A = 512, PRE_T_MIN_M_FOR_B = 512;
+constexpr long long PRE_T_MIN_ELEMS = 1ll << 19;
 constexpr size_t PRE_T_RESERVE = 64ull << 20;   // kept free behind the copies (stream-K partial tiles)
 
 bool pre_transpose(tt_handle_t h, cudaStream_t st, const float*& base, int rows, int K, int& row_stride,
@@ -426,21 +440,51 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g_in)
     if (h->variant == 0 && g.batch_count == 1 && g.batch.red_count == 1) {
         if (g.N >= PRE_T_MIN_N_FOR_A) pre_transpose(h, st, g.a, g.M, g.K, g.aMs, g.aKs, g.ws_off);
         if (g.M >= PRE_T_MIN_M_FOR_B) pre_transpose(h, st, g.b, g.N, g.K, g.bNs, g.bKs, g.ws_off);
+    } else if (h->variant == 0 && g.batch.red_count == 1) {
+        // Batched: an operand whose batch entries lie one after the other as ONE dense K-major
+        // matrix (a single non-broadcast batch axis of stride rows x K) is transposed as that
+        // matrix; its entries then sit side by side along the row axis of the copy.  What the
+        // copy is weighed against is the number of columns (rows) every operand entry meets
+        // over the whole call, i.e. N (M) times the entries of the other operand it is
+        // broadcast against.
+        const auto stacked = [&](const float*& base, int rows, int& row_stride, int& k_stride, int* bstride,
+                                 int other_extent, int min_other) {
+            int ax = -1;
+            for (int i = 0; i < g.batch.rank; i++) {
+                if (bstride[i] == 0) continue;
+                if (ax >= 0) return;                   // more than one batch axis: leave it
+                ax = i;
+            }
+            if (ax < 0 || k_stride != 1 || row_stride != g.K || rows % 4 != 0 ||
+                static_cast<long long>(bstride[ax]) != static_cast<long long>(rows) * g.K)
+                return;
+            const long long total_rows = static_cast<long long>(rows) * g.batch.dims[ax];
+            const long long other_total = static_cast<long long>(other_extent) * (g.batch_count / g.batch.dims[ax]);
+            if (total_rows > (1ll << 30) || other_total < min_other) return;
+            if (pre_transpose(h, st, base, static_cast<int>(total_rows), g.K, row_stride, k_stride, g.ws_off))
+                bstride[ax] = rows;                    // entries are `rows` columns apart in the [K][total rows] copy
+        };
+        stacked(g.a, g.M, g.aMs, g.aKs, g.batch.as, g.N, PRE_T_MIN_N_FOR_A);
+        stacked(g.b, g.N, g.bNs, g.bKs, g.batch.bs, g.M, PRE_T_MIN_M_FOR_B);
     }
     const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
-    SimtPlan plan = plan_simt(h, g.M, g.N, g.K, g.batch_count, ws_avail, g.batch.red_count);
-    if (h->variant == 2 || h->variant == 3) {
-        // pinned tile height (A/B measurements and tests): no split-K
+    const bool b_kmajor = g.bKs == 1 || g.K == 1;      // as operand_view classifies it
+    SimtPlan plan = plan_simt(h, g.M, g.N, g.K, g.batch_count, ws_avail, g.batch.red_count, b_kmajor);
+    if (h->variant == 2 || h->variant == 3 || h->variant == 7) {
+        // pinned tile shape (A/B measurements and tests): no split-K
         plan.tm = h->variant == 2 ? 16 : 8;
+        plan.nj = h->variant == 7 ? 3 : 2;
         plan.splits = 1;
         plan.kps = (g.K + simt::BK - 1) / simt::BK;
         plan.streamk = false;
+        if (plan.nj == 3 && b_kmajor) return TT_ERR_UNSUPPORTED;
     }
     if (h->variant == 6 || g.epi.scatter_rows > 0) {
         // pinned: 256x128 tiles with stream-K (measurements; the scatter epilogue lives in this form)
-        plan.tm = 16; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
+        plan.tm = 16; plan.nj = 2; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
         if (static_cast<size_t>(h->num_sms) * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
+    if (plan.nj == 3) return try_launch_simt_tm<8, 3>(h, st, g, plan);
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
 
@@ -544,7 +588,7 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
             if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
         }
-        if (h->variant == 2 || h->variant == 3 || h->variant == 6 || vol >= TMA_MIN_FLOP_ELEMS) {
+        if (h->variant == 2 || h->variant == 3 || h->variant == 6 || h->variant == 7 || vol >= TMA_MIN_FLOP_ELEMS) {
             const int rc = try_launch_simt(h, st, g);
             if (rc != TT_ERR_UNSUPPORTED) return rc;
         }
@@ -578,12 +622,25 @@ cudaError_t init_simt_tm()
     return init_simt_one<TM, false, false>();
 }
 
+template <bool AK>
+cudaError_t init_simt_wide()
+{
+    const int bytes = simt::Cfg<8, AK, false, 3>::SMEM_BYTES;
+    cudaError_t e = cudaFuncSetAttribute(simt::sgemm_simt_kernel<8, AK, false, simt::MODE_TILES, 3>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(simt::sgemm_simt_kernel<8, AK, false, simt::MODE_STREAMK, 3>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
 cudaError_t init_kernels()
 {
     cudaError_t e = init_simt_tm<8>();
     if (e != cudaSuccess) return e;
     e = init_simt_tm<16>();
     if (e != cudaSuccess) return e;
+    if ((e = init_simt_wide<true>()) != cudaSuccess) return e;
+    if ((e = init_simt_wide<false>()) != cudaSuccess) return e;
     if (mlp_step::init_device() != 0) return cudaErrorUnknown;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
@@ -811,7 +868,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 6) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 7) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }
@@ -894,6 +951,41 @@ TT_API int tt_matmul_batched_reduce(tt_handle_t h, void* stream, const float* a,
     hb.red_count = rc_n; hb.red_as = rc_a; hb.red_bs = rc_b;
     GemmCall g{a, b, c, M, N, K, aMs, aKs, bKs, bNs, hb, static_cast<int>(kept), Epilogue{nullptr, TT_ACT_NONE}};
     return run_gemm(h, static_cast<cudaStream_t>(stream), g);
+}
+
+TT_API int tt_reduce_sum_axes(tt_handle_t h, void* stream, const float* src, float* dst, int rank,
+                              const int* dims, const int* reduceAxis)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    if (rank < 0 || rank > 8 || (rank > 0 && (!dims || !reduceAxis))) return fail(h, TT_ERR_INVALID_ARG, "bad reduction rank");
+    ew::ReduceAxes ax;
+    memset(&ax, 0, sizeof(ax));
+    long long n_out = 1, n_red = 1, stride = 1;
+    long long strides[8];
+    for (int i = rank - 1; i >= 0; i--) {
+        if (dims[i] < 0) return fail(h, TT_ERR_INVALID_ARG, "negative dimension");
+        strides[i] = stride;
+        stride *= dims[i];
+    }
+    for (int i = 0; i < rank; i++) {
+        if (reduceAxis[i]) {
+            ax.red_dim[ax.n_red] = dims[i]; ax.red_stride[ax.n_red] = strides[i]; ax.n_red++;
+            n_red *= dims[i];
+        } else {
+            ax.kept_dim[ax.n_kept] = dims[i]; ax.kept_stride[ax.n_kept] = strides[i]; ax.n_kept++;
+            n_out *= dims[i];
+        }
+    }
+    if (n_out > 0 && (!dst || (n_red > 0 && !src))) return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    TT_BIND(h);
+    h->stats.calls++;
+    if (n_out == 0) return TT_OK;
+    ew::reduce_axes_kernel<<<static_cast<unsigned int>((n_out + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        src, dst, ax, n_out, n_red);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "reduction launch");
+    return TT_OK;
 }
 
 TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* bias,

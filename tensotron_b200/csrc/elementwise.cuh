@@ -218,6 +218,41 @@ clip_scale_kernel(float* __restrict__ g, const float* __restrict__ sumsq, long l
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) g[i] *= coef;
 }
 
+// dst[kept...] = sum over the reduced axes of src, each output by one thread that walks the reduced
+// index space in row-major (ascending) order: ReduceGradToShape
+// (src/Tensotron/TensorOps.cs:76-100) without its atomic chunked reduction.  Up to 8 axes;
+// kept / red: extents and source strides (elements) of the kept and of the reduced axes.
+struct ReduceAxes {
+    int n_kept, n_red;
+    int kept_dim[8], red_dim[8];
+    long long kept_stride[8], red_stride[8];
+};
+
+static __global__ void __launch_bounds__(256)
+reduce_axes_kernel(const float* __restrict__ src, float* __restrict__ dst, ReduceAxes ax, long long n_out,
+                   long long n_red)
+{
+    const long long o = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (o >= n_out) return;
+    long long rem = o, base = 0;
+    for (int i = ax.n_kept - 1; i >= 0; i--) {
+        const long long c = rem % ax.kept_dim[i];
+        rem /= ax.kept_dim[i];
+        base += c * ax.kept_stride[i];
+    }
+    float t = 0.f;
+    for (long long r = 0; r < n_red; r++) {
+        long long q = r, off = base;
+        for (int i = ax.n_red - 1; i >= 0; i--) {
+            const long long c = q % ax.red_dim[i];
+            q /= ax.red_dim[i];
+            off += c * ax.red_stride[i];
+        }
+        t += src[off];
+    }
+    dst[o] = t;
+}
+
 // adv = [t, 1/(1-b1^t), 1/(1-b2^t)]; one thread.
 static __global__ void adam_advance_kernel(float* adv, float b1, float b2)
 {

@@ -20,11 +20,14 @@
 // No atomics and no flag spinning anywhere: the only cross-CTA synchronisation is the hardware
 // cluster barrier, and all CTAs of a cluster are co-scheduled by construction.
 //
-// Every small product is C[i][j] = sum_l P[l][i] * Q[l][j] on operands stored with the contraction
-// index outermost, so a thread reads 2 + 4 consecutive values per l and does 8 FMAs, in ascending l
-// (one accumulator per output, fused multiply-add: the same summation rule as the large kernels).
-// That needs each activation and each gradient in both orientations, which the producing
-// product writes for free from its 2 x 4 register block.
+// Every operand keeps its natural row-major layout in shared memory; the only transposed copy is
+// W^T (made once per launch), which the forward pass needs.  A thread owns 2 x 4 output blocks and
+// walks the contraction index l in ascending order with one accumulator per output and fused
+// multiply-adds (the summation rule of the large kernels).  Two forms cover the three products:
+//   rows form   C[i][j] = sum_l P[i][l] * Q[l][j]   forward (x, W^T) and dX (g, W)
+//   outer form  C[i][j] = sum_l P[l][i] * Q[l][j]   dW (g, x)
+// Lanes of a warp differ in the column block j first, so the Q reads and the float4 stores of the
+// results are contiguous and free of bank conflicts, and the P reads are broadcasts.
 #include "../../include/tensotron_gemm.h"
 
 #include <cooperative_groups.h>
@@ -51,14 +54,18 @@ struct Plan {
     int rp;
     int total;                // floats of the flat parameter buffer (mlp layout: W_l (out,in), b_l, padded to 4)
     int w_off[MAX_LAYERS], b_off[MAX_LAYERS];   // flat offsets
+    int k_magic[MAX_LAYERS];  // floor(2^20 / K_l) + 1: (rel * magic) >> 20 == rel / K_l for rel < 4096, K_l <= 64
     // shared-memory offsets
-    int s_w[MAX_LAYERS];      // W_l natural  [N][Kp]
-    int s_wt[MAX_LAYERS];     // W_l^T        [K][Np]
+    int s_w[MAX_LAYERS];      // W_l      [N][Kp]
+    int s_wt[MAX_LAYERS];     // W_l^T    [K][Np + 4]  (the extra 4 floats of pitch keep the transposing stores
+                              //                         of 8 consecutive k in 8 different bank groups)
+    int s_par;                // the parameters as loaded, flat layout [total] (biases; Adam's p)
     int s_grad;               // partial gradients, flat layout [total]
-    int s_act[MAX_LAYERS + 1];   // activation l natural [rp][Dp_l]   (l = 0: the input)
-    int s_actt[MAX_LAYERS + 1];  // activation l transposed [D_l][rp]
-    int s_g[2], s_gt[2];      // gradient ping-pong: natural [rp][Wp], transposed [W][rp], W = widest layer output
-    int s_red;                // 64 floats: block-reduction scratch; [32..48) this CTA's published partial sums
+    int s_act[MAX_LAYERS + 1];   // activation l [rp][Dp_l]   (l = 0: the input)
+    int s_g[2];               // gradient ping-pong [rp][gw], gw = widest padded layer output
+    int gw;
+    int s_red;                // 64 floats: block-reduction scratch [0, 32); [32 + 2r], [33 + 2r]: loss and
+                              // sum-of-squares parts received from CTA r
     int floats;               // total shared floats
 };
 
@@ -75,6 +82,7 @@ inline Plan make_plan(const tt_mlp_desc& net, int rows)
     int cur = 0;
     for (int l = 0; l < net.n_layers; l++) {
         p.w_off[l] = cur;
+        p.k_magic[l] = (1 << 20) / net.dims[l] + 1;
         cur += net.dims[l + 1] * net.dims[l];
         p.b_off[l] = cur;
         cur += net.dims[l + 1];
@@ -84,18 +92,18 @@ inline Plan make_plan(const tt_mlp_desc& net, int rows)
     int off = 0, widest = 4;
     for (int l = 0; l < net.n_layers; l++) {
         const int K = net.dims[l], N = net.dims[l + 1];
-        p.s_w[l] = off;  off += N * pad4(K);
-        p.s_wt[l] = off; off += K * pad4(N);
+        p.s_w[l] = off;  off += pad4(N) * pad4(K);
+        p.s_wt[l] = off; off += pad4(K) * (pad4(N) + 4);
         if (pad4(N) > widest) widest = pad4(N);
     }
+    p.s_par = off; off += p.total;
     p.s_grad = off; off += p.total;
     for (int l = 0; l <= net.n_layers; l++) {
         p.s_act[l] = off;  off += p.rp * pad4(net.dims[l]);
-        p.s_actt[l] = off; off += net.dims[l] * p.rp;
     }
+    p.gw = widest;
     for (int i = 0; i < 2; i++) {
         p.s_g[i] = off;  off += p.rp * widest;
-        p.s_gt[i] = off; off += widest * p.rp;
     }
     p.s_red = off; off += 64;
     p.floats = off;
@@ -125,21 +133,21 @@ __device__ __forceinline__ float act_fwd(float v, int act)
     return v;
 }
 
-// C[i][j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending, one accumulator
-// per output, fused multiply-add).  ldp >= pad-to-2(I), ldq >= pad4(J), both buffers readable (zero
-// or finite) up to those paddings.  Each thread owns 2 x 4 output blocks; `emit(i, j, value)` is
-// called for every in-range output.
+// Outer form: C[i][j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending, one
+// accumulator per output, fused multiply-add).  ldp >= I rounded up to 2, ldq >= J rounded up to 4;
+// what lies in those roundings may be anything, it only reaches outputs that are not emitted.
+// `emit(i, j0, acc)` receives row i (< I) and the four columns j0 .. j0 + 3 (the caller masks j >= J).
 template <typename Emit>
-__device__ __forceinline__ void small_gemm(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
+__device__ __forceinline__ void gemm_outer(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
                                            int I, int J, int L, Emit emit)
 {
     const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
-        const int ib = blk % ib_n, jb = blk / ib_n;
+        const int jb = blk % jb_n, ib = blk / jb_n;
         const float* pp = P + 2 * ib;
         const float* qq = Q + 4 * jb;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
+#pragma unroll 8
         for (int l = 0; l < L; l++) {
             const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
             const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
@@ -148,13 +156,49 @@ __device__ __forceinline__ void small_gemm(const float* __restrict__ P, int ldp,
             acc[1][0] = fmaf(a.y, b.x, acc[1][0]); acc[1][1] = fmaf(a.y, b.y, acc[1][1]);
             acc[1][2] = fmaf(a.y, b.z, acc[1][2]); acc[1][3] = fmaf(a.y, b.w, acc[1][3]);
         }
-#pragma unroll
-        for (int di = 0; di < 2; di++)
-#pragma unroll
-            for (int dj = 0; dj < 4; dj++) {
-                const int i = 2 * ib + di, j = 4 * jb + dj;
-                if (i < I && j < J) emit(i, j, acc[di][dj]);
-            }
+        emit(2 * ib, 4 * jb, acc[0]);
+        if (2 * ib + 1 < I) emit(2 * ib + 1, 4 * jb, acc[1]);
+    }
+}
+
+// Rows form: C[i][j] = sum_l P[i * ldp + l] * Q[l * ldq + j], same rules.  The P rows are read four l
+// at a time (ldp a multiple of 4); the l beyond a multiple of 4 are done one by one, so nothing past
+// L enters a sum.  Rows i >= I of P are read (into results that are not emitted): P must have
+// I rounded up to 2 rows.
+template <typename Emit>
+__device__ __forceinline__ void gemm_rows(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
+                                          int I, int J, int L, Emit emit)
+{
+    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
+    const int L4 = L & ~3;
+    for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
+        const int jb = blk % jb_n, ib = blk / jb_n;
+        const float* p0 = P + (2 * ib) * ldp;
+        const float* p1 = p0 + ldp;
+        const float* qq = Q + 4 * jb;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const auto step = [&](float a0, float a1, const float4 b) {
+            acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
+            acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
+            acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
+            acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+        };
+#pragma unroll 2
+        for (int l = 0; l < L4; l += 4) {
+            const float4 a0 = *reinterpret_cast<const float4*>(p0 + l);
+            const float4 a1 = *reinterpret_cast<const float4*>(p1 + l);
+            const float4 b0 = *reinterpret_cast<const float4*>(qq + l * ldq);
+            const float4 b1 = *reinterpret_cast<const float4*>(qq + (l + 1) * ldq);
+            const float4 b2 = *reinterpret_cast<const float4*>(qq + (l + 2) * ldq);
+            const float4 b3 = *reinterpret_cast<const float4*>(qq + (l + 3) * ldq);
+            step(a0.x, a1.x, b0);
+            step(a0.y, a1.y, b1);
+            step(a0.z, a1.z, b2);
+            step(a0.w, a1.w, b3);
+        }
+        for (int l = L4; l < L; l++) step(p0[l], p1[l], *reinterpret_cast<const float4*>(qq + l * ldq));
+        emit(2 * ib, 4 * jb, acc[0]);
+        if (2 * ib + 1 < I) emit(2 * ib + 1, 4 * jb, acc[1]);
     }
 }
 
@@ -183,24 +227,57 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     const int L = p.n_layers, rp = p.rp;
     const int row0 = c * p.rows;                                  // first batch row of this CTA
     const int nrows = max(0, min(p.rows, a.batch - row0));        // rows that exist
+    const int NO = p.dims[L], NOp = pad4(NO);
+    // Global loads whose values are needed late are issued first, so their latency hides behind
+    // the set-up: the optimizer's step state, and each thread's first loss target.
+    const float adv_t = a.adv[0], adv_ibc1 = a.adv[1], adv_ibc2 = a.adv[2];
+    float tgt_first = 0.f;
+    int label_first = 0;
+    if (p.loss == TT_LOSS_MSE) {
+        if (tid < nrows * NO) tgt_first = static_cast<const float*>(a.target)[static_cast<long long>(row0) * NO + tid];
+    } else if (tid < nrows) {
+        label_first = static_cast<const int*>(a.target)[row0 + tid];
+    }
 
-    // ---- 1. clear, load parameters (both orientations) and the input rows -------------------
-    for (int i = tid; i < p.floats; i += THREADS) s[i] = 0.f;
-    __syncthreads();
-    // parameters: 128-bit loads over the flat buffer (all in flight at once), each element
-    // scattered into the natural and the transposed copy of its weight matrix
-    for (int i4 = tid; i4 < (p.total >> 2); i4 += THREADS) {
-        const float4 q = reinterpret_cast<const float4*>(a.params)[i4];
-        const float e[4] = {q.x, q.y, q.z, q.w};
+    // ---- 1. load the parameters and the input rows ------------------------------------------
+    // Only the gradient buffer has to start at zero (its padding floats between the layers are
+    // summed like everything else).  The paddings of the operand tiles may hold anything: a
+    // product reads them only into outputs that are never emitted.
+    for (int i = tid; i < p.total; i += THREADS) s[p.s_grad + i] = 0.f;
+    // parameters: 128-bit loads over the flat buffer (all in flight at once) into the flat copy
+    // and into the row-major weight matrices
+    constexpr int PAR_BATCH = 8;          // float4 loads per thread issued before the first is used
+    for (int base4 = 0; base4 < (p.total >> 2); base4 += THREADS * PAR_BATCH) {
+        float4 qs[PAR_BATCH];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int flat = 4 * i4 + j;
+        for (int u = 0; u < PAR_BATCH; u++) {
+            const int i4 = base4 + u * THREADS + tid;
+            if (i4 < (p.total >> 2)) qs[u] = reinterpret_cast<const float4*>(a.params)[i4];
+        }
+#pragma unroll
+        for (int u = 0; u < PAR_BATCH; u++) {
+            const int i4 = base4 + u * THREADS + tid;
+            if (i4 >= (p.total >> 2)) continue;
+            const float4 q = qs[u];
+            reinterpret_cast<float4*>(s + p.s_par)[i4] = q;
+            const float e[4] = {q.x, q.y, q.z, q.w};
+            const int flat = 4 * i4;
             for (int l = 0; l < L; l++) {
-                if (flat >= p.w_off[l] && flat < p.b_off[l]) {
-                    const int K = p.dims[l], rel = flat - p.w_off[l];
-                    const int n = rel / K, k = rel - n * K;
-                    s[p.s_w[l] + n * pad4(K) + k] = e[j];
-                    s[p.s_wt[l] + k * pad4(p.dims[l + 1]) + n] = e[j];
+                if (flat + 3 < p.w_off[l] || flat >= p.b_off[l]) continue;
+                const int K = p.dims[l], Kp = pad4(K);
+                if ((K & 3) == 0 && flat >= p.w_off[l] && flat + 3 < p.b_off[l]) {
+                    // the four floats are four consecutive k of one row
+                    const int rel = flat - p.w_off[l];
+                    const int n = static_cast<int>((static_cast<unsigned int>(rel) * static_cast<unsigned int>(p.k_magic[l])) >> 20);
+                    *reinterpret_cast<float4*>(s + p.s_w[l] + n * Kp + (rel - n * K)) = q;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int rel = flat + j - p.w_off[l];
+                        if (rel < 0 || flat + j >= p.b_off[l]) continue;
+                        const int n = static_cast<int>((static_cast<unsigned int>(rel) * static_cast<unsigned int>(p.k_magic[l])) >> 20);
+                        s[p.s_w[l] + n * Kp + (rel - n * K)] = e[j];
+                    }
                 }
             }
         }
@@ -209,36 +286,51 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const int K = p.dims[0], Kp = pad4(K);
         for (int i = tid; i < nrows * K; i += THREADS) {
             const int r = i / K, k = i - r * K;
-            const float val = a.x[static_cast<long long>(row0 + r) * K + k];
-            s[p.s_act[0] + r * Kp + k] = val;
-            s[p.s_actt[0] + k * rp + r] = val;
+            s[p.s_act[0] + r * Kp + k] = a.x[static_cast<long long>(row0) * K + i];
+        }
+    }
+    __syncthreads();
+    // W^T for the forward pass: thread <-> (k, four rows n): four reads down a column of W (lanes on
+    // consecutive k), one 128-bit store into row k of W^T
+    for (int l = 0; l < L; l++) {
+        const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Npt = pad4(N) + 4, n4_n = (N + 3) >> 2;
+        const float* w = s + p.s_w[l];
+        float* wt = s + p.s_wt[l];
+        for (int i = tid; i < K * n4_n; i += THREADS) {
+            const int n4 = i / K, k = i - n4 * K;
+            float4 v;
+            v.x = w[(4 * n4) * Kp + k];
+            v.y = 4 * n4 + 1 < N ? w[(4 * n4 + 1) * Kp + k] : 0.f;
+            v.z = 4 * n4 + 2 < N ? w[(4 * n4 + 2) * Kp + k] : 0.f;
+            v.w = 4 * n4 + 3 < N ? w[(4 * n4 + 3) * Kp + k] : 0.f;
+            *reinterpret_cast<float4*>(wt + k * Npt + 4 * n4) = v;
         }
     }
     __syncthreads();
 
     // ---- 2a. forward ------------------------------------------------------------------------
     for (int l = 0; l < L; l++) {
-        const int K = p.dims[l], N = p.dims[l + 1], Np = pad4(N);
-        const float* bias = a.params + p.b_off[l];
+        const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Np = pad4(N);
+        const float* bias = s + p.s_par + p.b_off[l];
         const int act = l + 1 < L ? p.act : TT_ACT_NONE;
         float* y = s + p.s_act[l + 1];
-        float* yt = s + p.s_actt[l + 1];
-        // y[r][n] = sum_k x^T[k][r] * W^T[k][n]
-        small_gemm(s + p.s_actt[l], rp, s + p.s_wt[l], Np, nrows, N, K, [&](int r, int n, float v) {
-            v = act_fwd(v + __ldg(bias + n), act);
-            y[r * Np + n] = v;
-            yt[n * rp + r] = v;
+        // y[r][n] = sum_k x[r][k] * W^T[k][n]
+        gemm_rows(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, [&](int r, int n0, const float* acc) {
+            float4 v;
+            v.x = act_fwd(acc[0] + bias[n0], act);
+            v.y = n0 + 1 < N ? act_fwd(acc[1] + bias[n0 + 1], act) : 0.f;
+            v.z = n0 + 2 < N ? act_fwd(acc[2] + bias[n0 + 2], act) : 0.f;
+            v.w = n0 + 3 < N ? act_fwd(acc[3] + bias[n0 + 3], act) : 0.f;
+            *reinterpret_cast<float4*>(y + r * Np + n0) = v;
         });
         __syncthreads();
     }
 
     // ---- 2b. loss and its gradient w.r.t. the network output ---------------------------------
-    const int NO = p.dims[L], NOp = pad4(NO);
     const float* out = s + p.s_act[L];
     int gcur = 0;                         // ping-pong index of the current upstream gradient
     float* g = s + p.s_g[gcur];
-    float* gt = s + p.s_gt[gcur];
-    const int gw = (p.s_gt[0] - p.s_g[0]) / rp;   // row pitch of the natural gradient buffers
+    const int gw = p.gw;                  // row pitch of the gradient buffers
     float loss_part = 0.f;
     if (p.loss == TT_LOSS_MSE) {
         // mean over batch x outputs of (o - t)^2; d/do = 2 (o - t) / count   (TensorOps.Losses.cs:29-61)
@@ -246,11 +338,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const float inv = 1.f / (static_cast<float>(a.batch) * static_cast<float>(NO));
         for (int i = tid; i < nrows * NO; i += THREADS) {
             const int r = i / NO, n = i - r * NO;
-            const float d = out[r * NOp + n] - tgt[static_cast<long long>(row0 + r) * NO + n];
+            const float d = out[r * NOp + n] - (i == tid ? tgt_first : tgt[static_cast<long long>(row0) * NO + i]);
             loss_part += d * d;
-            const float gv = (2.f * inv) * d;
-            g[r * gw + n] = gv;
-            gt[n * rp + r] = gv;
+            g[r * gw + n] = (2.f * inv) * d;
         }
         loss_part *= inv;
     } else {
@@ -263,20 +353,16 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
             float se = 0.f;
             for (int n = 0; n < NO; n++) se += expf(out[r * NOp + n] - mx);
             const float lse = logf(se) + mx;
-            const int label = labels[row0 + r];
+            const int label = r == tid ? label_first : labels[row0 + r];
             const bool ok = label >= 0 && label < NO;
             if (!ok && a.status) atomicCAS(a.status, 0u, 7u);
             loss_part += ok ? -(out[r * NOp + label] - lse) * inv : __int_as_float(0x7fc00000);
-            for (int n = 0; n < NO; n++) {
-                const float gv = (expf(out[r * NOp + n] - lse) - (n == label ? 1.f : 0.f)) * inv;
-                g[r * gw + n] = gv;
-                gt[n * rp + r] = gv;
-            }
+            for (int n = 0; n < NO; n++)
+                g[r * gw + n] = (expf(out[r * NOp + n] - lse) - (n == label ? 1.f : 0.f)) * inv;
         }
     }
     float* red = s + p.s_red;
     const float loss_cta = block_sum(loss_part, red);
-    if (tid == 0) red[32] = loss_cta;     // published: CTA 0 adds the CTAs' parts in rank order
     __syncthreads();
 
     // ---- 2c. backward -------------------------------------------------------------------------
@@ -285,42 +371,61 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K);
         // dW[n][k] = sum_r g[r][n] * x[r][k]
         float* dw = grad + p.w_off[l];
-        small_gemm(g, gw, s + p.s_act[l], Kp, N, K, nrows, [&](int n, int k, float v) { dw[n * K + k] = v; });
+        gemm_outer(g, gw, s + p.s_act[l], Kp, N, K, nrows, [&](int n, int k0, const float* acc) {
+            float* d = dw + n * K + k0;
+            if ((K & 3) == 0) {
+                *reinterpret_cast<float4*>(d) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+                d[0] = acc[0];
+                if (k0 + 1 < K) d[1] = acc[1];
+                if (k0 + 2 < K) d[2] = acc[2];
+                if (k0 + 3 < K) d[3] = acc[3];
+            }
+        });
         // db[n] = sum_r g[r][n], ascending r
         float* db = grad + p.b_off[l];
         for (int n = tid; n < N; n += THREADS) {
             float t = 0.f;
+#pragma unroll 8
             for (int r = 0; r < nrows; r++) t += g[r * gw + n];
             db[n] = t;
         }
         if (l > 0) {
-            // dx[r][k] = sum_n g^T[n][r] * W[n][k], then through the activation of layer l - 1
+            // dx[r][k] = sum_n g[r][n] * W[n][k], then through the activation of layer l - 1
             const float* h = s + p.s_act[l];
             float* gn = s + p.s_g[gcur ^ 1];
-            float* gnt = s + p.s_gt[gcur ^ 1];
             const int act = p.act;
-            small_gemm(gt, rp, s + p.s_w[l], Kp, nrows, K, N, [&](int r, int k, float v) {
-                const float y = h[r * Kp + k];
-                v = ew::act_grad(y, v, act);
-                gn[r * gw + k] = v;
-                gnt[k * rp + r] = v;
+            gemm_rows(g, gw, s + p.s_w[l], Kp, nrows, K, N, [&](int r, int k0, const float* acc) {
+                const float4 y = *reinterpret_cast<const float4*>(h + r * Kp + k0);
+                *reinterpret_cast<float4*>(gn + r * gw + k0) =
+                    make_float4(ew::act_grad(y.x, acc[0], act), ew::act_grad(y.y, acc[1], act),
+                                ew::act_grad(y.z, acc[2], act), ew::act_grad(y.w, acc[3], act));
             });
             __syncthreads();
             gcur ^= 1;
             g = gn;
-            gt = gnt;
         }
     }
     __syncthreads();
 
     // ---- 3. cluster-wide gradient sum (slice per CTA), gradient norm ---------------------------
-    cluster.sync();
     const int total4 = p.total >> 2;
     const int per4 = (total4 + C - 1) / C;
     const int lo4 = min(total4, c * per4), hi4 = min(total4, lo4 + per4);
+    constexpr int MAX_OWN = 8;            // float4s per thread: per4 <= THREADS * MAX_OWN (checked on the host)
+    // this thread's Adam moments: requested now, used after the two cluster barriers
+    float4 own_m[MAX_OWN], own_v[MAX_OWN];
+#pragma unroll
+    for (int u = 0; u < MAX_OWN; u++) {
+        const int i = lo4 + tid + u * THREADS;
+        if (i < hi4) {
+            own_m[u] = reinterpret_cast<const float4*>(a.m)[i];
+            own_v[u] = reinterpret_cast<const float4*>(a.v)[i];
+        }
+    }
+    cluster.sync();
     float sq = 0.f;
     // every thread keeps its elements' summed gradients in registers across the second barrier
-    constexpr int MAX_OWN = 8;            // float4s per thread: per4 <= THREADS * MAX_OWN (checked on the host)
     float4 own[MAX_OWN];
 #pragma unroll
     for (int u = 0; u < MAX_OWN; u++) {
@@ -336,13 +441,20 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         own[u] = sum;
     }
     const float sq_cta = block_sum(sq, red);
-    if (tid == 0) red[33] = sq_cta;
+    // Every CTA hands its two partial sums (loss, sum of squares of its slice) to every CTA of the
+    // cluster: thread r stores them into slot c of CTA r's shared memory.  After the barrier each
+    // CTA adds the slots it holds in rank order, and nothing reads another CTA's shared memory any
+    // more, so a CTA may finish while the others are still in their Adam loops.
+    if (tid < C) {
+        float* rr = cluster.map_shared_rank(red, tid);
+        rr[32 + 2 * c] = loss_cta;
+        rr[33 + 2 * c] = sq_cta;
+    }
     cluster.sync();
     float total_sq = 0.f, loss_total = 0.f;
     for (int r = 0; r < C; r++) {
-        const float* rr = cluster.map_shared_rank(red, r);
-        loss_total += rr[32];
-        total_sq += rr[33];
+        loss_total += red[32 + 2 * r];
+        total_sq += red[33 + 2 * r];
     }
     float coef = 1.f;
     if (a.max_norm > 0.f) {
@@ -352,7 +464,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     if (c == 0 && tid == 0 && a.loss_out) *a.loss_out = loss_total;
 
     // ---- 4. Adam on this CTA's slice ------------------------------------------------------------
-    float t = a.adv[0], ibc1 = a.adv[1], ibc2 = a.adv[2];
+    float t = adv_t, ibc1 = adv_ibc1, ibc2 = adv_ibc2;
     if (a.advance) {
         t += 1.f;
         ibc1 = 1.f / (1.f - powf(a.b1, t));
@@ -365,9 +477,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         if (i >= hi4) continue;
         float4 gg = own[u];
         if (a.max_norm > 0.f) { gg.x *= coef; gg.y *= coef; gg.z *= coef; gg.w *= coef; }
-        float4 pp = reinterpret_cast<const float4*>(a.params)[i];
-        float4 mm = reinterpret_cast<const float4*>(a.m)[i];
-        float4 vv = reinterpret_cast<const float4*>(a.v)[i];
+        float4 pp = reinterpret_cast<const float4*>(s + p.s_par)[i];
+        float4 mm = own_m[u];
+        float4 vv = own_v[u];
         ew::adam_one(pp.x, gg.x, mm.x, vv.x, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
         ew::adam_one(pp.y, gg.y, mm.y, vv.y, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
         ew::adam_one(pp.z, gg.z, mm.z, vv.z, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
@@ -377,9 +489,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         reinterpret_cast<float4*>(a.v)[i] = vv;
         if (a.grads_out) reinterpret_cast<float4*>(a.grads_out)[i] = gg;
     }
-    // Nobody leaves while another CTA may still read its shared memory; the step counter is
-    // written after every CTA has read it.
-    cluster.sync();
+    // (every CTA read the step state into registers before the first cluster barrier)
     if (c == 0 && tid == 0 && a.advance) {
         a.adv[0] = t;
         a.adv[1] = ibc1;
@@ -427,7 +537,9 @@ int launch(cudaStream_t st, const tt_mlp_desc* net, float* params, float* m, flo
     if (batch < 1 || batch > g_max_cluster * MAX_ROWS) return TT_ERR_UNSUPPORTED;
     // Cluster size: about 16 rows per CTA up to the largest cluster, then more rows per CTA.  The
     // choice depends on the batch only, so the summation order does too.
-    int C = 1;
+    // At least four CTAs: the optimizer part (a slice of the parameters per CTA) is worth
+    // spreading even when one CTA holds all the rows.
+    int C = g_max_cluster < 4 ? g_max_cluster : 4;
     while (C < g_max_cluster && batch > 16 * C) C *= 2;
     int rows = (batch + C - 1) / C;
     Plan plan = make_plan(*net, rows);

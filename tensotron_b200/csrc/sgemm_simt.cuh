@@ -57,9 +57,14 @@ __device__ __forceinline__ void consumer_sync()
     asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
 }
 
-template <int TM, bool A_KMAJ, bool B_KMAJ>
+// NJ = tile width in units of 64 columns: 2 (128 columns, 8 per thread) or 3 (192 columns, 12 per
+// thread; TM = 8 and MN-major B only -- a 192-column K-major tile has no transposition routine).
+// The 192-wide tile exists for N = 192-like shapes, where 128-wide tiles are a quarter padding.
+template <int TM, bool A_KMAJ, bool B_KMAJ, int NJ = 2>
 struct Cfg {
+    static_assert(NJ == 2 || (NJ == 3 && TM == 8 && !B_KMAJ), "tile width");
     static constexpr int BM = 16 * TM;
+    static constexpr int BN = 64 * NJ;
     static constexpr int RAW_A = BM * BK * 4;
     static constexpr int RAW_B = BN * BK * 4;
     static constexpr int STAGE_BYTES = RAW_A + RAW_B;
@@ -170,13 +175,14 @@ __device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst,
 //                starts (it is bounded like every other wait).
 constexpr int MODE_TILES = 0, MODE_SPLITK = 1, MODE_STREAMK = 2;
 
-template <int TM, bool A_KMAJ, bool B_KMAJ, int MODE>
+template <int TM, bool A_KMAJ, bool B_KMAJ, int MODE, int NJ = 2>
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b, const Params p)
 {
-    using C = Cfg<TM, A_KMAJ, B_KMAJ>;
+    using C = Cfg<TM, A_KMAJ, B_KMAJ, NJ>;
     constexpr int STAGES = C::STAGES;
+    constexpr int BN = C::BN;      // this instantiation's tile width (shadows the 128-column default)
     constexpr int HALVES = TM / 8;  // 8-row halves of the thread tile
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment.
@@ -274,9 +280,9 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     // Transposes the K-major tiles of TMA stage `s` into transposed buffer `tb`.
     auto transpose_stage = [&](uint32_t s, uint32_t tb) {
         const uint8_t* raw = smem + s * C::STAGE_BYTES;
-        if (A_KMAJ)
+        if constexpr (A_KMAJ)
             transpose_tile<C::BM, C::ROWB_A>(raw, smem + C::OFF_TA + tb * C::TA_BYTES, warp, lane);
-        if (B_KMAJ)
+        if constexpr (B_KMAJ)
             transpose_tile<BN, C::ROWB_B>(raw + C::RAW_A, smem + C::OFF_TB + tb * C::TB_BYTES, warp, lane);
     };
 
@@ -301,7 +307,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const int tx = lane & 7;
     constexpr int WROWS = C::BM / 4;  // rows per warp: 32 (TM=8) or 64 (TM=16)
     const int off_am = (wm * WROWS + ty * 4) * 4;
-    const int off_bm = (wn * 64 + tx * 4) * 4;
+    const int off_bm = (wn * (32 * NJ) + tx * 4) * 4;
 
     for (long long w = w_begin; w < w_end;) {
         long long unit;
@@ -332,11 +338,11 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         // so neither operand has to be broadcast into both halves of a register pair;
         // only the swapped column pair is built.  Each lane is an independent IEEE fma
         // in ascending k, so the bits equal the scalar-FMA formulation.
-        float2 d0[TM / 2][4], d1[TM / 2][4];
+        float2 d0[TM / 2][2 * NJ], d1[TM / 2][2 * NJ];
 #pragma unroll
         for (int i = 0; i < TM / 2; i++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
+            for (int j = 0; j < 2 * NJ; j++) d0[i][j] = d1[i][j] = make_float2(0.f, 0.f);
 
         const int iters = (ke - kb) * p.batch.red_count;  // k-tiles x entries of the reduced axis
 #pragma unroll 1
@@ -353,11 +359,11 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             const auto k_group = [&](int g) {  // one group of KG k-steps
                 const uint8_t* sag = sa + g * KG * C::ROWB_A;
                 const uint8_t* sbg = sb + g * KG * C::ROWB_B;
-                float4 bm[KG][2];  // [k][half] = 4 adjacent cols
+                float4 bm[KG][NJ];  // [k][32-column block] = 4 adjacent cols
 #pragma unroll
                 for (int kk = 0; kk < KG; kk++)
 #pragma unroll
-                    for (int jb = 0; jb < 2; jb++)
+                    for (int jb = 0; jb < NJ; jb++)
                         bm[kk][jb] = *reinterpret_cast<const float4*>(sbg + kk * C::ROWB_B + jb * 128);
 #pragma unroll
                 for (int h = 0; h < HALVES; h++) {
@@ -370,14 +376,14 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                                 sag + kk * C::ROWB_A + (h * 32 + ib * 16) * 4);
 #pragma unroll
                     for (int kk = 0; kk < KG; kk++) {
-                        float2 a2[4], b2[4], b2s[4];
+                        float2 a2[4], b2[2 * NJ], b2s[2 * NJ];
 #pragma unroll
                         for (int pr = 0; pr < 4; pr++) {  // row pairs of this half
                             const float4 v = am[kk][pr >> 1];
                             a2[pr] = (pr & 1) ? make_float2(v.z, v.w) : make_float2(v.x, v.y);
                         }
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {  // column pairs
+                        for (int q = 0; q < 2 * NJ; q++) {  // column pairs
                             const float4 v = bm[kk][q >> 1];
                             b2[q] = (q & 1) ? make_float2(v.z, v.w) : make_float2(v.x, v.y);
                             b2s[q] = make_float2(b2[q].y, b2[q].x);
@@ -385,7 +391,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                         for (int pr = 0; pr < 4; pr++)
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
+                            for (int q = 0; q < 2 * NJ; q++) {
                                 d0[h * 4 + pr][q] = __ffma2_rn(a2[pr], b2[q], d0[h * 4 + pr][q]);
                                 d1[h * 4 + pr][q] = __ffma2_rn(a2[pr], b2s[q], d1[h * 4 + pr][q]);
                             }
@@ -450,8 +456,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                         float* crow = cmat + static_cast<long long>(r) * p.shape.N;
                         const int ai = h * 8 + ib * 4 + i;
 #pragma unroll
-                        for (int jb = 0; jb < 2; jb++) {
-                            const int lc = wn * 64 + jb * 32 + tx * 4;
+                        for (int jb = 0; jb < NJ; jb++) {
+                            const int lc = wn * (32 * NJ) + jb * 32 + tx * 4;
                             const int cidx = tn * BN + lc;
                             float v[4];
 #pragma unroll
@@ -521,8 +527,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                                     const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
                                     const int ai = h * 8 + ib * 4 + i;
     #pragma unroll
-                                    for (int jb = 0; jb < 2; jb++) {
-                                        const int lc = wn * 64 + jb * 32 + tx * 4;
+                                    for (int jb = 0; jb < NJ; jb++) {
+                                        const int lc = wn * (32 * NJ) + jb * 32 + tx * 4;
                                         const float4 q = __ldcg(reinterpret_cast<const float4*>(src + lr * BN + lc));
                                         acc_ref(ai, jb * 4 + 0) += q.x;
                                         acc_ref(ai, jb * 4 + 1) += q.y;
@@ -559,8 +565,8 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                         float* crow = base + static_cast<long long>(lr) * ld;
                         const int ai = h * 8 + ib * 4 + i;
     #pragma unroll
-                        for (int jb = 0; jb < 2; jb++) {
-                            const int lc = wn * 64 + jb * 32 + tx * 4;
+                        for (int jb = 0; jb < NJ; jb++) {
+                            const int lc = wn * (32 * NJ) + jb * 32 + tx * 4;
                             float v[4];
     #pragma unroll
                             for (int j = 0; j < 4; j++) v[j] = acc_at(ai, jb * 4 + j);

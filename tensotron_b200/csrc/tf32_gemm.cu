@@ -376,6 +376,8 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t acc = 0, acc_phase = 0;
         const float* bias = p.epi.bias;
         const int act = p.epi.act;
+        const bool plain = bias == nullptr && act == 0;
+        const bool bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
         uint8_t* const out_blocks = smem + C::OFF_OUT + ew * C::OUT_WARP_BYTES;
         uint32_t out_buf = 0;   // staging block of the next 32 x 32 block (alternates when there are two)
         for (long long w = blockIdx.x; w < p.shape.work; w += gridDim.x) {
@@ -398,18 +400,42 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (C::EPI_BUFS == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
                 }
                 __syncwarp();   // the previous reads of this staging block are done
+                // Stage the block.  Without bias and activation this is a straight copy of the 32
+                // registers; the general form is kept out of that path (with two epilogue warps per
+                // scheduler every instruction of the read-out costs about ten cycles, and per-element
+                // bias / activation tests were three quarters of its instructions).
+                uint8_t* const my_row = out_stage + lane * 128;
+                const uint32_t sw = lane & 7;
+                if (plain) {
 #pragma unroll
-                for (int v4 = 0; v4 < 8; v4++) {
-                    const int col = n0 + c0 + v4 * 4;
-                    float v[4];
+                    for (int v4 = 0; v4 < 8; v4++)
+                        *reinterpret_cast<uint4*>(my_row + ((v4 ^ sw) << 4)) =
+                            make_uint4(r[v4 * 4], r[v4 * 4 + 1], r[v4 * 4 + 2], r[v4 * 4 + 3]);
+                } else {
+                    const int col0 = n0 + c0;
+                    const bool bias_whole = bias && bias_vec && col0 + 31 < p.shape.N;
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        v[e] = __uint_as_float(r[v4 * 4 + e]);
-                        if (bias && col + e < p.shape.N) v[e] += __ldg(bias + col + e);
-                        v[e] = act_apply(v[e], act);
+                    for (int v4 = 0; v4 < 8; v4++) {
+                        float4 t = make_float4(__uint_as_float(r[v4 * 4]), __uint_as_float(r[v4 * 4 + 1]),
+                                               __uint_as_float(r[v4 * 4 + 2]), __uint_as_float(r[v4 * 4 + 3]));
+                        if (bias_whole) {
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + col0) + v4);
+                            t.x += b4.x; t.y += b4.y; t.z += b4.z; t.w += b4.w;
+                        } else if (bias) {
+                            const int col = col0 + v4 * 4;
+                            if (col < p.shape.N) t.x += __ldg(bias + col);
+                            if (col + 1 < p.shape.N) t.y += __ldg(bias + col + 1);
+                            if (col + 2 < p.shape.N) t.z += __ldg(bias + col + 2);
+                            if (col + 3 < p.shape.N) t.w += __ldg(bias + col + 3);
+                        }
+                        if (act == 1) {
+                            t.x = t.x > 0.f ? t.x : 0.f; t.y = t.y > 0.f ? t.y : 0.f;
+                            t.z = t.z > 0.f ? t.z : 0.f; t.w = t.w > 0.f ? t.w : 0.f;
+                        } else if (act == 2) {
+                            t.x = tanhf(t.x); t.y = tanhf(t.y); t.z = tanhf(t.z); t.w = tanhf(t.w);
+                        }
+                        *reinterpret_cast<float4*>(my_row + ((v4 ^ sw) << 4)) = t;
                     }
-                    *reinterpret_cast<float4*>(out_stage + lane * 128 + ((v4 ^ (lane & 7)) << 4)) =
-                        make_float4(v[0], v[1], v[2], v[3]);
                 }
                 if (p.c_tma) {
                     // one asynchronous bulk store of the 32 x 32 block; rows >= M and columns >= N
@@ -646,35 +672,35 @@ int try_launch(int math_mode, cudaStream_t st, const float* a, const float* b, f
     if (!plan_batch(hb, b_bs, p.batch.b_slot, p.batch.b_mult, vb)) return 3;
     if (!tma_compatible(va) || !tma_compatible(vb)) return 3;
 
-    // Tile width: 256 columns unless a narrower tile (192 or 128, 64 for N <= 64) cuts the padded
-    // width by more than 8 % (N = 192: one 192-wide tile instead of a 256-wide one that is a
-    // quarter padding).  Wide tiles move fewer operand bytes per flop, so they stay the rule.
+    // Tile shape from a cost model in SM clocks per CTA (shape and SM count only, so the choice --
+    // and with it the summation order -- is a function of the call alone).  Measured: a k-tile of
+    // a 128-row tile is bound by the operand bytes it pulls through L2 -> SM, about 980 clk for
+    // 128 x 256 (48 KB), in proportion for narrower tiles; a 256-row tile (two MMAs per B tile)
+    // takes about 1545 clk per k-tile for twice the work.  Reading a 128 x 256 accumulator out
+    // takes about 3500 clk: hidden behind the next tile's MMAs in the 128-row form (two accumulator
+    // sets), exposed in the 256-row form (one set); handing a tile over costs about 3000 clk.
+    //   width:  256 columns unless a narrower tile is cheaper -- N = 192 is one 192-wide tile
+    //           instead of a 256-wide one that is a quarter padding, and a grid of few tiles
+    //           (1024^3: 32 tiles of 128 x 256) is cut into more, narrower ones to fill the SMs;
+    //   height: 256 rows when that is cheaper than the best 128-row form (large products).
+    const double k_tiles = (K + BK - 1) / BK;
+    const auto waves = [&](int bm, int w) {
+        const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + w - 1) / w);
+        return static_cast<double>((work + num_sms - 1) / num_sms);
+    };
     int bn = 256;
-    {
-        const auto padded = [&](int w) { return static_cast<long long>((N + w - 1) / w) * w; };
-        for (int w : {192, 128, 64})
-            if (padded(w) * 108 < padded(bn) * 100) bn = w;
+    double t1 = 1e300;
+    for (int w : {256, 192, 128, 64}) {
+        const double mma = k_tiles * 980.0 * (128 + w) / 384.0, readout = 3500.0 * w / 256.0;
+        const double t = waves(128, w) * ((mma > readout ? mma : readout) + 3000.0);
+        if (t < t1 * 0.98) { t1 = t; bn = w; }      // a narrower tile has to win by 2 %
     }
-    // Tile height.  Measured per k-tile (32 k) and SM: about 980 clk with 128x256 tiles and
-    // about 1545 clk with 256x256 tiles, which do twice the work (two MMAs share each B tile,
-    // so less L2 -> SM traffic per flop).  The 128-row form has two accumulator sets, so its
-    // epilogue (about 14000 clk) hides behind the next tile's MMAs unless K is very short; the
-    // 256-row form has one set and its epilogue (about 28000 clk) is exposed, and it quantises
-    // worse on small grids.  Pick the cheaper estimate; it depends on the shape and the SM
-    // count only.
     int mt = 1;
     if (!split) {
-        const double k_tiles = (K + BK - 1) / BK;
-        const auto waves = [&](int bm) {
-            const long long work = static_cast<long long>(batch_count) * ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
-            return static_cast<double>((work + num_sms - 1) / num_sms);
-        };
-        const double mma1 = k_tiles * 980.0;
-        const double t1 = waves(128) * (mma1 > 14000.0 ? mma1 : 14000.0) + 14000.0;
-        const double t2 = waves(256) * (k_tiles * 1545.0 + 28000.0);
-        if (t2 < t1) mt = 2;
+        const double t2 = waves(256, 256) * (k_tiles * 1545.0 + 7000.0 + 3000.0);
+        if (t2 < t1) { mt = 2; bn = 256; }
     }
-    if (forced_mt == 1 || forced_mt == 2) mt = split ? 1 : forced_mt;
+    if (forced_mt == 1 || forced_mt == 2) { mt = split ? 1 : forced_mt; if (mt == 2) bn = 256; }
     const int bm = 128 * mt;
 
     OperandView views[4] = {va, vb, va, vb};

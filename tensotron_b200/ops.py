@@ -77,18 +77,19 @@ def _raw_bmm(a, b, M, N, K, aMs, aKs, bKs, bNs, batch_dims, aBs, bBs):
 def _reduce_grad_to_shape(g, shape):
     """ReduceGradToShape (src/Tensotron/TensorOps.cs:76-100): sum over broadcast axes.  Only
     reached when the broadcast axes cannot be fused into the batched GEMM (they do not merge
-    into one strided axis); torch.sum stands in for LaunchReduceSum there."""
+    into one strided axis); then a fixed-order reduction kernel behind the C ABI does the sum."""
     shape = tuple(shape)
     if tuple(g.shape) == shape:
         return g.clone()
     r = g.dim()
-    axes = []
+    reduce_axis = []
     for j in range(r):
         axt = j - (r - len(shape))
         dt = shape[axt] if axt >= 0 else 1
-        if dt != g.shape[j]:
-            axes.append(j)
-    return g.sum(dim=axes, keepdim=True).reshape(shape)
+        reduce_axis.append(1 if dt != g.shape[j] else 0)
+    out = torch.empty(shape, dtype=torch.float32, device=g.device)
+    runtime(g.device.index).LaunchReduceSumAxes(g, out, list(g.shape), reduce_axis)
+    return out
 
 
 def _bmm_reduced(x, y, M, N, K, xMs, xKs, yKs, yNs, batch_dims, xBs, yBs, target_shape):

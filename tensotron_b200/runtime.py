@@ -20,7 +20,7 @@ EXPORTS = [
     "tt_version", "tt_create", "tt_destroy", "tt_last_error", "tt_set_math_mode", "tt_get_math_mode",
     "tt_matmul", "tt_matmul_batched", "tt_matmul_batched_reduce", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
-    "tt_set_variant", "tt_softmax_cross_entropy_static", "tt_mse_loss", "tt_clip_grad_norm", "tt_mlp_train_step",
+    "tt_set_variant", "tt_softmax_cross_entropy_static", "tt_mse_loss", "tt_clip_grad_norm", "tt_mlp_train_step", "tt_reduce_sum_axes",
     "tt_peer_alloc", "tt_peer_free", "tt_peer_export", "tt_peer_open", "tt_peer_close", "tt_peer_group_create",
     "tt_peer_group_destroy", "tt_peer_linear_bwd", "tt_peer_push", "tt_peer_adam_step", "tt_peer_sync",
     "tt_peer_set_wait_limit",
@@ -81,6 +81,7 @@ def load_library(path=None):
     L.tt_softmax_cross_entropy.argtypes = [vp, vp, vp, vp, vp, vp, i, i, f]
     L.tt_softmax_cross_entropy_static.argtypes = [vp, vp, vp, vp, vp, i, i, f]
     L.tt_adam_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, i]
+    L.tt_reduce_sum_axes.argtypes = [vp, vp, vp, vp, i, ip, ip]
     L.tt_mse_loss.argtypes = [vp, vp, vp, vp, vp, vp, ll]
     L.tt_clip_grad_norm.argtypes = [vp, vp, vp, ll, f, f, vp]
     L.tt_mlp_train_step.argtypes = [vp, vp, ctypes.POINTER(MlpDesc), vp, vp, vp, vp, vp, vp, vp, vp, i, f, f, f, f, f, f]
@@ -221,6 +222,11 @@ class TensorRuntime:
             self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c), M, N, K, aMs, aKs, bKs, bNs,
             len(batchDims), _iarr(batchDims), _iarr(aBatchStrides), _iarr(bBatchStrides),
             _iarr(reduceAxis)))
+
+    def LaunchReduceSumAxes(self, src, dst, dims, reduceAxis, stream=None):
+        """ReduceGradToShape's sum over the marked axes (src/Tensotron/TensorOps.cs:76-100), fixed order."""
+        self._ck(self._L.tt_reduce_sum_axes(self._h, self._st(stream), _ptr(src), _ptr(dst), len(dims),
+                                            _iarr(dims), _iarr(reduceAxis)))
 
     def LaunchLinearForward(self, x, w, bias, y, M, N, K, act=0, stream=None):
         self._ck(self._L.tt_linear_fwd(self._h, self._st(stream), _ptr(x), _ptr(w), _ptr(bias),

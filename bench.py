@@ -553,6 +553,29 @@ def run_one_bmm(spec):
         mode, " (B transposed)" if tb else "", ms * 1e3, 512 * 2.0 * 384 * 192 * 256 / ms / 1e9, nbytes / ms / 1e6))
 
 
+def run_one_mlp(spec):
+    """--one-mlp ROWS MODE EXCHANGE STEPS: runs STEPS training steps of the benchmark MLP
+    (784-4096-4096-4096-10, cross-entropy, Adam) on ROWS rows on one GPU -- ROWS = 1024 is one rank's
+    share of the 8-GPU strong-scaling run -- and prints the time per step.  EXCHANGE is `peer` (the
+    exchange calls at world size 1) or `none` (plain backward + one Adam launch).  The command the
+    per-kernel launch list of a data-parallel rank's step is captured from."""
+    import torch
+
+    from tensotron_b200.mlp import MlpTrainer
+    from tensotron_b200.runtime import TensorRuntime
+    rows, mode, exchange, steps = int(spec[0]), int(spec[1]), spec[2], int(spec[3])
+    rt = TensorRuntime(0, 1024 << 20)
+    tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, lr=1e-3, seed=2, math_mode=mode,
+                    exchange="peer" if exchange == "peer" else "nccl")
+    x = torch.randn((rows, 784), device="cuda")
+    y = torch.randint(0, 10, (rows,), device="cuda", dtype=torch.int32)
+    ms = time_calls(lambda: tr.step(x, y, global_batch=8192), steps)
+    rt.Check()
+    print("ok mlp 784-4096x3-10 rows %d m%d %s: %.3f ms per step (%.1f TF/s of GEMM work)"
+          % (rows, mode, exchange, ms, 1756.5 * rows / 8192.0 / ms))
+    tr.close()
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
     if rank != 0:
@@ -583,11 +606,14 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--one", nargs="+", metavar="ARG", help="MxNxK LAYOUT VARIANT MODE ITERS [graph]: time one GEMM shape and exit")
     ap.add_argument("--one-bmm", nargs="+", metavar="ARG", help="MODE ITERS [transposed_b]: time benchmark config 3 and exit")
+    ap.add_argument("--one-mlp", nargs="+", metavar="ARG", help="ROWS MODE EXCHANGE STEPS: time the benchmark MLP step on ROWS rows and exit")
     args = ap.parse_args()
     if args.one:
         return run_one(args.one)
     if args.one_bmm:
         return run_one_bmm(args.one_bmm)
+    if args.one_mlp:
+        return run_one_mlp(args.one_mlp)
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     rank = env_int("RANK", 0)
@@ -613,9 +639,9 @@ def main():
         os.environ.setdefault("NCCL_PROTO", "Simple")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    # raises if the CUDA library is missing: no fallback.  2.5 GiB workspace: 3xTF32 keeps
-    # hi/lo copies of both 8192^2 operands there.
-    rt = TensorRuntime(local_rank, 2560 << 20)
+    # raises if the CUDA library is missing: no fallback.  4.25 GiB workspace: 3xTF32 keeps hi / lo
+    # copies of both operands there (16384^3 on one GPU: 2 x (1 + 1) GiB).
+    rt = TensorRuntime(local_rank, 4352 << 20)
     rt.SetCuBlasMathMode(TT_MATH_FP32)
     n = N_TOTAL
     if n % world != 0:

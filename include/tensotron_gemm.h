@@ -149,6 +149,28 @@ TT_API int tt_mse_loss(tt_handle_t h, void* stream, const float* input, const fl
 TT_API int tt_clip_grad_norm(tt_handle_t h, void* stream, float* grads, long long n, float max_norm, float eps,
                              float* norm_out);
 
+/* Conv2d through the batched GEMM engine (src/Tensotron/TensorOps.Conv.cs:60-80: Im2Col, then
+ * MatMul((1, O, K), (N, K, L)), then the broadcast bias add; K = C*kh*kw, L = Ho*Wo; symmetric
+ * stride / padding / dilation as there).  x (N,C,H,W), w (O,C,kh,kw), bias (O) or NULL,
+ * y (N,O,Ho,Wo), all contiguous.  The columns and the packed weights live in the handle workspace
+ * (tt_conv2d_workspace bytes; TT_ERR_WORKSPACE when it is smaller); the bias rides in the GEMM as
+ * one extra k term, so forward is im2col + weight packing + ONE batched GEMM launch.
+ * Backward (what the reference's autograd chain computes: Kernels.Col2Im, src/Tensotron/Kernels.cs:803-814;
+ * the broadcast-reduced dW of src/Tensotron/TensorOps.MatMulND.cs:80-103):
+ *   dbias[o] = sum_{n,l} dy      dw = sum_n dy[n] . col[n]^T      dx = col2im(w^T . dy[n])
+ * every sum in a fixed order, no atomics (col2im gathers).  dx and dbias may be NULL.  The math
+ * mode of the handle applies to the GEMMs. */
+typedef struct tt_conv2d_desc {
+    int n, c, h, w;          /* input  (N, C, H, W)           */
+    int o, kh, kw;           /* weight (O, C, kh, kw)         */
+    int stride, padding, dilation;
+} tt_conv2d_desc;
+TT_API size_t tt_conv2d_workspace(const tt_conv2d_desc* d, int backward);
+TT_API int tt_conv2d_fwd(tt_handle_t h, void* stream, const tt_conv2d_desc* d, const float* x, const float* w,
+                         const float* bias, float* y);
+TT_API int tt_conv2d_bwd(tt_handle_t h, void* stream, const tt_conv2d_desc* d, const float* x, const float* w,
+                         const float* dy, float* dx, float* dw, float* dbias);
+
 /* Same result as tt_softmax_cross_entropy, for callers that may not allocate device
  * memory.  No counterpart in the reference: there the per-row losses live in tensors from
  * its own allocator.  It takes no handle (tt_create allocates) and keeps the per-row losses
@@ -213,6 +235,15 @@ TT_API int tt_add_into(tt_handle_t h, void* stream, float* target, const float* 
 TT_API int tt_broadcast_batch(int ra, const int* a_dims, const int* a_strides, int rb, const int* b_dims,
                        const int* b_strides, int* rank, int* dims, int* a_bs, int* b_bs);
 
+/* The multi-GPU forms of LaunchMatMul / LaunchMatMulBatched shard the rows of A and C (or the
+ * outermost batch axis) over one process per GPU with the other operand replicated: every rank
+ * calls tt_matmul / tt_matmul_batched on its own shard, there is no collective on the data path.
+ * This is the split every rank uses: `total` units cut into `world` contiguous blocks of
+ * ceil(total / world) (the row split of the reference's ParallelRows,
+ * src/Tensotron/CpuKernels.cs:461-472); *start / *count describe block `rank` (count may be 0).
+ * Pure host logic. */
+TT_API int tt_shard_range(long long total, int world, int rank, long long* start, long long* count);
+
 /* Counters in the spirit of TensorRuntime.Launches (src/Tensotron/TensorRuntime.cs:143-151). */
 typedef struct tt_stats {
     long long launches;        /* kernels enqueued by this handle                        */
@@ -237,7 +268,9 @@ TT_API int tt_check(tt_handle_t h, void* stream);
  * 2 TMA-fed FFMA kernel with 256x128 tiles, 3 the same with 128x128 tiles,
  * 4 / 5 tcgen05 kernel (TF32 modes only) with 128- / 256-row tiles,
  * 6 FFMA kernel with 256x128 tiles and stream-K work distribution,
- * 7 FFMA kernel with 128x192 tiles (B contiguous along N only). */
+ * 7 FFMA kernel with 128x192 tiles (B contiguous along N only),
+ * 8 any-stride kernel with its K ranges added through the workspace (two launches) instead of
+ *   through a thread-block cluster. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 /* ---- Data-parallel gradient exchange over peer memory ---------------------------------

@@ -182,6 +182,81 @@ def clip_grad_norm(grads, max_norm, eps=1e-6):
     return float(total)
 
 
+def _conv_out(size, k, stride, pad, dil):
+    """ConvOutSize (src/Tensotron/TensorOps.Conv.cs:5-6)."""
+    return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+
+def im2col(x, kh, kw, stride, pad, dil):
+    """Kernels.Im2Col (src/Tensotron/Kernels.cs:784-801): (N,C,H,W) -> (N, C*kh*kw, Ho*Wo), padding
+    positions read 0."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n, c, h, w = x.shape
+    ho, wo = _conv_out(h, kh, stride, pad, dil), _conv_out(w, kw, stride, pad, dil)
+    col = np.zeros((n, c * kh * kw, ho * wo), dtype=np.float32)
+    oh, ow = np.meshgrid(np.arange(ho), np.arange(wo), indexing="ij")
+    for ci in range(c):
+        for ki in range(kh):
+            for kj in range(kw):
+                ih = (oh * stride - pad + ki * dil).reshape(-1)
+                iw = (ow * stride - pad + kj * dil).reshape(-1)
+                ok = (ih >= 0) & (ih < h) & (iw >= 0) & (iw < w)
+                k = (ci * kh + ki) * kw + kj
+                col[:, k, ok] = x[:, ci, ih[ok], iw[ok]]
+    return col
+
+
+def col2im(gcol, shape, kh, kw, stride, pad, dil):
+    """Kernels.Col2Im (src/Tensotron/Kernels.cs:803-814): scatter-add each column gradient back
+    to its input pixel (the reference uses atomics; here every pixel adds its windows in k order)."""
+    n, c, h, w = shape
+    ho, wo = _conv_out(h, kh, stride, pad, dil), _conv_out(w, kw, stride, pad, dil)
+    gx = np.zeros(shape, dtype=np.float32)
+    oh, ow = np.meshgrid(np.arange(ho), np.arange(wo), indexing="ij")
+    for ci in range(c):
+        for ki in range(kh):
+            for kj in range(kw):
+                ih = (oh * stride - pad + ki * dil).reshape(-1)
+                iw = (ow * stride - pad + kj * dil).reshape(-1)
+                ok = (ih >= 0) & (ih < h) & (iw >= 0) & (iw < w)
+                k = (ci * kh + ki) * kw + kj
+                np.add.at(gx[:, ci], (slice(None), ih[ok], iw[ok]), gcol[:, k, ok])
+    return gx
+
+
+def conv2d_fwd(x, w, bias, stride=1, pad=0, dil=1):
+    """TensorOps.Conv2d (src/Tensotron/TensorOps.Conv.cs:60-80): Im2Col, then the batched matmul of
+    the weight (1, O, K) against the columns (N, K, L), then the broadcast bias add."""
+    n = x.shape[0]
+    o, c, kh, kw = w.shape
+    col = im2col(x, kh, kw, stride, pad, dil)
+    K, L = col.shape[1], col.shape[2]
+    out = matmul_batched(w.reshape(o, K), col, o, L, K, K, 1, L, 1, [n], [0], [K * L], fast=True)
+    if bias is not None:
+        out = out + np.asarray(bias, dtype=np.float32).reshape(1, o, 1)
+    ho, wo = _conv_out(x.shape[2], kh, stride, pad, dil), _conv_out(x.shape[3], kw, stride, pad, dil)
+    return out.astype(np.float32).reshape(n, o, ho, wo)
+
+
+def conv2d_bwd(x, w, dy, stride=1, pad=0, dil=1):
+    """The gradients the reference's autograd chain produces for Conv2d: through the bias add
+    (sum over batch and positions), the broadcast batched matmul (dW summed over the batch,
+    src/Tensotron/TensorOps.MatMulND.cs:80-103) and Im2Col's backward (Col2Im)."""
+    n = x.shape[0]
+    o, c, kh, kw = w.shape
+    col = im2col(x, kh, kw, stride, pad, dil)
+    K, L = col.shape[1], col.shape[2]
+    g = np.ascontiguousarray(dy, dtype=np.float32).reshape(n, o, L)
+    dbias = g.sum(axis=(0, 2), dtype=np.float32)
+    # dW[o][k] = sum_n sum_l g[n][o][l] * col[n][k][l]
+    dw_n = matmul_batched(g, col, o, K, L, L, 1, 1, L, [n], [o * L], [K * L], fast=True)
+    dw = dw_n.sum(axis=0, dtype=np.float32).reshape(w.shape)
+    # dcol[n][k][l] = sum_o W[o][k] * g[n][o][l]
+    dcol = matmul_batched(w.reshape(o, K), g, K, L, o, 1, K, L, 1, [n], [0], [o * L], fast=True)
+    dx = col2im(dcol, x.shape, kh, kw, stride, pad, dil)
+    return dx, dw, dbias
+
+
 def adam_step(p, g, m, v, adv, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.0):
     """In place on float32 numpy arrays (all contiguous); adv = [t, ibc1, ibc2]."""
     lib().oracle_adam_step(_p(p.reshape(-1)), _p(_flat(g)), _p(m.reshape(-1)), _p(v.reshape(-1)),

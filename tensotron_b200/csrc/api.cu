@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "conv.cuh"
 #include "elementwise.cuh"
 #include "gemm_common.h"
 #include "gemm_generic.cuh"
@@ -26,6 +27,7 @@ struct tt_handle_s {
     CUcontext ctx;   // the CUDA context the handle's memory and kernels live in (see tt_create)
     int device;
     int num_sms;
+    int max_cluster;   // largest thread-block cluster the any-stride kernel may use (16, else the portable 8)
     int math_mode;
     int variant;  // 0 auto, 1 generic, 2 simt-tma 256x128, 3 simt-tma 128x128, 4/5 tcgen05 tile height 128/256
     uint8_t* workspace;
@@ -43,6 +45,7 @@ constexpr size_t DEFAULT_WORKSPACE = 256ull << 20;
 // stream-K flag per CTA (zero between launches).
 constexpr int STREAMK_FLAGS_WORD = 64, HANDLE_WORDS = 1024;
 constexpr long long TMA_MIN_FLOP_ELEMS = 1ll << 21;  // M*N*K below this -> any-stride kernel
+constexpr long long SMALL_MAX_FLOP_ELEMS = 1ll << 27;  // ... and up to this when the output is a few tiles only
 
 int fail(tt_handle_t h, int code, const char* fmt, const char* detail = "")
 {
@@ -212,20 +215,40 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     p.shape.batch = g.batch_count;
     const long long tiles = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
     // Split K when the tiles alone leave most of the machine idle: aim at about two CTAs per
-    // SM, at least 64 k per range, and only as far as the workspace holds the partial tiles.
+    // SM and at least 64 k per range.  Up to 16 ranges (a power of two) run as one thread-block
+    // cluster per tile that adds its partial tiles through distributed shared memory (one
+    // launch, no workspace); beyond that the partial tiles go to the workspace and a second
+    // kernel adds them.  Both forms add the ranges in ascending k, so they give the same bits.
     int splits = 1, kspan = g.K > 0 ? g.K : 1;
+    bool cluster = false;
     const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
-    if (tiles < h->num_sms && g.K >= 512 && g.batch.red_count == 1) {
+    if (tiles < h->num_sms && g.K >= 128 && g.batch.red_count == 1) {
         long long want = (2ll * h->num_sms + tiles - 1) / tiles;
         const long long max_by_k = g.K / 64;
         if (want > max_by_k) want = max_by_k;
         if (want > 64) want = 64;
-        const size_t per_split = static_cast<size_t>(tiles) * generic::BM * generic::BN * sizeof(float);
-        if (per_split > 0 && want * per_split > ws_avail) want = static_cast<long long>(ws_avail / per_split);
-        if (want >= 2) {
-            kspan = static_cast<int>((g.K + want - 1) / want);
-            kspan = ((kspan + generic::BK - 1) / generic::BK) * generic::BK;
-            splits = (g.K + kspan - 1) / kspan;
+        bool chosen = false;
+        if (want >= 2 && want <= 2 * h->max_cluster) {
+            int sp = 2;
+            while (sp * 2 <= want && sp * 2 <= h->max_cluster) sp *= 2;
+            const int ks = ((g.K + sp - 1) / sp + generic::BK - 1) / generic::BK * generic::BK;
+            const size_t need = static_cast<size_t>(tiles) * sp * generic::BM * generic::BN * sizeof(float);
+            if ((g.K + ks - 1) / ks == sp && (h->variant != 8 || need <= ws_avail)) {   // no empty range
+                splits = sp;
+                kspan = ks;
+                cluster = h->variant != 8;     // variant 8: the same ranges, added through the workspace
+                chosen = true;
+            }
+        }
+        if (!chosen) {
+            kspan = g.K;
+            const size_t per_split = static_cast<size_t>(tiles) * generic::BM * generic::BN * sizeof(float);
+            if (per_split > 0 && want * per_split > ws_avail) want = static_cast<long long>(ws_avail / per_split);
+            if (want >= 2 && g.K >= 512) {
+                kspan = static_cast<int>((g.K + want - 1) / want);
+                kspan = ((kspan + generic::BK - 1) / generic::BK) * generic::BK;
+                splits = (g.K + kspan - 1) / kspan;
+            }
         }
     }
     p.splits = splits;
@@ -236,9 +259,29 @@ int launch_generic(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     fill_batch_desc(g.batch, p.batch);
     p.epi = g.epi;
     p.aMs = g.aMs; p.aKs = g.aKs; p.bKs = g.bKs; p.bNs = g.bNs;
+    if (cluster) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(static_cast<unsigned int>(p.shape.work), 1, 1);
+        cfg.blockDim = dim3(generic::THREADS, 1, 1);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned int>(splits);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t le = cudaLaunchKernelEx(&cfg, generic::gemm_generic_kernel<true>, p);
+        if (le != cudaSuccess) return cuda_fail(h, le, "generic gemm cluster launch");
+        h->stats.launches++;
+        h->stats.splitk++;
+        h->stats.generic++;
+        return TT_OK;
+    }
     const long long max_grid = static_cast<long long>(h->num_sms) * 8;
     const int grid = static_cast<int>(p.shape.work < max_grid ? p.shape.work : max_grid);
-    generic::gemm_generic_kernel<<<grid, generic::THREADS, 0, st>>>(p);
+    generic::gemm_generic_kernel<false><<<grid, generic::THREADS, 0, st>>>(p);
     h->stats.launches++;
     if (splits > 1) {
         const long long threads = tiles * (generic::BM * generic::BN / 4);
@@ -553,7 +596,7 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     if (g.epi.scatter_rows > 0) {
         // Row-block scatter: only the tensor-core kernel and the stream-K FMA kernel store
         // through the scatter table; anything else is the caller's fallback (local + copy).
-        if (g.K == 0 || g.batch_count != 1 || g.batch.red_count != 1 || h->variant == 1 ||
+        if (g.K == 0 || g.batch_count != 1 || g.batch.red_count != 1 || h->variant == 1 || h->variant == 8 ||
             g.epi.scatter_rows % 256 != 0)
             return TT_ERR_UNSUPPORTED;
         if (h->math_mode != TT_MATH_FP32) {
@@ -576,7 +619,7 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         const int rc = try_launch_skinny(h, st, g);
         if (rc != TT_ERR_UNSUPPORTED) return rc;
     }
-    if (g.K > 0 && h->variant != 1) {
+    if (g.K > 0 && h->variant != 1 && h->variant != 8) {
         if (h->math_mode != TT_MATH_FP32 && g.batch.red_count == 1) {  // the tensor-core kernel has no reduced axis
             int n_launch = 0;
             const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
@@ -588,13 +631,23 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             if (rc == TT_OK) { h->stats.launches += n_launch; h->stats.tcgen05++; return TT_OK; }
             if (rc != TT_ERR_UNSUPPORTED) return fail(h, rc, "tcgen05 gemm launch failed");
         }
-        if (h->variant == 2 || h->variant == 3 || h->variant == 6 || h->variant == 7 || vol >= TMA_MIN_FLOP_ELEMS) {
+        // A small output with little work in total (benchmark config 1, the GEMMs of the small
+        // networks) is latency-bound: the any-stride kernel serves it in ONE launch, K cut across
+        // the CTAs of a cluster, where the TMA-fed kernel would need a second launch to add its
+        // partial tiles.
+        const long long tiles64 = static_cast<long long>(g.batch_count) * ((g.M + 63) / 64) * ((g.N + 63) / 64);
+        const bool small_output = h->variant == 0 && g.batch.red_count == 1 && tiles64 <= h->num_sms / 2 &&
+                                  vol <= SMALL_MAX_FLOP_ELEMS;
+        if (!small_output &&
+            (h->variant == 2 || h->variant == 3 || h->variant == 6 || h->variant == 7 || vol >= TMA_MIN_FLOP_ELEMS)) {
             const int rc = try_launch_simt(h, st, g);
             if (rc != TT_ERR_UNSUPPORTED) return rc;
         }
     }
     return launch_generic(h, st, g);
 }
+
+bool g_generic_cluster16 = false;
 
 // Per-device kernel attributes, set once at handle creation so that no compute call
 // does lazy set-up work (which could not be captured into a graph).
@@ -641,6 +694,10 @@ cudaError_t init_kernels()
     if (e != cudaSuccess) return e;
     if ((e = init_simt_wide<true>()) != cudaSuccess) return e;
     if ((e = init_simt_wide<false>()) != cudaSuccess) return e;
+    // clusters of 16 CTAs need this attribute; without it the any-stride kernel stays at 8
+    g_generic_cluster16 = cudaFuncSetAttribute(generic::gemm_generic_kernel<true>,
+                                               cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (!g_generic_cluster16) cudaGetLastError();
     if (mlp_step::init_device() != 0) return cudaErrorUnknown;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
@@ -824,6 +881,7 @@ TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle
     cudaMemset(h->status, 0, HANDLE_WORDS * sizeof(unsigned int));
     // kernel attributes are per context: set them in this one
     if (init_kernels() != cudaSuccess) { cudaFree(h->workspace); cudaFree(h->status); delete h; return TT_ERR_CUDA; }
+    h->max_cluster = g_generic_cluster16 ? 16 : 8;
     h->stats.workspace_bytes = static_cast<long long>(h->workspace_bytes);
     h->err[0] = 0;
     *out_handle = h;
@@ -868,7 +926,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 7) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 8) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }
@@ -1006,6 +1064,148 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
 {
     return linear_bwd_impl(h, static_cast<cudaStream_t>(stream), x, w, y, dy, dx, dw, dbias, M, N, K, act,
                            nullptr, nullptr);
+}
+
+namespace {
+// Fills the derived sizes; false when the description is not a valid convolution.
+bool conv_shape(const tt_conv2d_desc* d, conv::Shape& s)
+{
+    if (!d || d->n < 0 || d->c <= 0 || d->h <= 0 || d->w <= 0 || d->o <= 0 || d->kh <= 0 || d->kw <= 0 ||
+        d->stride <= 0 || d->dilation <= 0 || d->padding < 0)
+        return false;
+    s.n = d->n; s.c = d->c; s.h = d->h; s.w = d->w; s.o = d->o; s.kh = d->kh; s.kw = d->kw;
+    s.stride = d->stride; s.pad = d->padding; s.dil = d->dilation;
+    // ConvOutSize (src/Tensotron/TensorOps.Conv.cs:5-6)
+    s.ho = (d->h + 2 * d->padding - d->dilation * (d->kh - 1) - 1) / d->stride + 1;
+    s.wo = (d->w + 2 * d->padding - d->dilation * (d->kw - 1) - 1) / d->stride + 1;
+    if (s.ho <= 0 || s.wo <= 0) return false;
+    const long long K = static_cast<long long>(d->c) * d->kh * d->kw, L = static_cast<long long>(s.ho) * s.wo;
+    if (K + 4 > 0x7fffffffll || L > 0x7fffffffll || static_cast<long long>(d->n) * (K + 4) * L > 0x7fffffffll ||
+        static_cast<long long>(d->n) * d->o * L > 0x7fffffffll)
+        return false;     // element offsets fit int32, like every buffer of the reference
+    s.K = static_cast<int>(K);
+    s.L = static_cast<int>(L);
+    s.Kp = (s.K + 1 + 3) & ~3;
+    return true;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct ConvWorkspace {
+    size_t col, wp, dcol, end;   // byte offsets into the handle workspace
+};
+
+ConvWorkspace conv_workspace(const conv::Shape& s, bool backward)
+{
+    ConvWorkspace w;
+    w.col = 0;
+    w.wp = align256(sizeof(float) * static_cast<size_t>(s.n) * s.Kp * s.L);
+    w.dcol = w.wp + align256(sizeof(float) * static_cast<size_t>(s.o) * s.Kp);
+    w.end = w.dcol + (backward ? align256(sizeof(float) * static_cast<size_t>(s.n) * s.K * s.L) : 0);
+    return w;
+}
+
+int conv_im2col(tt_handle_t h, cudaStream_t st, const conv::Shape& s, const float* x, float* col)
+{
+    const long long total = static_cast<long long>(s.n) * s.Kp * s.L;
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(h->num_sms) * 32;
+    if (blocks > cap) blocks = cap;
+    conv::im2col_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(x, col, s);
+    h->stats.launches++;
+    return TT_OK;
+}
+}  // namespace
+
+TT_API size_t tt_conv2d_workspace(const tt_conv2d_desc* d, int backward)
+{
+    conv::Shape s;
+    if (!conv_shape(d, s)) return 0;
+    // + room for what the GEMMs themselves may take (split-K partial tiles, 3xTF32 operand planes)
+    return conv_workspace(s, backward != 0).end + (64ull << 20);
+}
+
+TT_API int tt_conv2d_fwd(tt_handle_t h, void* stream, const tt_conv2d_desc* d, const float* x, const float* w,
+                         const float* bias, float* y)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    conv::Shape s;
+    if (!conv_shape(d, s)) return fail(h, TT_ERR_INVALID_ARG, "bad convolution description");
+    if (s.n > 0 && (!x || !w || !y)) return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    TT_BIND(h);
+    h->stats.calls++;
+    if (s.n == 0) return TT_OK;
+    const ConvWorkspace ws = conv_workspace(s, false);
+    if (ws.end > h->workspace_bytes) return fail(h, TT_ERR_WORKSPACE, "workspace too small for the convolution's columns");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* col = reinterpret_cast<float*>(h->workspace + ws.col);
+    float* wp = reinterpret_cast<float*>(h->workspace + ws.wp);
+    conv_im2col(h, st, s, x, col);
+    conv::pack_weight_kernel<<<(s.o * s.Kp + 255) / 256, 256, 0, st>>>(w, bias, wp, s.o, s.K, s.Kp);
+    h->stats.launches++;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "im2col launch");
+    // y[n][o][l] = sum_k wp[o][k] * col[n][k][l]   (the k = K term is bias[o] * 1)
+    GemmCall g{wp, col, y, s.o, s.L, s.Kp, s.Kp, 1, s.L, 1, HostBatch(), s.n, Epilogue{nullptr, TT_ACT_NONE}};
+    const int bd[1] = {s.n}, as[1] = {0}, bs[1] = {s.Kp * s.L};
+    if (!collapse_batch(1, bd, as, bs, g.batch)) return fail(h, TT_ERR_UNSUPPORTED, "batch");
+    g.ws_off = ws.end;
+    return run_gemm(h, st, g);
+}
+
+TT_API int tt_conv2d_bwd(tt_handle_t h, void* stream, const tt_conv2d_desc* d, const float* x, const float* w,
+                         const float* dy, float* dx, float* dw, float* dbias)
+{
+    if (!h) return TT_ERR_INVALID_ARG;
+    conv::Shape s;
+    if (!conv_shape(d, s)) return fail(h, TT_ERR_INVALID_ARG, "bad convolution description");
+    if (!x || !w || !dy || !dw) return fail(h, TT_ERR_INVALID_ARG, "null device pointer");
+    TT_BIND(h);
+    h->stats.calls++;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (s.n == 0) {
+        cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(s.o) * s.K, st);
+        if (dbias) cudaMemsetAsync(dbias, 0, sizeof(float) * s.o, st);
+        return TT_OK;
+    }
+    const ConvWorkspace ws = conv_workspace(s, dx != nullptr);
+    if (ws.end > h->workspace_bytes) return fail(h, TT_ERR_WORKSPACE, "workspace too small for the convolution's columns");
+    float* col = reinterpret_cast<float*>(h->workspace + ws.col);
+    conv_im2col(h, st, s, x, col);
+    if (dbias) {
+        conv::bias_grad_kernel<<<s.o, 256, 0, st>>>(dy, dbias, s.n, s.o, s.L);
+        h->stats.launches++;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(h, e, "convolution backward launch");
+    int rc;
+    {
+        // dw[o][k] = sum_n sum_l dy[n][o][l] * col[n][k][l]: the batch axis is summed inside the k loop
+        GemmCall g{dy, col, dw, s.o, s.K, s.L, s.L, 1, 1, s.L, HostBatch(), 1, Epilogue{nullptr, TT_ACT_NONE}};
+        g.batch.red_count = s.n;
+        g.batch.red_as = s.o * s.L;
+        g.batch.red_bs = s.Kp * s.L;
+        g.ws_off = ws.end;
+        if ((rc = run_gemm(h, st, g))) return rc;
+    }
+    if (dx) {
+        // dcol[n][k][l] = sum_o w[o][k] * dy[n][o][l]
+        float* dcol = reinterpret_cast<float*>(h->workspace + ws.dcol);
+        GemmCall g{w, dy, dcol, s.K, s.L, s.o, 1, s.K, s.L, 1, HostBatch(), s.n, Epilogue{nullptr, TT_ACT_NONE}};
+        const int bd[1] = {s.n}, as[1] = {0}, bs[1] = {s.o * s.L};
+        if (!collapse_batch(1, bd, as, bs, g.batch)) return fail(h, TT_ERR_UNSUPPORTED, "batch");
+        g.ws_off = ws.end;
+        if ((rc = run_gemm(h, st, g))) return rc;
+        const long long total = static_cast<long long>(s.n) * s.c * s.h * s.w;
+        long long blocks = (total + 255) / 256;
+        const long long cap = static_cast<long long>(h->num_sms) * 32;
+        if (blocks > cap) blocks = cap;
+        conv::col2im_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(dcol, dx, s);
+        h->stats.launches++;
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "col2im launch");
+    }
+    return TT_OK;
 }
 
 TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
@@ -1170,6 +1370,17 @@ TT_API int tt_broadcast_batch(int ra, const int* a_dims, const int* a_strides, i
         a_bs[j] = (axa >= 0 && da == od) ? a_strides[axa] : 0;
         b_bs[j] = (axb >= 0 && db == od) ? b_strides[axb] : 0;
     }
+    return TT_OK;
+}
+
+TT_API int tt_shard_range(long long total, int world, int rank, long long* start, long long* count)
+{
+    if (total < 0 || world < 1 || rank < 0 || rank >= world || !start || !count) return TT_ERR_INVALID_ARG;
+    const long long per = (total + world - 1) / world;
+    const long long s0 = per * rank < total ? per * rank : total;
+    const long long s1 = s0 + per < total ? s0 + per : total;
+    *start = s0;
+    *count = s1 - s0;
     return TT_OK;
 }
 

@@ -3,7 +3,18 @@
 // combination (odd leading dimensions, unaligned sub-views, "TT" strides, tiny
 // shapes).  64x64x16 tiles, 256 threads, 4x4 accumulators per thread, ascending-k
 // summation with one accumulator per output (bit-stable).
+//
+// Small outputs with a long K (a handful of tiles: the latency-bound shapes of small networks)
+// are cut along K.  Two forms of the same sum, split by split in ascending k:
+//   workspace form  partial tiles go to the handle workspace, generic_reduce_kernel adds them;
+//   cluster form    the CTAs that share an output tile are one thread-block cluster (2, 4, 8 or
+//                   16 CTAs); each leaves its partial tile in its own shared memory and, after a
+//                   cluster barrier, adds 64 / splits rows of the tile over all CTAs of the
+//                   cluster through distributed shared memory and stores them with the
+//                   epilogue: one launch, no workspace.
 #pragma once
+#include <cooperative_groups.h>
+
 #include "gemm_common.h"
 
 namespace tt {
@@ -34,6 +45,7 @@ __device__ __forceinline__ float act_apply(float v, int act)
     return v;
 }
 
+template <bool CLUSTER>
 __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
 {
     __shared__ __align__(16) float As[BK][BM + 4];
@@ -132,6 +144,46 @@ __global__ void __launch_bounds__(THREADS) gemm_generic_kernel(const Params p)
         }
         }  // reduced axis
 
+        if constexpr (CLUSTER) {
+            // grid == work: this loop body runs once per CTA, and the CTAs of a cluster are the
+            // splits of one tile in ascending order (cluster rank == split)
+            namespace cg = cooperative_groups;
+            __shared__ __align__(16) float Cs[BM][BN + 4];
+            cg::cluster_group cluster = cg::this_cluster();
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                *reinterpret_cast<float4*>(&Cs[ty * 4 + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            cluster.sync();
+            const int S = static_cast<int>(cluster.num_blocks()), rank = static_cast<int>(cluster.block_rank());
+            const int rows_per = BM / S;
+            float* C = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
+            for (int e = tid; e < rows_per * (BN / 4); e += THREADS) {
+                const int lr = rank * rows_per + e / (BN / 4), lc = (e % (BN / 4)) * 4;
+                float4 sum = *reinterpret_cast<const float4*>(&cluster.map_shared_rank(&Cs[0][0], 0)[lr * (BN + 4) + lc]);
+                for (int r = 1; r < S; r++) {
+                    const float4 q = *reinterpret_cast<const float4*>(&cluster.map_shared_rank(&Cs[0][0], r)[lr * (BN + 4) + lc]);
+                    sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+                }
+                const int gm = m0 + lr, gn0 = n0 + lc;
+                if (gm >= p.shape.M) continue;
+                float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (p.epi.bias && gn0 + j < p.shape.N) v[j] += __ldg(p.epi.bias + gn0 + j);
+                    v[j] = act_apply(v[j], p.epi.act);
+                }
+                float* crow = C + static_cast<long long>(gm) * p.shape.N;
+                if (p.c_vec_ok && gn0 + 3 < p.shape.N) {
+                    *reinterpret_cast<float4*>(crow + gn0) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        if (gn0 + j < p.shape.N) crow[gn0 + j] = v[j];
+                }
+            }
+            cluster.sync();     // nobody leaves while its partial tile may still be read
+            continue;
+        }
         if (p.splits > 1) {
             float* mine = p.partial + w * (BM * BN);
 #pragma unroll

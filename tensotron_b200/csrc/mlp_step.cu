@@ -133,72 +133,93 @@ __device__ __forceinline__ float act_fwd(float v, int act)
     return v;
 }
 
+// acc[0..3] += a * b as two packed two-wide FP32 FMAs (each lane an IEEE fused multiply-add, so
+// the bits equal four scalar fmaf).
+__device__ __forceinline__ void fma_row4(float (&acc)[4], float a, const float4 b)
+{
+    const float2 ap = make_float2(a, a);
+    float2 r;
+    r = __ffma2_rn(ap, make_float2(b.x, b.y), make_float2(acc[0], acc[1])); acc[0] = r.x; acc[1] = r.y;
+    r = __ffma2_rn(ap, make_float2(b.z, b.w), make_float2(acc[2], acc[3])); acc[2] = r.x; acc[3] = r.y;
+}
+
 // Outer form: C[i][j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending, one
-// accumulator per output, fused multiply-add).  ldp >= I rounded up to 2, ldq >= J rounded up to 4;
-// what lies in those roundings may be anything, it only reaches outputs that are not emitted.
+// accumulator per output, fused multiply-add).  A thread owns IB x 4 output blocks (IB = 2 or 4: the
+// taller block halves the shared-memory bytes read per FMA and is used when there are enough rows
+// to keep the threads busy).  ldp >= I rounded up to IB, ldq >= J rounded up to 4; what lies in
+// those roundings may be anything, it only reaches outputs that are not emitted.
 // `emit(i, j0, acc)` receives row i (< I) and the four columns j0 .. j0 + 3 (the caller masks j >= J).
-template <typename Emit>
+template <int IB, typename Emit>
 __device__ __forceinline__ void gemm_outer(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
                                            int I, int J, int L, Emit emit)
 {
-    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
+    const int ib_n = (I + IB - 1) / IB, jb_n = (J + 3) >> 2;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
         const int jb = blk % jb_n, ib = blk / jb_n;
-        const float* pp = P + 2 * ib;
+        const float* pp = P + IB * ib;
         const float* qq = Q + 4 * jb;
-        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float acc[IB][4];
+#pragma unroll
+        for (int r = 0; r < IB; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 #pragma unroll 8
         for (int l = 0; l < L; l++) {
-            const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
             const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
-            acc[0][0] = fmaf(a.x, b.x, acc[0][0]); acc[0][1] = fmaf(a.x, b.y, acc[0][1]);
-            acc[0][2] = fmaf(a.x, b.z, acc[0][2]); acc[0][3] = fmaf(a.x, b.w, acc[0][3]);
-            acc[1][0] = fmaf(a.y, b.x, acc[1][0]); acc[1][1] = fmaf(a.y, b.y, acc[1][1]);
-            acc[1][2] = fmaf(a.y, b.z, acc[1][2]); acc[1][3] = fmaf(a.y, b.w, acc[1][3]);
+            if constexpr (IB == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(pp + l * ldp);
+                fma_row4(acc[0], a.x, b); fma_row4(acc[1], a.y, b); fma_row4(acc[2], a.z, b); fma_row4(acc[3], a.w, b);
+            } else {
+                const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
+                fma_row4(acc[0], a.x, b); fma_row4(acc[1], a.y, b);
+            }
         }
-        emit(2 * ib, 4 * jb, acc[0]);
-        if (2 * ib + 1 < I) emit(2 * ib + 1, 4 * jb, acc[1]);
+#pragma unroll
+        for (int r = 0; r < IB; r++)
+            if (IB * ib + r < I) emit(IB * ib + r, 4 * jb, acc[r]);
     }
 }
 
 // Rows form: C[i][j] = sum_l P[i * ldp + l] * Q[l * ldq + j], same rules.  The P rows are read four l
 // at a time (ldp a multiple of 4); the l beyond a multiple of 4 are done one by one, so nothing past
 // L enters a sum.  Rows i >= I of P are read (into results that are not emitted): P must have
-// I rounded up to 2 rows.
-template <typename Emit>
+// I rounded up to IB rows.
+template <int IB, typename Emit>
 __device__ __forceinline__ void gemm_rows(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
                                           int I, int J, int L, Emit emit)
 {
-    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
+    const int ib_n = (I + IB - 1) / IB, jb_n = (J + 3) >> 2;
     const int L4 = L & ~3;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
         const int jb = blk % jb_n, ib = blk / jb_n;
-        const float* p0 = P + (2 * ib) * ldp;
-        const float* p1 = p0 + ldp;
+        const float* p0 = P + (IB * ib) * ldp;
         const float* qq = Q + 4 * jb;
-        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        const auto step = [&](float a0, float a1, const float4 b) {
-            acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
-            acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
-            acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
-            acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
-        };
+        float acc[IB][4];
+#pragma unroll
+        for (int r = 0; r < IB; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 #pragma unroll 2
         for (int l = 0; l < L4; l += 4) {
-            const float4 a0 = *reinterpret_cast<const float4*>(p0 + l);
-            const float4 a1 = *reinterpret_cast<const float4*>(p1 + l);
+            float4 a[IB];
+#pragma unroll
+            for (int r = 0; r < IB; r++) a[r] = *reinterpret_cast<const float4*>(p0 + r * ldp + l);
             const float4 b0 = *reinterpret_cast<const float4*>(qq + l * ldq);
             const float4 b1 = *reinterpret_cast<const float4*>(qq + (l + 1) * ldq);
             const float4 b2 = *reinterpret_cast<const float4*>(qq + (l + 2) * ldq);
             const float4 b3 = *reinterpret_cast<const float4*>(qq + (l + 3) * ldq);
-            step(a0.x, a1.x, b0);
-            step(a0.y, a1.y, b1);
-            step(a0.z, a1.z, b2);
-            step(a0.w, a1.w, b3);
+#pragma unroll
+            for (int r = 0; r < IB; r++) {
+                fma_row4(acc[r], a[r].x, b0);
+                fma_row4(acc[r], a[r].y, b1);
+                fma_row4(acc[r], a[r].z, b2);
+                fma_row4(acc[r], a[r].w, b3);
+            }
         }
-        for (int l = L4; l < L; l++) step(p0[l], p1[l], *reinterpret_cast<const float4*>(qq + l * ldq));
-        emit(2 * ib, 4 * jb, acc[0]);
-        if (2 * ib + 1 < I) emit(2 * ib + 1, 4 * jb, acc[1]);
+        for (int l = L4; l < L; l++) {
+            const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
+#pragma unroll
+            for (int r = 0; r < IB; r++) fma_row4(acc[r], p0[r * ldp + l], b);
+        }
+#pragma unroll
+        for (int r = 0; r < IB; r++)
+            if (IB * ib + r < I) emit(IB * ib + r, 4 * jb, acc[r]);
     }
 }
 
@@ -244,6 +265,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     // summed like everything else).  The paddings of the operand tiles may hold anything: a
     // product reads them only into outputs that are never emitted.
     for (int i = tid; i < p.total; i += THREADS) s[p.s_grad + i] = 0.f;
+    // this thread's first input elements: requested before the parameters are unpacked
+    constexpr int X_FIRST = 2;
+    float x_first[X_FIRST];
+#pragma unroll
+    for (int u = 0; u < X_FIRST; u++) {
+        const int i = tid + u * THREADS;
+        x_first[u] = i < nrows * p.dims[0] ? a.x[static_cast<long long>(row0) * p.dims[0] + i] : 0.f;
+    }
     // parameters: 128-bit loads over the flat buffer (all in flight at once) into the flat copy
     // and into the row-major weight matrices
     constexpr int PAR_BATCH = 8;          // float4 loads per thread issued before the first is used
@@ -284,10 +313,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
     {
         const int K = p.dims[0], Kp = pad4(K);
-        for (int i = tid; i < nrows * K; i += THREADS) {
-            const int r = i / K, k = i - r * K;
-            s[p.s_act[0] + r * Kp + k] = a.x[static_cast<long long>(row0) * K + i];
+#pragma unroll
+        for (int u = 0; u < X_FIRST; u++) {
+            const int i = tid + u * THREADS;
+            if (i < nrows * K) s[p.s_act[0] + (i / K) * Kp + (i % K)] = x_first[u];
         }
+        for (int i = tid + X_FIRST * THREADS; i < nrows * K; i += THREADS)
+            s[p.s_act[0] + (i / K) * Kp + (i % K)] = a.x[static_cast<long long>(row0) * K + i];
     }
     __syncthreads();
     // W^T for the forward pass: thread <-> (k, four rows n): four reads down a column of W (lanes on
@@ -308,6 +340,11 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
     __syncthreads();
 
+    // 2-row output blocks throughout: the 4-row form (half the shared-memory bytes per FMA) measured
+    // slower at every batch size here -- it leaves half the threads without a block, and these
+    // products are bound by latency, not by shared-memory bandwidth
+    const bool tall_rows = false;
+
     // ---- 2a. forward ------------------------------------------------------------------------
     for (int l = 0; l < L; l++) {
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Np = pad4(N);
@@ -315,14 +352,16 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const int act = l + 1 < L ? p.act : TT_ACT_NONE;
         float* y = s + p.s_act[l + 1];
         // y[r][n] = sum_k x[r][k] * W^T[k][n]
-        gemm_rows(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, [&](int r, int n0, const float* acc) {
+        const auto fwd_emit = [&](int r, int n0, const float* acc) {
             float4 v;
             v.x = act_fwd(acc[0] + bias[n0], act);
             v.y = n0 + 1 < N ? act_fwd(acc[1] + bias[n0 + 1], act) : 0.f;
             v.z = n0 + 2 < N ? act_fwd(acc[2] + bias[n0 + 2], act) : 0.f;
             v.w = n0 + 3 < N ? act_fwd(acc[3] + bias[n0 + 3], act) : 0.f;
             *reinterpret_cast<float4*>(y + r * Np + n0) = v;
-        });
+        };
+        if (tall_rows) gemm_rows<4>(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, fwd_emit);
+        else           gemm_rows<2>(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, fwd_emit);
         __syncthreads();
     }
 
@@ -371,7 +410,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K);
         // dW[n][k] = sum_r g[r][n] * x[r][k]
         float* dw = grad + p.w_off[l];
-        gemm_outer(g, gw, s + p.s_act[l], Kp, N, K, nrows, [&](int n, int k0, const float* acc) {
+        const auto dw_emit = [&](int n, int k0, const float* acc) {
             float* d = dw + n * K + k0;
             if ((K & 3) == 0) {
                 *reinterpret_cast<float4*>(d) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -381,7 +420,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
                 if (k0 + 2 < K) d[2] = acc[2];
                 if (k0 + 3 < K) d[3] = acc[3];
             }
-        });
+        };
+        gemm_outer<2>(g, gw, s + p.s_act[l], Kp, N, K, nrows, dw_emit);
         // db[n] = sum_r g[r][n], ascending r
         float* db = grad + p.b_off[l];
         for (int n = tid; n < N; n += THREADS) {
@@ -395,12 +435,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
             const float* h = s + p.s_act[l];
             float* gn = s + p.s_g[gcur ^ 1];
             const int act = p.act;
-            gemm_rows(g, gw, s + p.s_w[l], Kp, nrows, K, N, [&](int r, int k0, const float* acc) {
+            const auto dx_emit = [&](int r, int k0, const float* acc) {
                 const float4 y = *reinterpret_cast<const float4*>(h + r * Kp + k0);
                 *reinterpret_cast<float4*>(gn + r * gw + k0) =
                     make_float4(ew::act_grad(y.x, acc[0], act), ew::act_grad(y.y, acc[1], act),
                                 ew::act_grad(y.z, acc[2], act), ew::act_grad(y.w, acc[3], act));
-            });
+            };
+            if (tall_rows) gemm_rows<4>(g, gw, s + p.s_w[l], Kp, nrows, K, N, dx_emit);
+            else           gemm_rows<2>(g, gw, s + p.s_w[l], Kp, nrows, K, N, dx_emit);
             __syncthreads();
             gcur ^= 1;
             g = gn;
@@ -535,12 +577,12 @@ int launch(cudaStream_t st, const tt_mlp_desc* net, float* params, float* m, flo
     for (int i = 0; i <= net->n_layers; i++)
         if (net->dims[i] < 1 || net->dims[i] > MAX_WIDTH) return TT_ERR_UNSUPPORTED;
     if (batch < 1 || batch > g_max_cluster * MAX_ROWS) return TT_ERR_UNSUPPORTED;
-    // Cluster size: about 16 rows per CTA up to the largest cluster, then more rows per CTA.  The
+    // Cluster size: about 8 rows per CTA up to the largest cluster, then more rows per CTA.  The
     // choice depends on the batch only, so the summation order does too.
     // At least four CTAs: the optimizer part (a slice of the parameters per CTA) is worth
     // spreading even when one CTA holds all the rows.
     int C = g_max_cluster < 4 ? g_max_cluster : 4;
-    while (C < g_max_cluster && batch > 16 * C) C *= 2;
+    while (C < g_max_cluster && batch > 8 * C) C *= 2;
     int rows = (batch + C - 1) / C;
     Plan plan = make_plan(*net, rows);
     if (static_cast<size_t>(plan.floats) * sizeof(float) > MAX_SMEM_BYTES) return TT_ERR_UNSUPPORTED;

@@ -110,6 +110,20 @@ __device__ __forceinline__ float apply_act(float v, int act)
     return v;
 }
 
+// Bias and activation of four adjacent outputs (columns c0 .. c0 + 3, those < ncols).  Kept out of
+// line on purpose: inlined into the fully unrolled store loops (up to 128 outputs per thread, each
+// with its own copy of tanhf) it made the epilogue tens of kilobytes of code that every tile had to
+// pull through the instruction cache, which showed as `no_instruction` stalls on short-K shapes
+// even when no bias or activation was asked for.  The store loops call it only when there is one.
+__device__ __noinline__ void bias_act4(float* v, const float* __restrict__ bias, int c0, int ncols, int act)
+{
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (bias && c0 + j < ncols) v[j] += __ldg(bias + c0 + j);
+        v[j] = apply_act(v[j], act);
+    }
+}
+
 // Batch coordinates (TMA coordinate slots 0..2 per operand) of batch entry bidx.
 struct BatchCoords {
     int a[3], b[3];
@@ -444,6 +458,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             float* cmat = p.c + static_cast<long long>(bidx) * p.shape.M * p.shape.N;
             const float* bias = p.epi.bias;
             const int act = p.epi.act;
+            const bool plain = bias == nullptr && act == 0;
 #pragma unroll
             for (int h = 0; h < HALVES; h++)
 #pragma unroll
@@ -462,11 +477,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             float v[4];
 #pragma unroll
                             for (int j = 0; j < 4; j++) v[j] = acc_at(ai, jb * 4 + j);
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                if (bias && cidx + j < p.shape.N) v[j] += __ldg(bias + cidx + j);
-                                v[j] = apply_act(v[j], act);
-                            }
+                            if (!plain) bias_act4(v, bias, cidx, p.shape.N, act);
                             if (p.c_vec_ok && cidx + 3 < p.shape.N) {
                                 *reinterpret_cast<float4*>(crow + cidx) = make_float4(v[0], v[1], v[2], v[3]);
                             } else {
@@ -570,11 +581,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                             float v[4];
     #pragma unroll
                             for (int j = 0; j < 4; j++) v[j] = acc_at(ai, jb * 4 + j);
-    #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                if (bias && lc + j < col_lim) v[j] += __ldg(bias + lc + j);
-                                v[j] = apply_act(v[j], act);
-                            }
+                            if (bias != nullptr || act != 0) bias_act4(v, bias, lc, col_lim, act);
                             if (vec_ok && lc + 3 < col_lim) {
                                 *reinterpret_cast<float4*>(crow + lc) = make_float4(v[0], v[1], v[2], v[3]);
                             } else {

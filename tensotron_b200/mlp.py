@@ -33,9 +33,9 @@ from .runtime import ACT, LOSS, TT_LOSS_CE, TT_MATH_FP32, TensorRuntime, Tensotr
 def shard_rows(total, world, rank):
     """Contiguous row block [start, end) of `total` rows owned by `rank` (same split as the
     reference's ParallelRows: ceil-sized blocks, src/Tensotron/CpuKernels.cs:461-472)."""
-    per = (total + world - 1) // world
-    start = min(total, rank * per)
-    return start, min(total, start + per)
+    from .runtime import shard_range
+    start, count = shard_range(total, world, rank)     # the split lives behind the C ABI (tt_shard_range)
+    return start, start + count
 
 
 def layer_layout(dims):

@@ -12,7 +12,7 @@ import math
 
 import torch
 
-from .runtime import ACT, TensorRuntime, TensotronGemmError, broadcast_batch
+from .runtime import ACT, Conv2dDesc, TensorRuntime, TensotronGemmError, broadcast_batch
 
 _runtime = {}
 
@@ -240,6 +240,47 @@ def MatMulNTBackward(a, b, g):
     dB = torch.empty((N, K), dtype=torch.float32, device=a.device)
     rt.LaunchMatMul(g, a, dB, N, K, M, 1, N, K, 1)
     return dA, dB
+
+
+def _conv_desc(x, weight, stride, padding, dilation):
+    if x.dim() != 4:
+        raise TensotronGemmError(1, "Conv2d expects (N,C,H,W), got %s." % list(x.shape))
+    if weight.dim() != 4:
+        raise TensotronGemmError(1, "Conv2d weight must be (O,C,kh,kw), got %s." % list(weight.shape))
+    if weight.shape[1] != x.shape[1]:
+        raise TensotronGemmError(1, "Conv2d channel mismatch: input %d vs weight %d." % (x.shape[1], weight.shape[1]))
+    d = Conv2dDesc()
+    d.n, d.c, d.h, d.w = (int(v) for v in x.shape)
+    d.o, d.kh, d.kw = int(weight.shape[0]), int(weight.shape[2]), int(weight.shape[3])
+    d.stride, d.padding, d.dilation = int(stride), int(padding), int(dilation)
+    ho = (d.h + 2 * d.padding - d.dilation * (d.kh - 1) - 1) // d.stride + 1
+    wo = (d.w + 2 * d.padding - d.dilation * (d.kw - 1) - 1) // d.stride + 1
+    if ho <= 0 or wo <= 0:
+        raise TensotronGemmError(1, "Im2Col: non-positive output size (%dx%d) for %s." % (ho, wo, list(x.shape)))
+    return d, ho, wo
+
+
+def Conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1):
+    """TensorOps.Conv2d (src/Tensotron/TensorOps.Conv.cs:60-80): im2col + batched matmul + bias, on
+    the batched GEMM engine.  The handle workspace must hold the columns
+    (TensorRuntime.Conv2dWorkspace)."""
+    _check(x), _check(weight)
+    d, ho, wo = _conv_desc(x, weight, stride, padding, dilation)
+    y = torch.empty((d.n, d.o, ho, wo), dtype=torch.float32, device=x.device)
+    runtime(x.device.index).LaunchConv2dForward(d, x, weight, bias, y)
+    return y
+
+
+def Conv2dBackward(x, weight, g, stride=1, padding=0, dilation=1, need_dx=True, has_bias=True):
+    """(dx, dW, dbias) for upstream gradient g of Conv2d's output: what the reference's autograd
+    chain (bias add, broadcast matmul, Im2Col) hands to AddGrad."""
+    _check(x), _check(weight), _check(g)
+    d, _, _ = _conv_desc(x, weight, stride, padding, dilation)
+    dx = torch.empty_like(x) if need_dx else None
+    dw = torch.empty_like(weight)
+    db = torch.empty((d.o,), dtype=torch.float32, device=x.device) if has_bias else None
+    runtime(x.device.index).LaunchConv2dBackward(d, x, weight, g, dx, dw, db)
+    return dx, dw, db
 
 
 class Linear:

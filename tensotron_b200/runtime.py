@@ -21,6 +21,7 @@ EXPORTS = [
     "tt_matmul", "tt_matmul_batched", "tt_matmul_batched_reduce", "tt_linear_fwd", "tt_linear_bwd", "tt_softmax_cross_entropy",
     "tt_adam_step", "tt_add_into", "tt_broadcast_batch", "tt_get_stats", "tt_reset_stats", "tt_check",
     "tt_set_variant", "tt_softmax_cross_entropy_static", "tt_mse_loss", "tt_clip_grad_norm", "tt_mlp_train_step", "tt_reduce_sum_axes",
+    "tt_conv2d_workspace", "tt_conv2d_fwd", "tt_conv2d_bwd", "tt_shard_range",
     "tt_peer_alloc", "tt_peer_free", "tt_peer_export", "tt_peer_open", "tt_peer_close", "tt_peer_group_create",
     "tt_peer_group_destroy", "tt_peer_linear_bwd", "tt_peer_push", "tt_peer_adam_step", "tt_peer_sync",
     "tt_peer_set_wait_limit",
@@ -42,6 +43,11 @@ class MlpDesc(ctypes.Structure):
     """tt_mlp_desc: a small MLP for tt_mlp_train_step."""
     _fields_ = [("n_layers", ctypes.c_int), ("dims", ctypes.c_int * (MLP_MAX_LAYERS + 1)),
                 ("act", ctypes.c_int), ("loss", ctypes.c_int)]
+
+
+class Conv2dDesc(ctypes.Structure):
+    """tt_conv2d_desc."""
+    _fields_ = [(n, ctypes.c_int) for n in ("n", "c", "h", "w", "o", "kh", "kw", "stride", "padding", "dilation")]
 
 
 class Stats(ctypes.Structure):
@@ -82,6 +88,11 @@ def load_library(path=None):
     L.tt_softmax_cross_entropy_static.argtypes = [vp, vp, vp, vp, vp, i, i, f]
     L.tt_adam_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, i]
     L.tt_reduce_sum_axes.argtypes = [vp, vp, vp, vp, i, ip, ip]
+    cd = ctypes.POINTER(Conv2dDesc)
+    L.tt_conv2d_workspace.argtypes = [cd, i]
+    L.tt_conv2d_workspace.restype = ctypes.c_size_t
+    L.tt_conv2d_fwd.argtypes = [vp, vp, cd, vp, vp, vp, vp]
+    L.tt_conv2d_bwd.argtypes = [vp, vp, cd, vp, vp, vp, vp, vp, vp]
     L.tt_mse_loss.argtypes = [vp, vp, vp, vp, vp, vp, ll]
     L.tt_clip_grad_norm.argtypes = [vp, vp, vp, ll, f, f, vp]
     L.tt_mlp_train_step.argtypes = [vp, vp, ctypes.POINTER(MlpDesc), vp, vp, vp, vp, vp, vp, vp, vp, i, f, f, f, f, f, f]
@@ -131,6 +142,19 @@ def softmax_cross_entropy_static(logits, labels, dlogits, loss, rows, classes, s
         raise TensotronGemmError(rc, "rows %d exceed the built-in scratch (%d rows)" % (rows, STATIC_CE_MAX_ROWS))
     if rc:
         raise TensotronGemmError(rc, "tt_softmax_cross_entropy_static failed")
+
+
+def shard_range(total, world, rank):
+    """tt_shard_range: the contiguous block [start, start + count) of `total` units that `rank` of
+    `world` owns (ceil-sized blocks)."""
+    L = load_library()
+    L.tt_shard_range.argtypes = [ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]
+    s, c = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    rc = L.tt_shard_range(total, world, rank, ctypes.byref(s), ctypes.byref(c))
+    if rc:
+        raise TensotronGemmError(rc, "bad shard arguments")
+    return s.value, c.value
 
 
 def broadcast_batch(a_dims, a_strides, b_dims, b_strides):
@@ -222,6 +246,18 @@ class TensorRuntime:
             self._h, self._st(stream), _ptr(a), _ptr(b), _ptr(c), M, N, K, aMs, aKs, bKs, bNs,
             len(batchDims), _iarr(batchDims), _iarr(aBatchStrides), _iarr(bBatchStrides),
             _iarr(reduceAxis)))
+
+    @staticmethod
+    def Conv2dWorkspace(desc, backward=False):
+        return load_library().tt_conv2d_workspace(ctypes.byref(desc), 1 if backward else 0)
+
+    def LaunchConv2dForward(self, desc, x, w, bias, y, stream=None):
+        """Conv2d = Im2Col + batched matmul + bias (src/Tensotron/TensorOps.Conv.cs:60-80)."""
+        self._ck(self._L.tt_conv2d_fwd(self._h, self._st(stream), ctypes.byref(desc), _ptr(x), _ptr(w), _ptr(bias), _ptr(y)))
+
+    def LaunchConv2dBackward(self, desc, x, w, dy, dx, dw, dbias, stream=None):
+        self._ck(self._L.tt_conv2d_bwd(self._h, self._st(stream), ctypes.byref(desc), _ptr(x), _ptr(w), _ptr(dy),
+                                       _ptr(dx), _ptr(dw), _ptr(dbias)))
 
     def LaunchReduceSumAxes(self, src, dst, dims, reduceAxis, stream=None):
         """ReduceGradToShape's sum over the marked axes (src/Tensotron/TensorOps.cs:76-100), fixed order."""

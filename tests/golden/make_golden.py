@@ -7,7 +7,7 @@ Run in a checkout that has the reference mounted:
 Two sources go into tests/golden/*.json:
 
 1. The reference's own torch fixtures that pin this path
-   (tests/Tensotron.Tests/Fixtures/{matmul,matmul_nd,add,unary,losses,optim}.json).
+   (tests/Tensotron.Tests/Fixtures/{matmul,matmul_nd,add,unary,losses,optim,conv}.json).
    Only the cases on the path are kept.  Every kept case is re-computed with the
    local torch (same version as the fixtures' torch_version) and must reproduce the
    recorded output and gradients, so a drifted fixture cannot slip in.
@@ -103,6 +103,14 @@ def from_reference(ref_root):
             opt.step()
         _close(p, c["output"]["data"], c["name"])
     out["groups"]["adam"] = adam
+
+    conv = [c for c in load("conv")["cases"] if c["meta"]["op"] == "conv2d"]
+    assert len(conv) == 5
+    for c in conv:
+        cfg = c["meta"]["config"]
+        _recheck(c, lambda x, w, b=None, cfg=cfg: torch.nn.functional.conv2d(
+            x, w, b, stride=cfg["stride"], padding=cfg["padding"], dilation=cfg["dilation"]))
+    out["groups"]["conv2d"] = conv
     return out
 
 

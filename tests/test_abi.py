@@ -12,7 +12,7 @@ from tensotron_b200 import runtime
 
 def test_library_exports_every_declared_symbol(gemm_lib):
     header = open(os.path.join(ROOT, "include", "tensotron_gemm.h")).read()
-    declared = re.findall(r"TT_API\s+(?:const\s+char\*|int)\s+(tt_\w+)\s*\(", header)
+    declared = re.findall(r"TT_API\s+(?:const\s+char\*|int|size_t)\s+(tt_\w+)\s*\(", header)
     assert len(declared) >= 18
     for name in declared:
         assert getattr(gemm_lib, name) is not None, name
@@ -29,6 +29,19 @@ def test_broadcast_batch_matches_reference_rules(gemm_lib):
     assert runtime.broadcast_batch([2, 1], [6, 6], [2], [15]) == ([2, 2], [6, 0], [0, 15])
     with pytest.raises(runtime.TensotronGemmError):
         runtime.broadcast_batch([3], [6], [4], [15])
+
+
+def test_shard_range_is_the_ceil_block_split(gemm_lib):
+    for total, world in ((16384, 8), (32, 3), (5, 8), (0, 2), (1000, 7)):
+        per = -(-total // world)
+        covered = 0
+        for rank in range(world):
+            s, c = runtime.shard_range(total, world, rank)
+            assert s == min(total, rank * per) and c == min(total, s + per) - s
+            covered += c
+        assert covered == total
+    with pytest.raises(runtime.TensotronGemmError):
+        runtime.shard_range(10, 2, 2)
 
 
 def test_null_handle_and_bad_arguments_are_status_codes(gemm_lib):

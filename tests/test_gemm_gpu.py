@@ -109,12 +109,36 @@ def test_config1_uniform_seed0(rt):
         assert np.abs(got - exp).max() <= fp32_bound(512, a, b)
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 512), (64, 64, 128), (64, 128, 64), (200, 36, 1000), (512, 512, 512), (100, 300, 4096)])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_small_outputs_cut_k_across_a_cluster_in_one_launch(rt, shape, layout):
+    """A few output tiles and a long K (benchmark config 1; the GEMMs of the small networks): the
+    any-stride kernel cuts K across the CTAs of a thread-block cluster, which add their partial
+    tiles through distributed shared memory in ascending k -- one launch, and the same bits as the
+    two-launch form that adds the ranges through the workspace (variant 8)."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 2 * N + 3 * K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = layout_strides(layout, M, N, K)
+    rt.ResetCounters()
+    one = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    assert stats["generic"] == 1 and stats["launches"] == 1, stats
+    two = run_matmul(rt, a, b, M, N, K, st, 8)
+    assert np.array_equal(one, two)
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(one - exp).max() <= fp32_bound(K, a, b)
+    again = run_matmul(rt, a, b, M, N, K, st, 0)
+    assert np.array_equal(one, again)
+
+
 def test_tma_kernel_serves_aligned_shapes(rt):
     rng = np.random.default_rng(1)
-    a = rng.uniform(-1, 1, (512, 256)).astype(np.float32)
-    b = rng.uniform(-1, 1, (256, 384)).astype(np.float32)
+    a = rng.uniform(-1, 1, (1024, 256)).astype(np.float32)
+    b = rng.uniform(-1, 1, (256, 768)).astype(np.float32)
     rt.ResetCounters()
-    run_matmul(rt, a, b, 512, 384, 256, (256, 1, 384, 1))
+    run_matmul(rt, a, b, 1024, 768, 256, (256, 1, 768, 1))
     s = rt.Stats()
     # one GEMM launch, plus the split-K reduction when the plan cut K
     assert s["simt_tma"] == 1 and s["generic"] == 0 and s["launches"] == 1 + s["splitk"]
@@ -136,10 +160,10 @@ def test_bitwise_repeatable_and_grid_independent(rt):
     r4 = run_matmul(rt, a, b, M, N, K, (K, 1, N, 1), 1)
     exp = oracle.matmul2d(a, b, M, N, K, K, 1, N, 1)
     assert np.abs(r4 - exp).max() <= fp32_bound(K, a, b)
-    # without split-K (short K) the any-stride kernel also reproduces the bits
-    a2, b2 = a[:M * 256].copy(), b[:256 * N].copy()
-    assert np.array_equal(run_matmul(rt, a2, b2, M, N, 256, (256, 1, N, 1), 2),
-                          run_matmul(rt, a2, b2, M, N, 256, (256, 1, N, 1), 1))
+    # without a cut along K (short K) the any-stride kernel also reproduces the bits
+    a2, b2 = a[:M * 64].copy(), b[:64 * N].copy()
+    assert np.array_equal(run_matmul(rt, a2, b2, M, N, 64, (64, 1, N, 1), 2),
+                          run_matmul(rt, a2, b2, M, N, 64, (64, 1, N, 1), 1))
 
 
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
@@ -541,21 +565,24 @@ def test_add_into(rt):
 def test_tensor_map_descriptors_are_cached_per_buffer_and_shape(rt):
     """The TMA descriptors of a call are a function of (pointer, dims, strides, box): the second
     call on the same buffers re-encodes nothing, another buffer or shape does."""
-    a = torch.randn(512, 256, device="cuda")
-    b = torch.randn(256, 384, device="cuda")
-    c = torch.empty(512, 384, device="cuda")
-    rt.LaunchMatMul(a, b, c, 512, 384, 256, 256, 1, 384, 1)
+    M, N, K = 1024, 768, 256
+    a = torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda")
+    c = torch.empty(M, N, device="cuda")
+    rt.LaunchMatMul(a, b, c, M, N, K, K, 1, N, 1)
     rt.ResetCounters()
-    rt.LaunchMatMul(a, b, c, 512, 384, 256, 256, 1, 384, 1)
+    rt.LaunchMatMul(a, b, c, M, N, K, K, 1, N, 1)
     s = rt.Stats()
     assert s["simt_tma"] == 1 and s["tensor_map_misses"] == 0 and s["tensor_map_hits"] == 2, s
-    a2 = torch.randn(512, 256, device="cuda")
-    rt.LaunchMatMul(a2, b, c, 512, 384, 256, 256, 1, 384, 1)
+    # the same product read through another leading dimension: a new descriptor for A only
+    a2 = torch.randn(M, K + 72, device="cuda")
+    rt.LaunchMatMul(a2, b, c, M, N, K, K + 72, 1, N, 1)
     s = rt.Stats()
     assert s["tensor_map_misses"] == 1 and s["tensor_map_hits"] == 3, s
     rt.Check()
-    exp = oracle.matmul2d(a2.cpu().numpy(), b.cpu().numpy(), 512, 384, 256, 256, 1, 384, 1)
-    assert np.abs(c.cpu().numpy() - exp).max() <= fp32_bound(256, a2.cpu().numpy(), b.cpu().numpy())
+    a2h = a2.cpu().numpy()
+    exp = oracle.matmul2d(a2h, b.cpu().numpy(), M, N, K, K + 72, 1, N, 1)
+    assert np.abs(c.cpu().numpy() - exp).max() <= fp32_bound(K, a2h, b.cpu().numpy())
 
 
 # ---- stream capture (the reference's native-graph contract) --------------------------------

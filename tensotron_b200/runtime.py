@@ -171,6 +171,17 @@ def broadcast_batch(a_dims, a_strides, b_dims, b_strides):
     return list(dims)[:r], list(a_bs)[:r], list(b_bs)[:r]
 
 
+_parked = []     # handles whose owner was collected during a stream capture: destroyed later
+
+
+def _capturing():
+    try:
+        import torch
+        return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+    except Exception:
+        return False
+
+
 class TensorRuntime:
     """The CUDA-backend runtime surface of the matmul path, one handle per device."""
 
@@ -188,9 +199,20 @@ class TensorRuntime:
         if self._h:
             self._L.tt_destroy(self._h)
             self._h = ctypes.c_void_p()
+        while _parked and not _capturing():
+            L, h = _parked.pop()
+            L.tt_destroy(h)
 
     def __del__(self):
+        # The garbage collector may run this at any point, also while some stream of the process is
+        # being captured into a CUDA graph -- and tt_destroy frees device memory, which invalidates a
+        # capture in progress.  So a handle that dies during a capture is parked and destroyed with
+        # the next one that dies (or is disposed) outside a capture.
         try:
+            if self._h and _capturing():
+                _parked.append((self._L, self._h))
+                self._h = ctypes.c_void_p()
+                return
             self.Dispose()
         except Exception:
             pass

@@ -165,6 +165,8 @@ def test_exchange_step_replays_from_a_cuda_graph():
             _emulated_step(eager, x, y)
         _emulated_step(graphed, x, y)                      # warm-up: buffers allocated, step 1 done
         torch.cuda.synchronize()
+        import gc
+        gc.collect()                                       # no handle of an earlier test dies (and frees) mid-capture
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             _emulated_step(graphed, x, y, check=False)     # recorded, not run

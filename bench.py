@@ -30,7 +30,7 @@ UNIT = "TFLOP/s"
 # DRAM bytes (read + write) per launch of sgemm_simt_kernel from one ncu capture, keyed by problem
 # edge.  8192 is captured; 16384 is that capture scaled (reads x 8, writes x 4), because a
 # 3 GB / 157 ms launch is too large to capture.
-NCU_TRAFFIC_BYTES = {8192: 3366821376 + 254345472, 16384: 8 * 3366821376 + 4 * 254345472}
+NCU_TRAFFIC_BYTES = {8192: 2241620992 + 260361984, 16384: 8 * 2241620992 + 4 * 260361984}
 
 
 def env_int(name, default):
@@ -393,11 +393,23 @@ def mlp_steps_per_s(rt, rank, world, local_rank, pg, steps=10, warmup=3):
             gen.manual_seed(1)
             y = torch.randint(0, 10, (gb,), generator=gen, device="cuda", dtype=torch.int32)[s:e].contiguous()
             cur_gb = gb
+        tr, err = None, None
         try:
             tr = MlpTrainer([784, 4096, 4096, 4096, 10], rt=rt, device=local_rank, lr=1e-3, seed=2,
                             process_group=pg, math_mode=mode, exchange=exchange)
         except Exception as ex:     # e.g. peer mapping refused by the platform: report, keep the other runs
-            res[name] = {"error": "%s: %s" % (type(ex).__name__, ex)}
+            err = "%s: %s" % (type(ex).__name__, ex)
+        if world > 1:
+            # every rank skips the run when any rank failed to set it up (a rank that went on alone
+            # would wait in its first collective for the others)
+            ok = torch.tensor([0.0 if err else 1.0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0.0 and err is None:
+                err = "set-up failed on another rank"
+        if err is not None:
+            if tr is not None:
+                tr.close()
+            res[name] = {"error": err}
             continue
         for _ in range(warmup):
             tr.step(x, y, global_batch=gb)
@@ -576,6 +588,30 @@ def run_one_mlp(spec):
     tr.close()
 
 
+def run_one_step(spec):
+    """--one-step DIMS BATCH STEPS: times the one-launch training step (tt_mlp_train_step) of a small
+    Tanh MLP with MSE loss, ClipGradNorm(0.5) and Adam(1e-3) -- DIMS like 8,64,64,2 -- eagerly and
+    under CUDA-graph replay (10 steps per graph)."""
+    import torch
+
+    from tensotron_b200.mlp import MlpTrainer
+    from tensotron_b200.runtime import TensorRuntime
+    dims, batch, steps = [int(v) for v in spec[0].split(",")], int(spec[1]), int(spec[2])
+    rt = TensorRuntime(0, 64 << 20)
+    tr = MlpTrainer(dims, rt=rt, lr=1e-3, seed=3, act="tanh", loss="mse", max_grad_norm=0.5, fused=True)
+    x = torch.rand((batch, dims[0]), device="cuda") - 0.5
+    t = torch.zeros((batch, dims[-1]), device="cuda")
+    ms = time_calls(lambda: tr.step(x, t), steps, warmup=5)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(10):
+            tr.step(x, t)
+    us = time_calls(g.replay, 10, warmup=2) / 10 * 1e3
+    rt.Check()
+    print("ok one-launch step %s batch %d: %.2f us eager, %.2f us per step under graph replay"
+          % (spec[0], batch, ms * 1e3, us))
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
     if rank != 0:
@@ -607,6 +643,7 @@ def main():
     ap.add_argument("--one", nargs="+", metavar="ARG", help="MxNxK LAYOUT VARIANT MODE ITERS [graph]: time one GEMM shape and exit")
     ap.add_argument("--one-bmm", nargs="+", metavar="ARG", help="MODE ITERS [transposed_b]: time benchmark config 3 and exit")
     ap.add_argument("--one-mlp", nargs="+", metavar="ARG", help="ROWS MODE EXCHANGE STEPS: time the benchmark MLP step on ROWS rows and exit")
+    ap.add_argument("--one-step", nargs="+", metavar="ARG", help="DIMS BATCH STEPS: time the one-launch small-MLP training step and exit")
     args = ap.parse_args()
     if args.one:
         return run_one(args.one)
@@ -614,6 +651,8 @@ def main():
         return run_one_bmm(args.one_bmm)
     if args.one_mlp:
         return run_one_mlp(args.one_mlp)
+    if args.one_step:
+        return run_one_step(args.one_step)
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     rank = env_int("RANK", 0)

@@ -13,7 +13,17 @@
  *     stream.  Every call only enqueues stream-ordered work: no synchronisation,
  *     no allocation, no host-visible side effect, so a call can be re-fired under
  *     stream capture (src/Tensotron/TensorRuntime.cs:596-698).
- *   - single caller thread per handle (README.md:168-170); no internal locking.
+ *   - single caller thread per handle (README.md:168-170); no internal locking.  One handle
+ *     serves ONE stream at a time: its workspace, its split-K / stream-K partial tiles and flags
+ *     and its status word are shared by all calls on the handle, so calls that may overlap on the
+ *     GPU (two streams) need two handles.
+ *   - the handle lives in the CUDA context that is current on the calling thread at tt_create
+ *     (the device's primary context only when none is current).  Every later entry runs in that
+ *     context: when another context, or none, is current, the handle's context is pushed for the
+ *     duration of the call and popped again.
+ *   - results are bit-stable from run to run for a given call on a given handle.  Forms that cut
+ *     K (small outputs, partial last waves) regroup the sum; whether they are used depends on the
+ *     shape, the SM count and the handle's free workspace.
  */
 #ifndef TENSOTRON_GEMM_H
 #define TENSOTRON_GEMM_H
@@ -59,7 +69,9 @@ TT_API const char* tt_version(void);
 
 /* Created once next to the cuBLAS handle (src/Tensotron/TensorRuntime.cs:509-510)
  * and destroyed in Dispose (:1402-1415).  `workspace_bytes` sizes the split-K /
- * backward scratch owned by the handle (0 picks a default).  Binds to `device`. */
+ * backward scratch owned by the handle (0 picks a default: 256 MiB).  The handle binds to the
+ * context that is current on the calling thread when it belongs to `device`, else to the
+ * device's primary context (which is then made current). */
 TT_API int tt_create(int device, size_t workspace_bytes, tt_handle_t* out_handle);
 TT_API int tt_destroy(tt_handle_t h);
 
@@ -67,7 +79,8 @@ TT_API int tt_destroy(tt_handle_t h);
 TT_API const char* tt_last_error(tt_handle_t h);
 
 /* Replaces AllowTf32 / SetCuBlasMathMode (src/Tensotron/TensorRuntime.cs:158-159,
- * :332-338). */
+ * :332-338).  Accepts 0, 3, 4 and 1 (cuBLAS's legacy tensor-op math, which the reference's setter
+ * also takes: served by the TF32 kernel). */
 TT_API int tt_set_math_mode(tt_handle_t h, int mode);
 TT_API int tt_get_math_mode(tt_handle_t h, int* mode);
 
@@ -129,9 +142,11 @@ TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const floa
 
 /* CrossEntropy(mean-style) forward+backward in one launch
  * (src/Tensotron/TensorOps.Losses.cs:97-108, src/Tensotron/TensorOps.Reduce.cs:122-141):
- * labels are device int32; dlogits = (softmax - onehot) * scale; *loss (device
+ * labels are device int32 in [0, classes); dlogits = (softmax - onehot) * scale; *loss (device
  * float) = scale * sum_rows(-log softmax[label]); row sums are reduced in a fixed
- * order.  `loss` and `dlogits` may each be NULL. */
+ * order.  `loss` and `dlogits` may each be NULL.  A label outside the range is never used as an
+ * index: that row's loss (and so *loss) becomes NaN, its gradient is the plain softmax, and
+ * tt_check reports TT_ERR_BAD_LABEL (the reference throws on the host for such a target). */
 TT_API int tt_softmax_cross_entropy(tt_handle_t h, void* stream, const float* logits, const int* labels,
                              float* dlogits, float* loss, int rows, int classes, float scale);
 
@@ -178,7 +193,8 @@ TT_API int tt_conv2d_bwd(tt_handle_t h, void* stream, const tt_conv2d_desc* d, c
  * until exit (TT_STATIC_CE_MAX_ROWS floats).  rows above that limit are refused with
  * TT_ERR_STATIC_LIMIT.  The call runs on the current device; its first call on a device
  * looks the array's address up, so make that call before any stream capture.  All calls
- * share the array: calls that overlap on the GPU race on it. */
+ * share the array: calls that overlap on the GPU race on it.  A label outside [0, classes)
+ * makes *loss NaN (there is no handle to report it through). */
 #define TT_STATIC_CE_MAX_ROWS 65536
 TT_API int tt_softmax_cross_entropy_static(void* stream, const float* logits, const int* labels,
                                     float* dlogits, float* loss, int rows, int classes, float scale);
@@ -270,7 +286,8 @@ TT_API int tt_check(tt_handle_t h, void* stream);
  * 6 FFMA kernel with 256x128 tiles and stream-K work distribution,
  * 7 FFMA kernel with 128x192 tiles (B contiguous along N only),
  * 8 any-stride kernel with its K ranges added through the workspace (two launches) instead of
- *   through a thread-block cluster. */
+ *   through a thread-block cluster,
+ * 9 FFMA kernel with 128x128 tiles and stream-K work distribution. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 /* ---- Data-parallel gradient exchange over peer memory ---------------------------------

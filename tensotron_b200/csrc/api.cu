@@ -360,16 +360,23 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             if (t < best_t) { best_t = t; best = SimtPlan{tm, splits, kps, false, sh.nj}; }
         }
         // stream-K: no wave quantisation (work / SMs tile-times); needs one partial-tile slot
-        // per CTA and enough k-tiles for the ranges to be worth cutting
-        if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / 2) {
+        // per CTA and enough k-tiles for the ranges to be worth cutting.  Less than one wave of
+        // 128x128 tiles may be cut over up to four CTAs per tile (a partial tile of that shape
+        // is half the traffic of a 256x128 one).
+        const bool sub_wave = tm == 8 && sh.nj == 2 && tiles < h->num_sms;
+        if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / (sub_wave ? 4 : 2)) {
             const size_t need = static_cast<size_t>(h->num_sms) * bm * bn * sizeof(float);
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
             if (need <= ws_avail && fill < 0.97) {
-                // measured: storing and re-reading the partial tiles costs about 20 us (11 units)
-                // whatever the shape, and a fully busy chip clocks a little lower than one with
-                // idle SMs (5 %)
-                const double t = ((static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost + 11.0) * 1.05;
+                // measured cost of storing and re-reading the partial tiles, in units of a 128x128
+                // k-tile: about 11 (20 us) whatever the shape, and a fully busy chip clocks a
+                // little lower than one with idle SMs (5 %); below one wave of 128x128 tiles 2.5
+                // plus 1.5 per CTA that shares a tile (1024^3: 50 us against 54 with two split-K
+                // ranges, 1024 x 1024 x 4096: 155 against 175, 768^3: 31 against 27)
+                const double body = (static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost;
+                const double t = sub_wave ? body + 2.5 + 1.5 * h->num_sms / static_cast<double>(tiles)
+                                          : (body + 11.0) * 1.05;
                 if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true, sh.nj}; }
             }
         }
@@ -527,6 +534,11 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g_in)
         plan.tm = 16; plan.nj = 2; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
         if (static_cast<size_t>(h->num_sms) * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
+    if (h->variant == 9) {
+        // pinned: 128x128 tiles with stream-K (measurements)
+        plan.tm = 8; plan.nj = 2; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
+        if (static_cast<size_t>(h->num_sms) * 128 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
+    }
     if (plan.nj == 3) return try_launch_simt_tm<8, 3>(h, st, g, plan);
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
 }
@@ -639,7 +651,8 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         const bool small_output = h->variant == 0 && g.batch.red_count == 1 && tiles64 <= h->num_sms / 2 &&
                                   vol <= SMALL_MAX_FLOP_ELEMS;
         if (!small_output &&
-            (h->variant == 2 || h->variant == 3 || h->variant == 6 || h->variant == 7 || vol >= TMA_MIN_FLOP_ELEMS)) {
+            (h->variant == 2 || h->variant == 3 || h->variant == 6 || h->variant == 7 || h->variant == 9 ||
+             vol >= TMA_MIN_FLOP_ELEMS)) {
             const int rc = try_launch_simt(h, st, g);
             if (rc != TT_ERR_UNSUPPORTED) return rc;
         }
@@ -797,13 +810,14 @@ int linear_bwd_impl(tt_handle_t h, cudaStream_t st, const float* x, const float*
         if (g_bytes_al + part_bytes > h->workspace_bytes)
             return fail(h, TT_ERR_WORKSPACE, "workspace too small for linear backward");
         float* gbuf = act != TT_ACT_NONE ? reinterpret_cast<float*>(h->workspace) : nullptr;
-        float* partial = dbias ? reinterpret_cast<float*>(h->workspace + g_bytes_al) : nullptr;
+        // one chunk of rows (M < 128): the column sums are final, they go straight to dbias
+        float* partial = !dbias ? nullptr : chunks == 1 ? dbias : reinterpret_cast<float*>(h->workspace + g_bytes_al);
         const bool vec = (N % 4 == 0) && aligned16(dy) && (!act || aligned16(y));
         const dim3 grid((N + ew::COLSUM_COLS - 1) / ew::COLSUM_COLS, chunks);
         if (vec) ew::act_bwd_colsum_kernel<true><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
         else     ew::act_bwd_colsum_kernel<false><<<grid, 256, 0, st>>>(y, dy, gbuf, partial, M, N, act, chunks);
         h->stats.launches++;
-        if (dbias) {
+        if (dbias && chunks > 1) {
             ew::colsum_finish_kernel<<<(N + 255) / 256, 256, 0, st>>>(partial, dbias, N, chunks);
             h->stats.launches++;
         }
@@ -926,7 +940,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 8) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 9) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }

@@ -20,6 +20,13 @@
 // No atomics and no flag spinning anywhere: the only cross-CTA synchronisation is the hardware
 // cluster barrier, and all CTAs of a cluster are co-scheduled by construction.
 //
+// The step is a chain of short dependent phases, and the first thing that bounds it is the
+// instruction stream itself: code that runs once per launch is fetched from L2 line by line.  So
+// the kernel is written for a small footprint: global -> shared copies are cp.async loops (no
+// register staging, nothing unrolled), the two product forms are out-of-line functions shared by
+// all their uses, the transcendental functions exist once, and the optimizer loop is rolled with
+// its operands (moments prefetched by cp.async, summed gradients) in shared memory.
+//
 // Every operand keeps its natural row-major layout in shared memory; the only transposed copy is
 // W^T (made once per launch), which the forward pass needs.  A thread owns 2 x 4 output blocks and
 // walks the contraction index l in ascending order with one accumulator per output and fused
@@ -36,6 +43,7 @@
 
 #include "elementwise.cuh"
 #include "mlp_step.h"
+#include "ptx.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -66,10 +74,12 @@ struct Plan {
     int gw;
     int s_red;                // 64 floats: block-reduction scratch [0, 32); [32 + 2r], [33 + 2r]: loss and
                               // sum-of-squares parts received from CTA r
+    int per4;                 // float4s of the flat buffer one CTA owns in the optimizer part
+    int s_m, s_v, s_sum;      // this CTA's slice of the moments and of the summed gradients [4 * per4] each
     int floats;               // total shared floats
 };
 
-inline Plan make_plan(const tt_mlp_desc& net, int rows)
+inline Plan make_plan(const tt_mlp_desc& net, int rows, int ctas)
 {
     Plan p;
     memset(&p, 0, sizeof(p));
@@ -90,13 +100,15 @@ inline Plan make_plan(const tt_mlp_desc& net, int rows)
     }
     p.total = cur;
     int off = 0, widest = 4;
+    p.s_par = off; off += p.total;
     for (int l = 0; l < net.n_layers; l++) {
         const int K = net.dims[l], N = net.dims[l + 1];
-        p.s_w[l] = off;  off += pad4(N) * pad4(K);
+        // a weight matrix whose rows are whole float4s is used where the flat copy has it
+        if ((K & 3) == 0) { p.s_w[l] = p.s_par + p.w_off[l]; }
+        else              { p.s_w[l] = off;  off += pad4(N) * pad4(K); }
         p.s_wt[l] = off; off += pad4(K) * (pad4(N) + 4);
         if (pad4(N) > widest) widest = pad4(N);
     }
-    p.s_par = off; off += p.total;
     p.s_grad = off; off += p.total;
     for (int l = 0; l <= net.n_layers; l++) {
         p.s_act[l] = off;  off += p.rp * pad4(net.dims[l]);
@@ -106,6 +118,10 @@ inline Plan make_plan(const tt_mlp_desc& net, int rows)
         p.s_g[i] = off;  off += p.rp * widest;
     }
     p.s_red = off; off += 64;
+    p.per4 = ((p.total >> 2) + ctas - 1) / ctas;
+    p.s_m = off;   off += 4 * p.per4;
+    p.s_v = off;   off += 4 * p.per4;
+    p.s_sum = off; off += 4 * p.per4;
     p.floats = off;
     return p;
 }
@@ -124,14 +140,28 @@ struct Args {
     int batch;
     float lr, b1, b2, eps, max_norm, clip_eps;
     int advance;
+    int x_vec;             // the input rows of every CTA start on 16 bytes and are whole float4s: copied by cp.async
 };
 
-__device__ __forceinline__ float act_fwd(float v, int act)
+// The functions below are deliberately NOT inlined: each exists once in the kernel's code.
+__device__ __noinline__ float act_fwd(float v, int act)
 {
     if (act == TT_ACT_RELU) return v > 0.f ? v : 0.f;
     if (act == TT_ACT_TANH) return tanhf(v);
     return v;
 }
+
+// 1 / (1 - b^t), Adam's bias correction (the arithmetic of tt_adam_advance)
+__device__ __noinline__ float inv_bias_correction(float b, float t) { return 1.f / (1.f - powf(b, t)); }
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(__cvta_generic_to_global(gmem_src))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_last() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // acc[0..3] += a * b as two packed two-wide FP32 FMAs (each lane an IEEE fused multiply-add, so
 // the bits equal four scalar fmaf).
@@ -143,88 +173,111 @@ __device__ __forceinline__ void fma_row4(float (&acc)[4], float a, const float4 
     r = __ffma2_rn(ap, make_float2(b.z, b.w), make_float2(acc[2], acc[3])); acc[2] = r.x; acc[3] = r.y;
 }
 
-// Outer form: C[i][j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending, one
-// accumulator per output, fused multiply-add).  A thread owns IB x 4 output blocks (IB = 2 or 4: the
-// taller block halves the shared-memory bytes read per FMA and is used when there are enough rows
-// to keep the threads busy).  ldp >= I rounded up to IB, ldq >= J rounded up to 4; what lies in
-// those roundings may be anything, it only reaches outputs that are not emitted.
-// `emit(i, j0, acc)` receives row i (< I) and the four columns j0 .. j0 + 3 (the caller masks j >= J).
-template <int IB, typename Emit>
-__device__ __forceinline__ void gemm_outer(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
-                                           int I, int J, int L, Emit emit)
+// Outer form: out[i * ldo + j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending,
+// one accumulator per output, fused multiply-add).  A thread owns 2 x 4 output blocks.  ldp >= I
+// rounded up to 2, ldq >= J rounded up to 4; what lies in those roundings may be anything, it only
+// reaches outputs that are not written.  Used for dW (P = g, Q = x, out = the flat gradient).
+__device__ __noinline__ void product_outer(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
+                                           int I, int J, int L, float* __restrict__ out, int ldo)
 {
-    const int ib_n = (I + IB - 1) / IB, jb_n = (J + 3) >> 2;
+    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
+    const bool vec = (ldo & 3) == 0;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
         const int jb = blk % jb_n, ib = blk / jb_n;
-        const float* pp = P + IB * ib;
+        const float* pp = P + 2 * ib;
         const float* qq = Q + 4 * jb;
-        float acc[IB][4];
+        float acc[2][4];
 #pragma unroll
-        for (int r = 0; r < IB; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-#pragma unroll 8
+        for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+#pragma unroll 4
         for (int l = 0; l < L; l++) {
             const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
-            if constexpr (IB == 4) {
-                const float4 a = *reinterpret_cast<const float4*>(pp + l * ldp);
-                fma_row4(acc[0], a.x, b); fma_row4(acc[1], a.y, b); fma_row4(acc[2], a.z, b); fma_row4(acc[3], a.w, b);
-            } else {
-                const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
-                fma_row4(acc[0], a.x, b); fma_row4(acc[1], a.y, b);
-            }
+            const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
+            fma_row4(acc[0], a.x, b);
+            fma_row4(acc[1], a.y, b);
         }
 #pragma unroll
-        for (int r = 0; r < IB; r++)
-            if (IB * ib + r < I) emit(IB * ib + r, 4 * jb, acc[r]);
+        for (int r = 0; r < 2; r++) {
+            const int i = 2 * ib + r, j0 = 4 * jb;
+            if (i >= I) continue;
+            float* d = out + i * ldo + j0;
+            if (vec) {
+                *reinterpret_cast<float4*>(d) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+            } else {
+                d[0] = acc[r][0];
+                if (j0 + 1 < J) d[1] = acc[r][1];
+                if (j0 + 2 < J) d[2] = acc[r][2];
+                if (j0 + 3 < J) d[3] = acc[r][3];
+            }
+        }
     }
 }
 
-// Rows form: C[i][j] = sum_l P[i * ldp + l] * Q[l * ldq + j], same rules.  The P rows are read four l
+// Rows form: acc[i][j] = sum_l P[i * ldp + l] * Q[l * ldq + j], same rules.  The P rows are read four l
 // at a time (ldp a multiple of 4); the l beyond a multiple of 4 are done one by one, so nothing past
-// L enters a sum.  Rows i >= I of P are read (into results that are not emitted): P must have
-// I rounded up to IB rows.
-template <int IB, typename Emit>
-__device__ __forceinline__ void gemm_rows(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
-                                          int I, int J, int L, Emit emit)
+// L enters a sum.  Rows i >= I of P are read (into results that are not written): P must have
+// I rounded up to 2 rows.  What is written (128 bits per row and column block, ldo a multiple of 4):
+//   forward (FWD)  out[i][j] = act(acc + aux[j])                      aux = the bias vector, 0 beyond J
+//   backward       out[i][j] = acc * act'(aux[i * lda + j])           aux = the layer's forward output
+constexpr int ROWS_FWD = 0, ROWS_BWD = 1;
+__device__ __noinline__ void product_rows(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
+                                          int I, int J, int L, int mode, int act, const float* __restrict__ aux, int lda,
+                                          float* __restrict__ out, int ldo)
 {
-    const int ib_n = (I + IB - 1) / IB, jb_n = (J + 3) >> 2;
+    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
     const int L4 = L & ~3;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
         const int jb = blk % jb_n, ib = blk / jb_n;
-        const float* p0 = P + (IB * ib) * ldp;
+        const float* p0 = P + (2 * ib) * ldp;
         const float* qq = Q + 4 * jb;
-        float acc[IB][4];
+        float acc[2][4];
 #pragma unroll
-        for (int r = 0; r < IB; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+        for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 #pragma unroll 2
         for (int l = 0; l < L4; l += 4) {
-            float4 a[IB];
+            float4 a[2];
 #pragma unroll
-            for (int r = 0; r < IB; r++) a[r] = *reinterpret_cast<const float4*>(p0 + r * ldp + l);
+            for (int r = 0; r < 2; r++) a[r] = *reinterpret_cast<const float4*>(p0 + r * ldp + l);
             const float4 b0 = *reinterpret_cast<const float4*>(qq + l * ldq);
             const float4 b1 = *reinterpret_cast<const float4*>(qq + (l + 1) * ldq);
             const float4 b2 = *reinterpret_cast<const float4*>(qq + (l + 2) * ldq);
             const float4 b3 = *reinterpret_cast<const float4*>(qq + (l + 3) * ldq);
 #pragma unroll
-            for (int r = 0; r < IB; r++) {
+            for (int r = 0; r < 2; r++) {
                 fma_row4(acc[r], a[r].x, b0);
                 fma_row4(acc[r], a[r].y, b1);
                 fma_row4(acc[r], a[r].z, b2);
                 fma_row4(acc[r], a[r].w, b3);
             }
         }
+#pragma unroll 1
         for (int l = L4; l < L; l++) {
             const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
 #pragma unroll
-            for (int r = 0; r < IB; r++) fma_row4(acc[r], p0[r * ldp + l], b);
+            for (int r = 0; r < 2; r++) fma_row4(acc[r], p0[r * ldp + l], b);
         }
 #pragma unroll
-        for (int r = 0; r < IB; r++)
-            if (IB * ib + r < I) emit(IB * ib + r, 4 * jb, acc[r]);
+        for (int r = 0; r < 2; r++) {
+            const int i = 2 * ib + r, j0 = 4 * jb;
+            if (i >= I) continue;
+            float4 v;
+            if (mode == ROWS_FWD) {
+                v.x = act_fwd(acc[r][0] + aux[j0], act);
+                v.y = j0 + 1 < J ? act_fwd(acc[r][1] + aux[j0 + 1], act) : 0.f;
+                v.z = j0 + 2 < J ? act_fwd(acc[r][2] + aux[j0 + 2], act) : 0.f;
+                v.w = j0 + 3 < J ? act_fwd(acc[r][3] + aux[j0 + 3], act) : 0.f;
+            } else {
+                const float4 y = *reinterpret_cast<const float4*>(aux + i * lda + j0);
+                v = make_float4(ew::act_grad(y.x, acc[r][0], act), ew::act_grad(y.y, acc[r][1], act),
+                                ew::act_grad(y.z, acc[r][2], act), ew::act_grad(y.w, acc[r][3], act));
+            }
+            *reinterpret_cast<float4*>(out + i * ldo + j0) = v;
+        }
     }
 }
 
 // Sum of v over the CTA in a fixed order: each thread's value, then a shared-memory tree.
-__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */)
+__device__ __noinline__ float block_sum(float v, float* scratch /* >= 32 floats */)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -232,6 +285,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
     __syncthreads();
     float t = 0.f;
+#pragma unroll
     for (int w = 0; w < THREADS / 32; w++) t += scratch[w];
     return t;
 }
@@ -249,8 +303,29 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     const int row0 = c * p.rows;                                  // first batch row of this CTA
     const int nrows = max(0, min(p.rows, a.batch - row0));        // rows that exist
     const int NO = p.dims[L], NOp = pad4(NO);
-    // Global loads whose values are needed late are issued first, so their latency hides behind
-    // the set-up: the optimizer's step state, and each thread's first loss target.
+    const int total4 = p.total >> 2;
+    const int lo4 = min(total4, c * p.per4), hi4 = min(total4, lo4 + p.per4);   // the optimizer slice of this CTA
+
+    // ---- 1. global -> shared ---------------------------------------------------------------------
+    // Everything the step reads from global memory is requested here, before anything waits:
+    // the parameters and the input rows (first cp.async group), this CTA's slice of the Adam
+    // moments (second group, consumed after the two cluster barriers), the step state and each
+    // thread's first loss target (registers).
+#pragma unroll 1
+    for (int i = tid; i < total4; i += THREADS) cp_async16(s + p.s_par + 4 * i, a.params + 4 * i);
+    const int K0 = p.dims[0];
+    if (a.x_vec) {
+        const float* xr = a.x + static_cast<long long>(row0) * K0;
+#pragma unroll 1
+        for (int i = tid; i < (nrows * K0) >> 2; i += THREADS) cp_async16(s + p.s_act[0] + 4 * i, xr + 4 * i);
+    }
+    cp_async_commit();
+#pragma unroll 1
+    for (int i = lo4 + tid; i < hi4; i += THREADS) {
+        cp_async16(s + p.s_m + 4 * (i - lo4), a.m + 4 * i);
+        cp_async16(s + p.s_v + 4 * (i - lo4), a.v + 4 * i);
+    }
+    cp_async_commit();
     const float adv_t = a.adv[0], adv_ibc1 = a.adv[1], adv_ibc2 = a.adv[2];
     float tgt_first = 0.f;
     int label_first = 0;
@@ -259,75 +334,39 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     } else if (tid < nrows) {
         label_first = static_cast<const int*>(a.target)[row0 + tid];
     }
-
-    // ---- 1. load the parameters and the input rows ------------------------------------------
     // Only the gradient buffer has to start at zero (its padding floats between the layers are
     // summed like everything else).  The paddings of the operand tiles may hold anything: a
-    // product reads them only into outputs that are never emitted.
-    for (int i = tid; i < p.total; i += THREADS) s[p.s_grad + i] = 0.f;
-    // this thread's first input elements: requested before the parameters are unpacked
-    constexpr int X_FIRST = 2;
-    float x_first[X_FIRST];
-#pragma unroll
-    for (int u = 0; u < X_FIRST; u++) {
-        const int i = tid + u * THREADS;
-        x_first[u] = i < nrows * p.dims[0] ? a.x[static_cast<long long>(row0) * p.dims[0] + i] : 0.f;
+    // product reads them only into outputs that are never written.
+#pragma unroll 1
+    for (int i = tid; i < total4; i += THREADS) reinterpret_cast<float4*>(s + p.s_grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!a.x_vec) {
+        const int Kp = pad4(K0);
+#pragma unroll 1
+        for (int i = tid; i < nrows * K0; i += THREADS)
+            s[p.s_act[0] + (i / K0) * Kp + (i % K0)] = a.x[static_cast<long long>(row0) * K0 + i];
     }
-    // parameters: 128-bit loads over the flat buffer (all in flight at once) into the flat copy
-    // and into the row-major weight matrices
-    constexpr int PAR_BATCH = 8;          // float4 loads per thread issued before the first is used
-    for (int base4 = 0; base4 < (p.total >> 2); base4 += THREADS * PAR_BATCH) {
-        float4 qs[PAR_BATCH];
-#pragma unroll
-        for (int u = 0; u < PAR_BATCH; u++) {
-            const int i4 = base4 + u * THREADS + tid;
-            if (i4 < (p.total >> 2)) qs[u] = reinterpret_cast<const float4*>(a.params)[i4];
-        }
-#pragma unroll
-        for (int u = 0; u < PAR_BATCH; u++) {
-            const int i4 = base4 + u * THREADS + tid;
-            if (i4 >= (p.total >> 2)) continue;
-            const float4 q = qs[u];
-            reinterpret_cast<float4*>(s + p.s_par)[i4] = q;
-            const float e[4] = {q.x, q.y, q.z, q.w};
-            const int flat = 4 * i4;
-            for (int l = 0; l < L; l++) {
-                if (flat + 3 < p.w_off[l] || flat >= p.b_off[l]) continue;
-                const int K = p.dims[l], Kp = pad4(K);
-                if ((K & 3) == 0 && flat >= p.w_off[l] && flat + 3 < p.b_off[l]) {
-                    // the four floats are four consecutive k of one row
-                    const int rel = flat - p.w_off[l];
-                    const int n = static_cast<int>((static_cast<unsigned int>(rel) * static_cast<unsigned int>(p.k_magic[l])) >> 20);
-                    *reinterpret_cast<float4*>(s + p.s_w[l] + n * Kp + (rel - n * K)) = q;
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const int rel = flat + j - p.w_off[l];
-                        if (rel < 0 || flat + j >= p.b_off[l]) continue;
-                        const int n = static_cast<int>((static_cast<unsigned int>(rel) * static_cast<unsigned int>(p.k_magic[l])) >> 20);
-                        s[p.s_w[l] + n * Kp + (rel - n * K)] = e[j];
-                    }
-                }
-            }
-        }
-    }
-    {
-        const int K = p.dims[0], Kp = pad4(K);
-#pragma unroll
-        for (int u = 0; u < X_FIRST; u++) {
-            const int i = tid + u * THREADS;
-            if (i < nrows * K) s[p.s_act[0] + (i / K) * Kp + (i % K)] = x_first[u];
-        }
-        for (int i = tid + X_FIRST * THREADS; i < nrows * K; i += THREADS)
-            s[p.s_act[0] + (i / K) * Kp + (i % K)] = a.x[static_cast<long long>(row0) * K + i];
+    cp_async_wait_all_but_last();
+    __syncthreads();
+    // Row-major W with rows padded to whole float4s (only layers whose K is not a multiple of 4:
+    // the others are used in place in the flat copy), then W^T for the forward pass: thread <->
+    // (k, four rows n): four reads down a column of W (lanes on consecutive k), one 128-bit store
+    // into row k of W^T.
+#pragma unroll 1
+    for (int l = 0; l < L; l++) {
+        const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K);
+        if ((K & 3) == 0) continue;
+        const float* src = s + p.s_par + p.w_off[l];
+        float* w = s + p.s_w[l];
+#pragma unroll 1
+        for (int i = tid; i < N * K; i += THREADS) w[(i / K) * Kp + (i % K)] = src[i];
     }
     __syncthreads();
-    // W^T for the forward pass: thread <-> (k, four rows n): four reads down a column of W (lanes on
-    // consecutive k), one 128-bit store into row k of W^T
+#pragma unroll 1
     for (int l = 0; l < L; l++) {
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Npt = pad4(N) + 4, n4_n = (N + 3) >> 2;
         const float* w = s + p.s_w[l];
         float* wt = s + p.s_wt[l];
+#pragma unroll 1
         for (int i = tid; i < K * n4_n; i += THREADS) {
             const int n4 = i / K, k = i - n4 * K;
             float4 v;
@@ -340,28 +379,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
     __syncthreads();
 
-    // 2-row output blocks throughout: the 4-row form (half the shared-memory bytes per FMA) measured
-    // slower at every batch size here -- it leaves half the threads without a block, and these
-    // products are bound by latency, not by shared-memory bandwidth
-    const bool tall_rows = false;
-
-    // ---- 2a. forward ------------------------------------------------------------------------
+    // ---- 2a. forward: y[r][n] = act(sum_k x[r][k] * W^T[k][n] + b[n]) ---------------------------------
+#pragma unroll 1
     for (int l = 0; l < L; l++) {
-        const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Np = pad4(N);
-        const float* bias = s + p.s_par + p.b_off[l];
-        const int act = l + 1 < L ? p.act : TT_ACT_NONE;
-        float* y = s + p.s_act[l + 1];
-        // y[r][n] = sum_k x[r][k] * W^T[k][n]
-        const auto fwd_emit = [&](int r, int n0, const float* acc) {
-            float4 v;
-            v.x = act_fwd(acc[0] + bias[n0], act);
-            v.y = n0 + 1 < N ? act_fwd(acc[1] + bias[n0 + 1], act) : 0.f;
-            v.z = n0 + 2 < N ? act_fwd(acc[2] + bias[n0 + 2], act) : 0.f;
-            v.w = n0 + 3 < N ? act_fwd(acc[3] + bias[n0 + 3], act) : 0.f;
-            *reinterpret_cast<float4*>(y + r * Np + n0) = v;
-        };
-        if (tall_rows) gemm_rows<4>(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, fwd_emit);
-        else           gemm_rows<2>(s + p.s_act[l], Kp, s + p.s_wt[l], Np + 4, nrows, N, K, fwd_emit);
+        const int K = p.dims[l], N = p.dims[l + 1];
+        product_rows(s + p.s_act[l], pad4(K), s + p.s_wt[l], pad4(N) + 4, nrows, N, K, ROWS_FWD,
+                     l + 1 < L ? p.act : TT_ACT_NONE, s + p.s_par + p.b_off[l], 0, s + p.s_act[l + 1], pad4(N));
         __syncthreads();
     }
 
@@ -375,6 +398,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         // mean over batch x outputs of (o - t)^2; d/do = 2 (o - t) / count   (TensorOps.Losses.cs:29-61)
         const float* tgt = static_cast<const float*>(a.target);
         const float inv = 1.f / (static_cast<float>(a.batch) * static_cast<float>(NO));
+#pragma unroll 1
         for (int i = tid; i < nrows * NO; i += THREADS) {
             const int r = i / NO, n = i - r * NO;
             const float d = out[r * NOp + n] - (i == tid ? tgt_first : tgt[static_cast<long long>(row0) * NO + i]);
@@ -386,16 +410,20 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         // softmax cross-entropy, mean over the batch, int32 labels (TensorOps.Losses.cs:97-108)
         const int* labels = static_cast<const int*>(a.target);
         const float inv = 1.f / static_cast<float>(a.batch);
+#pragma unroll 1
         for (int r = tid; r < nrows; r += THREADS) {
             float mx = -INFINITY;
+#pragma unroll 1
             for (int n = 0; n < NO; n++) mx = fmaxf(mx, out[r * NOp + n]);
             float se = 0.f;
+#pragma unroll 1
             for (int n = 0; n < NO; n++) se += expf(out[r * NOp + n] - mx);
             const float lse = logf(se) + mx;
             const int label = r == tid ? label_first : labels[row0 + r];
             const bool ok = label >= 0 && label < NO;
             if (!ok && a.status) atomicCAS(a.status, 0u, 7u);
             loss_part += ok ? -(out[r * NOp + label] - lse) * inv : __int_as_float(0x7fc00000);
+#pragma unroll 1
             for (int n = 0; n < NO; n++)
                 g[r * gw + n] = (expf(out[r * NOp + n] - lse) - (n == label ? 1.f : 0.f)) * inv;
         }
@@ -406,81 +434,44 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
 
     // ---- 2c. backward -------------------------------------------------------------------------
     float* grad = s + p.s_grad;
+#pragma unroll 1
     for (int l = L - 1; l >= 0; l--) {
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K);
         // dW[n][k] = sum_r g[r][n] * x[r][k]
-        float* dw = grad + p.w_off[l];
-        const auto dw_emit = [&](int n, int k0, const float* acc) {
-            float* d = dw + n * K + k0;
-            if ((K & 3) == 0) {
-                *reinterpret_cast<float4*>(d) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            } else {
-                d[0] = acc[0];
-                if (k0 + 1 < K) d[1] = acc[1];
-                if (k0 + 2 < K) d[2] = acc[2];
-                if (k0 + 3 < K) d[3] = acc[3];
-            }
-        };
-        gemm_outer<2>(g, gw, s + p.s_act[l], Kp, N, K, nrows, dw_emit);
+        product_outer(g, gw, s + p.s_act[l], Kp, N, K, nrows, grad + p.w_off[l], K);
         // db[n] = sum_r g[r][n], ascending r
         float* db = grad + p.b_off[l];
+#pragma unroll 1
         for (int n = tid; n < N; n += THREADS) {
             float t = 0.f;
-#pragma unroll 8
+#pragma unroll 4
             for (int r = 0; r < nrows; r++) t += g[r * gw + n];
             db[n] = t;
         }
         if (l > 0) {
             // dx[r][k] = sum_n g[r][n] * W[n][k], then through the activation of layer l - 1
-            const float* h = s + p.s_act[l];
             float* gn = s + p.s_g[gcur ^ 1];
-            const int act = p.act;
-            const auto dx_emit = [&](int r, int k0, const float* acc) {
-                const float4 y = *reinterpret_cast<const float4*>(h + r * Kp + k0);
-                *reinterpret_cast<float4*>(gn + r * gw + k0) =
-                    make_float4(ew::act_grad(y.x, acc[0], act), ew::act_grad(y.y, acc[1], act),
-                                ew::act_grad(y.z, acc[2], act), ew::act_grad(y.w, acc[3], act));
-            };
-            if (tall_rows) gemm_rows<4>(g, gw, s + p.s_w[l], Kp, nrows, K, N, dx_emit);
-            else           gemm_rows<2>(g, gw, s + p.s_w[l], Kp, nrows, K, N, dx_emit);
+            product_rows(g, gw, s + p.s_w[l], Kp, nrows, K, N, ROWS_BWD, p.act, s + p.s_act[l], Kp, gn, gw);
             __syncthreads();
             gcur ^= 1;
             g = gn;
         }
     }
-    __syncthreads();
 
     // ---- 3. cluster-wide gradient sum (slice per CTA), gradient norm ---------------------------
-    const int total4 = p.total >> 2;
-    const int per4 = (total4 + C - 1) / C;
-    const int lo4 = min(total4, c * per4), hi4 = min(total4, lo4 + per4);
-    constexpr int MAX_OWN = 8;            // float4s per thread: per4 <= THREADS * MAX_OWN (checked on the host)
-    // this thread's Adam moments: requested now, used after the two cluster barriers
-    float4 own_m[MAX_OWN], own_v[MAX_OWN];
-#pragma unroll
-    for (int u = 0; u < MAX_OWN; u++) {
-        const int i = lo4 + tid + u * THREADS;
-        if (i < hi4) {
-            own_m[u] = reinterpret_cast<const float4*>(a.m)[i];
-            own_v[u] = reinterpret_cast<const float4*>(a.v)[i];
-        }
-    }
     cluster.sync();
     float sq = 0.f;
-    // every thread keeps its elements' summed gradients in registers across the second barrier
-    float4 own[MAX_OWN];
-#pragma unroll
-    for (int u = 0; u < MAX_OWN; u++) {
-        const int i = lo4 + tid + u * THREADS;
+    float* own = s + p.s_sum;             // the summed gradients of this CTA's slice
+#pragma unroll 1
+    for (int i = lo4 + tid; i < hi4; i += THREADS) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i < hi4) {
-            for (int r = 0; r < C; r++) {
-                const float4 q = reinterpret_cast<const float4*>(cluster.map_shared_rank(grad, r))[i];
-                sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
-            }
-            sq += sum.x * sum.x; sq += sum.y * sum.y; sq += sum.z * sum.z; sq += sum.w * sum.w;
+#pragma unroll 1
+        for (int r = 0; r < C; r++) {
+            const float4 q = reinterpret_cast<const float4*>(cluster.map_shared_rank(grad, r))[i];
+            sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
         }
-        own[u] = sum;
+        sq += sum.x * sum.x; sq += sum.y * sum.y; sq += sum.z * sum.z; sq += sum.w * sum.w;
+        reinterpret_cast<float4*>(own)[i - lo4] = sum;
     }
     const float sq_cta = block_sum(sq, red);
     // Every CTA hands its two partial sums (loss, sum of squares of its slice) to every CTA of the
@@ -494,6 +485,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
     cluster.sync();
     float total_sq = 0.f, loss_total = 0.f;
+#pragma unroll 1
     for (int r = 0; r < C; r++) {
         loss_total += red[32 + 2 * r];
         total_sq += red[33 + 2 * r];
@@ -509,19 +501,18 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     float t = adv_t, ibc1 = adv_ibc1, ibc2 = adv_ibc2;
     if (a.advance) {
         t += 1.f;
-        ibc1 = 1.f / (1.f - powf(a.b1, t));
-        ibc2 = 1.f / (1.f - powf(a.b2, t));
+        ibc1 = inv_bias_correction(a.b1, t);
+        ibc2 = inv_bias_correction(a.b2, t);
     }
     const float omb1 = 1.f - a.b1, omb2 = 1.f - a.b2;
-#pragma unroll
-    for (int u = 0; u < MAX_OWN; u++) {
-        const int i = lo4 + tid + u * THREADS;
-        if (i >= hi4) continue;
-        float4 gg = own[u];
+    cp_async_wait_all();                  // each thread consumes the moments it requested itself
+#pragma unroll 1
+    for (int i = lo4 + tid; i < hi4; i += THREADS) {
+        float4 gg = reinterpret_cast<const float4*>(own)[i - lo4];
         if (a.max_norm > 0.f) { gg.x *= coef; gg.y *= coef; gg.z *= coef; gg.w *= coef; }
         float4 pp = reinterpret_cast<const float4*>(s + p.s_par)[i];
-        float4 mm = own_m[u];
-        float4 vv = own_v[u];
+        float4 mm = reinterpret_cast<const float4*>(s + p.s_m)[i - lo4];
+        float4 vv = reinterpret_cast<const float4*>(s + p.s_v)[i - lo4];
         ew::adam_one(pp.x, gg.x, mm.x, vv.x, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
         ew::adam_one(pp.y, gg.y, mm.y, vv.y, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
         ew::adam_one(pp.z, gg.z, mm.z, vv.z, a.b1, omb1, a.b2, omb2, a.lr, a.eps, ibc1, ibc2, 0.f, 1.f);
@@ -538,6 +529,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         a.adv[2] = ibc2;
     }
 }
+
 
 // Largest cluster the device schedules for this kernel at its largest shared-memory size: 16
 // (needs the non-portable attribute) where possible, else the portable 8.
@@ -584,10 +576,11 @@ int launch(cudaStream_t st, const tt_mlp_desc* net, float* params, float* m, flo
     int C = g_max_cluster < 4 ? g_max_cluster : 4;
     while (C < g_max_cluster && batch > 8 * C) C *= 2;
     int rows = (batch + C - 1) / C;
-    Plan plan = make_plan(*net, rows);
+    Plan plan = make_plan(*net, rows, C);
     if (static_cast<size_t>(plan.floats) * sizeof(float) > MAX_SMEM_BYTES) return TT_ERR_UNSUPPORTED;
-    const int per4 = ((plan.total >> 2) + C - 1) / C;
-    if (per4 > THREADS * 8) return TT_ERR_UNSUPPORTED;
+    // the flat buffers are moved 128 bits at a time
+    const auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!aligned16(params) || !aligned16(m) || !aligned16(v) || !aligned16(grads_out)) return TT_ERR_UNSUPPORTED;
     Args a;
     a.plan = plan;
     a.params = params; a.m = m; a.v = v; a.adv = adv; a.grads_out = grads_out;
@@ -595,6 +588,7 @@ int launch(cudaStream_t st, const tt_mlp_desc* net, float* params, float* m, flo
     a.batch = batch;
     a.lr = lr; a.b1 = b1; a.b2 = b2; a.eps = eps; a.max_norm = max_norm; a.clip_eps = clip_eps;
     a.advance = advance;
+    a.x_vec = (net->dims[0] % 4 == 0) && aligned16(x);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(C, 1, 1);

@@ -105,10 +105,17 @@ class PeerGroup:
         self.n = n_floats
         self._sizes = {"stage": 4 * self.world * n_floats, "params": 4 * n_floats, "flags": 4 * FLAG_WORDS}
         self._own, self._opened, self._g = {}, [], None
-        for name, nbytes in self._sizes.items():
-            p = ctypes.c_void_p()
-            rt._ck(L.tt_peer_alloc(h, nbytes, ctypes.byref(p)))
-            self._own[name] = p.value
+        try:
+            for name, nbytes in self._sizes.items():
+                p = ctypes.c_void_p()
+                rt._ck(L.tt_peer_alloc(h, nbytes, ctypes.byref(p)))
+                self._own[name] = p.value
+        except Exception:
+            # a failed allocation must not leave the earlier buffers of this group behind
+            for p in self._own.values():
+                L.tt_peer_free(h, ctypes.c_void_p(p))
+            self._own = {}
+            raise
         if _emulated is not None:
             return                      # emulate() connects the ranks
         maps = {name: [None] * self.world for name in self._sizes}

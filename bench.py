@@ -644,7 +644,12 @@ def main():
     ap.add_argument("--one-bmm", nargs="+", metavar="ARG", help="MODE ITERS [transposed_b]: time benchmark config 3 and exit")
     ap.add_argument("--one-mlp", nargs="+", metavar="ARG", help="ROWS MODE EXCHANGE STEPS: time the benchmark MLP step on ROWS rows and exit")
     ap.add_argument("--one-step", nargs="+", metavar="ARG", help="DIMS BATCH STEPS: time the one-launch small-MLP training step and exit")
+    ap.add_argument("--one-small", action="store_true", help="time the latency-bound small configurations (graph replay) and exit")
     args = ap.parse_args()
+    if args.one_small:
+        from tensotron_b200.runtime import TensorRuntime
+        print(json.dumps(small_configs(TensorRuntime(0, 256 << 20)), indent=1))
+        return
     if args.one:
         return run_one(args.one)
     if args.one_bmm:

@@ -136,7 +136,8 @@ TT_API int tt_linear_fwd(tt_handle_t h, void* stream, const float* x, const floa
  *   dbias[n] = sum_m g[m,n]  in a fixed order (no atomics) -- skipped when NULL
  * Outputs are written, not accumulated (accumulation stays with Tensor.AddGrad).
  * When act != TT_ACT_NONE the masked gradient g needs M*N floats of the handle
- * workspace. */
+ * workspace.  Layers up to M*N*K = 2^21 run as ONE launch (g formed on the fly, no
+ * workspace); larger ones as three (activation backward + column sums, dx, dw). */
 TT_API int tt_linear_bwd(tt_handle_t h, void* stream, const float* x, const float* w, const float* y,
                   const float* dy, float* dx, float* dw, float* dbias, int M, int N, int K, int act);
 

@@ -14,6 +14,7 @@
 #include "elementwise.cuh"
 #include "gemm_common.h"
 #include "gemm_generic.cuh"
+#include "linear_small.cuh"
 #include "mlp_step.h"
 #include "peer.cuh"
 #include "sgemm_simt.cuh"
@@ -45,6 +46,7 @@ constexpr size_t DEFAULT_WORKSPACE = 256ull << 20;
 // stream-K flag per CTA (zero between launches).
 constexpr int STREAMK_FLAGS_WORD = 64, HANDLE_WORDS = 1024;
 constexpr long long TMA_MIN_FLOP_ELEMS = 1ll << 21;  // M*N*K below this -> any-stride kernel
+constexpr long long LINEAR_SMALL_MAX_ELEMS = 1ll << 21;  // M x N x K up to which a Linear backward is ONE launch (linear_small.cuh)
 constexpr long long SMALL_MAX_FLOP_ELEMS = 1ll << 27;  // ... and up to this when the output is a few tiles only
 
 int fail(tt_handle_t h, int code, const char* fmt, const char* detail = "")
@@ -365,15 +367,17 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
         // is half the traffic of a 256x128 one).
         const bool sub_wave = tm == 8 && sh.nj == 2 && tiles < h->num_sms;
         if (red_count == 1 && k_tiles >= 8 && tiles >= h->num_sms / (sub_wave ? 4 : 2)) {
-            const size_t need = static_cast<size_t>(h->num_sms) * bm * bn * sizeof(float);
+            const size_t need = 2 * static_cast<size_t>(h->num_sms) * bm * bn * sizeof(float);   // two partial-tile slots per CTA
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
             if (need <= ws_avail && fill < 0.97) {
-                // measured cost of storing and re-reading the partial tiles, in units of a 128x128
-                // k-tile: about 11 (20 us) whatever the shape, and a fully busy chip clocks a
-                // little lower than one with idle SMs (5 %); below one wave of 128x128 tiles 2.5
-                // plus 1.5 per CTA that shares a tile (1024^3: 50 us against 54 with two split-K
-                // ranges, 1024 x 1024 x 4096: 155 against 175, 768^3: 31 against 27)
+                // measured: storing and re-reading the partial tiles costs about 20 us (11 units of a
+                // 128x128 k-tile) whatever the shape, and the stream-K form of the kernel runs its
+                // main loop about 4 % slower than the whole-tile form (16384^3: 145.1 ms against
+                // 141.1 ms although it saves 0.65 of a wave; 4096^3, 3.46 waves: 2.30 against 2.55 ms).
+                // Below one wave of 128x128 tiles: 2.5 units plus 1.5 per CTA that shares a tile
+                // (1024^3: 50 us against 54 with two split-K ranges, 1024 x 1024 x 4096: 155 against
+                // 175, 768^3: 31 against 27).
                 const double body = (static_cast<double>(tiles) / h->num_sms) * (k_tiles + 2.0) * tile_cost;
                 const double t = sub_wave ? body + 2.5 + 1.5 * h->num_sms / static_cast<double>(tiles)
                                           : (body + 11.0) * 1.05;
@@ -419,14 +423,24 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     const long long tiles = static_cast<long long>(g.batch_count) * p.shape.tiles_m * p.shape.tiles_n;
     const int k_tiles = (g.K + simt::BK - 1) / simt::BK;
     const int mode = plan.streamk ? simt::MODE_STREAMK : plan.splits > 1 ? simt::MODE_SPLITK : simt::MODE_TILES;
-    // work = what the CTAs share out: tiles x k-tiles units (stream-K) or tiles x splits items
-    p.shape.work = plan.streamk ? tiles * k_tiles : tiles * plan.splits;
+    // work = what the CTAs share out: tiles x splits items, or for stream-K the k-tile units of the
+    // tiles behind the whole waves.  The whole waves stop one wave early when the remainder is
+    // less than half a wave, so the unit part holds between half a tile and a tile and a half per
+    // CTA (an output tile is then shared by three CTAs at most).
+    p.sk_first = 0;
+    if (plan.streamk && tiles >= h->num_sms) {
+        long long whole = tiles / h->num_sms;
+        if (tiles - whole * h->num_sms < h->num_sms / 2) whole -= 1;
+        p.sk_first = whole * h->num_sms;
+    }
+    p.shape.work = plan.streamk ? (tiles - p.sk_first) * k_tiles : tiles * plan.splits;
+    if (plan.streamk && p.shape.work >= (1ll << 31)) return TT_ERR_UNSUPPORTED;   // the kernel's unit cursor is 32 bits
     p.epi = g.epi;
     p.c = g.c;
     p.status = h->status;
     p.sk_flags = h->status + STREAMK_FLAGS_WORD;
     p.c_vec_ok = aligned16(g.c) && (g.N % 4 == 0);
-    const int grid = static_cast<int>(p.shape.work < h->num_sms ? p.shape.work : h->num_sms);
+    const int grid = static_cast<int>(p.shape.work < h->num_sms && p.sk_first == 0 ? p.shape.work : h->num_sms);
     if (plan.splits > 1 || plan.streamk) h->stats.splitk++;
     int rc;
     if constexpr (NJ == 3) {
@@ -532,12 +546,12 @@ int try_launch_simt(tt_handle_t h, cudaStream_t st, const GemmCall& g_in)
     if (h->variant == 6 || g.epi.scatter_rows > 0) {
         // pinned: 256x128 tiles with stream-K (measurements; the scatter epilogue lives in this form)
         plan.tm = 16; plan.nj = 2; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
-        if (static_cast<size_t>(h->num_sms) * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
+        if (2 * static_cast<size_t>(h->num_sms) * 256 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
     if (h->variant == 9) {
         // pinned: 128x128 tiles with stream-K (measurements)
         plan.tm = 8; plan.nj = 2; plan.splits = 1; plan.kps = (g.K + simt::BK - 1) / simt::BK; plan.streamk = true;
-        if (static_cast<size_t>(h->num_sms) * 128 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
+        if (2 * static_cast<size_t>(h->num_sms) * 128 * simt::BN * sizeof(float) > ws_avail) return TT_ERR_UNSUPPORTED;
     }
     if (plan.nj == 3) return try_launch_simt_tm<8, 3>(h, st, g, plan);
     return plan.tm == 16 ? try_launch_simt_tm<16>(h, st, g, plan) : try_launch_simt_tm<8>(h, st, g, plan);
@@ -799,6 +813,22 @@ int linear_bwd_impl(tt_handle_t h, cudaStream_t st, const float* x, const float*
     TT_BIND(h);
     int rc = TT_OK;
     h->stats.calls++;
+
+    // Small layers (the latency-bound shapes of small networks): everything in one launch.
+    if (h->variant == 0 && !(scatter && scatter->scatter_rows > 0) && M > 0 && N > 0 && K > 0 &&
+        static_cast<long long>(M) * N * K <= LINEAR_SMALL_MAX_ELEMS) {
+        lin_small::Params lp;
+        lp.x = x; lp.w = w; lp.y = y; lp.dy = dy; lp.dx = dx; lp.dw = dw; lp.db = dbias;
+        lp.M = M; lp.N = N; lp.K = K; lp.act = act;
+        lp.tiles_k = (K + lin_small::T - 1) / lin_small::T;
+        lp.tiles_dx = dx ? ((M + lin_small::T - 1) / lin_small::T) * lp.tiles_k : 0;
+        const int tiles_dw = ((N + lin_small::T - 1) / lin_small::T) * lp.tiles_k;
+        lin_small::linear_bwd_small_kernel<<<lp.tiles_dx + tiles_dw, lin_small::THREADS, 0, st>>>(lp);
+        h->stats.launches++;
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(h, e, "small linear backward launch");
+        return TT_OK;
+    }
 
     const float* g = dy;
     size_t ws_used = 0;  // the masked gradient and the column-sum partials stay live during the GEMMs

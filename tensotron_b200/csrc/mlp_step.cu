@@ -144,15 +144,24 @@ struct Args {
 };
 
 // The functions below are deliberately NOT inlined: each exists once in the kernel's code.
-__device__ __noinline__ float act_fwd(float v, int act)
+__device__ __forceinline__ float act_one(float v, int act)
 {
     if (act == TT_ACT_RELU) return v > 0.f ? v : 0.f;
     if (act == TT_ACT_TANH) return tanhf(v);
     return v;
 }
+// four values per call, so the four tanh chains overlap
+__device__ __noinline__ float4 act_fwd4(float4 v, int act)
+{
+    return make_float4(act_one(v.x, act), act_one(v.y, act), act_one(v.z, act), act_one(v.w, act));
+}
 
-// 1 / (1 - b^t), Adam's bias correction (the arithmetic of tt_adam_advance)
-__device__ __noinline__ float inv_bias_correction(float b, float t) { return 1.f / (1.f - powf(b, t)); }
+// 1 / (1 - b^t) for both moments, Adam's bias corrections (the arithmetic of tt_adam_advance); one
+// call, so the two powf chains overlap
+__device__ __noinline__ float2 inv_bias_corrections(float b1, float b2, float t)
+{
+    return make_float2(1.f / (1.f - powf(b1, t)), 1.f / (1.f - powf(b2, t)));
+}
 
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src)
 {
@@ -174,31 +183,42 @@ __device__ __forceinline__ void fma_row4(float (&acc)[4], float a, const float4 
 }
 
 // Outer form: out[i * ldo + j] = sum_l P[l * ldp + i] * Q[l * ldq + j] for i < I, j < J (l ascending,
-// one accumulator per output, fused multiply-add).  A thread owns 2 x 4 output blocks.  ldp >= I
-// rounded up to 2, ldq >= J rounded up to 4; what lies in those roundings may be anything, it only
-// reaches outputs that are not written.  Used for dW (P = g, Q = x, out = the flat gradient).
+// one accumulator per output, fused multiply-add).  A thread owns IB x 4 output blocks (IB = 4 halves
+// the shared-memory bytes per FMA and is used when it still gives every second thread a block).
+// ldp >= I rounded up to IB, ldq >= J rounded up to 4; what lies in those roundings may be
+// anything, it only reaches outputs that are not written.  Used for dW (P = g, Q = x, out = the
+// flat gradient).
+template <int IB>
 __device__ __noinline__ void product_outer(const float* __restrict__ P, int ldp, const float* __restrict__ Q, int ldq,
                                            int I, int J, int L, float* __restrict__ out, int ldo)
 {
-    const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
+    const int ib_n = (I + IB - 1) / IB, jb_n = (J + 3) >> 2;
     const bool vec = (ldo & 3) == 0;
     for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
         const int jb = blk % jb_n, ib = blk / jb_n;
-        const float* pp = P + 2 * ib;
+        const float* pp = P + IB * ib;
         const float* qq = Q + 4 * jb;
-        float acc[2][4];
+        float acc[IB][4];
 #pragma unroll
-        for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+        for (int r = 0; r < IB; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 #pragma unroll 4
         for (int l = 0; l < L; l++) {
             const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
-            const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
-            fma_row4(acc[0], a.x, b);
-            fma_row4(acc[1], a.y, b);
+            if constexpr (IB == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(pp + l * ldp);
+                fma_row4(acc[0], a.x, b);
+                fma_row4(acc[1], a.y, b);
+                fma_row4(acc[2], a.z, b);
+                fma_row4(acc[3], a.w, b);
+            } else {
+                const float2 a = *reinterpret_cast<const float2*>(pp + l * ldp);
+                fma_row4(acc[0], a.x, b);
+                fma_row4(acc[1], a.y, b);
+            }
         }
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const int i = 2 * ib + r, j0 = 4 * jb;
+        for (int r = 0; r < IB; r++) {
+            const int i = IB * ib + r, j0 = 4 * jb;
             if (i >= I) continue;
             float* d = out + i * ldo + j0;
             if (vec) {
@@ -226,15 +246,27 @@ __device__ __noinline__ void product_rows(const float* __restrict__ P, int ldp, 
 {
     const int ib_n = (I + 1) >> 1, jb_n = (J + 3) >> 2;
     const int L4 = L & ~3;
-    for (int blk = threadIdx.x; blk < ib_n * jb_n; blk += THREADS) {
-        const int jb = blk % jb_n, ib = blk / jb_n;
+    // Few output blocks (a handful of batch rows): the contraction is cut over the four 8-lane
+    // groups of a warp, so a thread's chain of dependent FMAs is a quarter as long; the four partial
+    // sums are added by a fixed xor-shuffle tree ((q0 + q1) + (q2 + q3), the same bits in all lanes).
+    const bool cut = ib_n * jb_n * 4 <= THREADS && L4 >= 16;
+    const int lane = threadIdx.x & 31;
+    const int kq = cut ? lane >> 3 : 0;
+    const int first = cut ? (threadIdx.x >> 5) * 8 + (lane & 7) : threadIdx.x;
+    const int groups = L4 >> 2, gpq = cut ? (groups + 3) >> 2 : groups;
+    const int l_lo = 4 * min(groups, kq * gpq), l_hi = 4 * min(groups, (kq + 1) * gpq);
+    const int nblk = ib_n * jb_n;
+    const int blk_end = cut ? ((nblk + 7) & ~7) : nblk;      // whole 8-lane groups enter the shuffles together
+    for (int blk = first; blk < blk_end; blk += THREADS) {
+        const bool live = blk < nblk;
+        const int jb = live ? blk % jb_n : 0, ib = live ? blk / jb_n : 0;
         const float* p0 = P + (2 * ib) * ldp;
         const float* qq = Q + 4 * jb;
         float acc[2][4];
 #pragma unroll
         for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 #pragma unroll 2
-        for (int l = 0; l < L4; l += 4) {
+        for (int l = l_lo; l < l_hi; l += 4) {
             float4 a[2];
 #pragma unroll
             for (int r = 0; r < 2; r++) a[r] = *reinterpret_cast<const float4*>(p0 + r * ldp + l);
@@ -250,22 +282,38 @@ __device__ __noinline__ void product_rows(const float* __restrict__ P, int ldp, 
                 fma_row4(acc[r], a[r].w, b3);
             }
         }
+        if (!cut || kq == 3) {
 #pragma unroll 1
-        for (int l = L4; l < L; l++) {
-            const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
+            for (int l = L4; l < L; l++) {
+                const float4 b = *reinterpret_cast<const float4*>(qq + l * ldq);
 #pragma unroll
-            for (int r = 0; r < 2; r++) fma_row4(acc[r], p0[r * ldp + l], b);
+                for (int r = 0; r < 2; r++) fma_row4(acc[r], p0[r * ldp + l], b);
+            }
         }
+        if (cut) {
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 8);
+                    acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 16);
+                }
+            if (kq != 0) continue;
+        }
+        if (!live) continue;
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             const int i = 2 * ib + r, j0 = 4 * jb;
             if (i >= I) continue;
             float4 v;
             if (mode == ROWS_FWD) {
-                v.x = act_fwd(acc[r][0] + aux[j0], act);
-                v.y = j0 + 1 < J ? act_fwd(acc[r][1] + aux[j0 + 1], act) : 0.f;
-                v.z = j0 + 2 < J ? act_fwd(acc[r][2] + aux[j0 + 2], act) : 0.f;
-                v.w = j0 + 3 < J ? act_fwd(acc[r][3] + aux[j0 + 3], act) : 0.f;
+                // (reading up to 3 floats past the bias vector stays inside the shared-memory block;
+                // those lanes are zeroed below)
+                v = make_float4(acc[r][0] + aux[j0], acc[r][1] + aux[j0 + 1], acc[r][2] + aux[j0 + 2], acc[r][3] + aux[j0 + 3]);
+                if (act != TT_ACT_NONE) v = act_fwd4(v, act);
+                if (j0 + 1 >= J) v.y = 0.f;
+                if (j0 + 2 >= J) v.z = 0.f;
+                if (j0 + 3 >= J) v.w = 0.f;
             } else {
                 const float4 y = *reinterpret_cast<const float4*>(aux + i * lda + j0);
                 v = make_float4(ew::act_grad(y.x, acc[r][0], act), ew::act_grad(y.y, acc[r][1], act),
@@ -299,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     const int C = static_cast<int>(cluster.num_blocks());
     const int c = static_cast<int>(cluster.block_rank());
     const int tid = threadIdx.x;
-    const int L = p.n_layers, rp = p.rp;
+    const int L = p.n_layers;
     const int row0 = c * p.rows;                                  // first batch row of this CTA
     const int nrows = max(0, min(p.rows, a.batch - row0));        // rows that exist
     const int NO = p.dims[L], NOp = pad4(NO);
@@ -366,7 +414,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K), Npt = pad4(N) + 4, n4_n = (N + 3) >> 2;
         const float* w = s + p.s_w[l];
         float* wt = s + p.s_wt[l];
-#pragma unroll 1
+#pragma unroll 2
         for (int i = tid; i < K * n4_n; i += THREADS) {
             const int n4 = i / K, k = i - n4 * K;
             float4 v;
@@ -438,7 +486,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     for (int l = L - 1; l >= 0; l--) {
         const int K = p.dims[l], N = p.dims[l + 1], Kp = pad4(K);
         // dW[n][k] = sum_r g[r][n] * x[r][k]
-        product_outer(g, gw, s + p.s_act[l], Kp, N, K, nrows, grad + p.w_off[l], K);
+        if (((N + 3) >> 2) * ((K + 3) >> 2) * 2 >= THREADS) product_outer<4>(g, gw, s + p.s_act[l], Kp, N, K, nrows, grad + p.w_off[l], K);
+        else                                                product_outer<2>(g, gw, s + p.s_act[l], Kp, N, K, nrows, grad + p.w_off[l], K);
         // db[n] = sum_r g[r][n], ascending r
         float* db = grad + p.b_off[l];
 #pragma unroll 1
@@ -459,14 +508,24 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
 
     // ---- 3. cluster-wide gradient sum (slice per CTA), gradient norm ---------------------------
-    cluster.sync();
+    // The optimizer's bias corrections (two powf) are register work that depends on nothing of this
+    // step: they fill the time between arriving at the first cluster barrier and its completion.
+    cluster.barrier_arrive();
+    float t = adv_t, ibc1 = adv_ibc1, ibc2 = adv_ibc2;
+    if (a.advance) {
+        t += 1.f;
+        const float2 ibc = inv_bias_corrections(a.b1, a.b2, t);
+        ibc1 = ibc.x;
+        ibc2 = ibc.y;
+    }
+    cluster.barrier_wait();
     float sq = 0.f;
     float* own = s + p.s_sum;             // the summed gradients of this CTA's slice
 #pragma unroll 1
     for (int i = lo4 + tid; i < hi4; i += THREADS) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-        for (int r = 0; r < C; r++) {
+#pragma unroll 4
+        for (int r = 0; r < C; r++) {        // (unrolled: four remote loads in flight, still added in rank order)
             const float4 q = reinterpret_cast<const float4*>(cluster.map_shared_rank(grad, r))[i];
             sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
         }
@@ -485,7 +544,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     }
     cluster.sync();
     float total_sq = 0.f, loss_total = 0.f;
-#pragma unroll 1
+#pragma unroll 4
     for (int r = 0; r < C; r++) {
         loss_total += red[32 + 2 * r];
         total_sq += red[33 + 2 * r];
@@ -498,12 +557,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlp_train_step_kernel(const Args a
     if (c == 0 && tid == 0 && a.loss_out) *a.loss_out = loss_total;
 
     // ---- 4. Adam on this CTA's slice ------------------------------------------------------------
-    float t = adv_t, ibc1 = adv_ibc1, ibc2 = adv_ibc2;
-    if (a.advance) {
-        t += 1.f;
-        ibc1 = inv_bias_correction(a.b1, t);
-        ibc2 = inv_bias_correction(a.b2, t);
-    }
     const float omb1 = 1.f - a.b1, omb2 = 1.f - a.b2;
     cp_async_wait_all();                  // each thread consumes the moments it requested itself
 #pragma unroll 1

@@ -106,6 +106,21 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+// On the way out after a wait gave up: waits for `parity` on `bar` for at most DRAIN_LIMIT_NS,
+// whatever the abort flag says.  A thread uses it for the asynchronous copies or MMAs it issued
+// itself, so that the CTA does not release its shared memory or TMEM under them.
+constexpr unsigned long long DRAIN_LIMIT_NS = 200000000ull;
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xFFu) == 0 && global_timer_ns() - t0 > DRAIN_LIMIT_NS) return false;
+    }
+    return true;
+}
+
 // 5-D tiled TMA load, global -> this CTA's shared memory, completion on `bar`.
 __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2, int c3, int c4)

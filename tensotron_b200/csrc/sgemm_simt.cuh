@@ -101,6 +101,10 @@ struct Params {
     // stream-K: one "partial tile stored" flag per CTA (zero outside a launch; set by the CTA
     // whose range starts inside a tile, cleared by the CTA that adds that partial tile)
     unsigned int* sk_flags;
+    // stream-K: the first `sk_first` tiles (whole waves of the grid) are computed as whole tiles,
+    // round-robin like MODE_TILES; only the tiles behind them are dealt out as k-tile units
+    // (shape.work counts those units)
+    long long sk_first;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act)
@@ -179,7 +183,9 @@ __device__ __forceinline__ void transpose_tile(const uint8_t* raw, uint8_t* dst,
 // the main loop 14 % through register allocation; the three modes share one store loop):
 //   MODE_TILES   whole output tiles, round-robin over the CTAs;
 //   MODE_SPLITK  every tile cut into `splits` equal k ranges (small M x N);
-//   MODE_STREAMK the tiles x k-tiles units are dealt to the CTAs as equal contiguous ranges,
+//   MODE_STREAMK whole waves of tiles first (round-robin, so the CTAs in flight share A and B
+//                panels in L2 exactly as in MODE_TILES); the tiles x k-tiles units of the rest
+//                are dealt to the CTAs as equal contiguous ranges,
 //                so no SM idles in a partial last wave.  A CTA whose range starts inside a tile
 //                computes that segment first, stores it as a partial tile and raises its flag;
 //                the CTA that holds the head of the tile (k from 0, the last segment of its
@@ -215,8 +221,13 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const int tiles_per_mat = p.shape.tiles_m * p.shape.tiles_n;
     // This CTA's work: items blockIdx.x, +gridDim.x, ... (< work), or for MODE_STREAMK the
     // contiguous unit range [w_begin, w_end) of the work = tiles x k-tiles units.
-    const long long w_begin = MODE == 2 ? (p.shape.work * blockIdx.x) / gridDim.x : blockIdx.x;
-    const long long w_end = MODE == 2 ? (p.shape.work * (blockIdx.x + 1)) / gridDim.x : p.shape.work;
+    // (both the producer and the consumers walk it with the cursor pair below: `ca` over the
+    // round-robin items, then `cw` over the unit range)
+    const long long a_end = MODE == 2 ? p.sk_first : p.shape.work;
+    // (the unit part is at most a tile and a half per CTA: its unit count fits 32 bits, the host
+    // checks)
+    const int w_begin = MODE == 2 ? static_cast<int>((p.shape.work * blockIdx.x) / gridDim.x) : 0;
+    const int w_end = MODE == 2 ? static_cast<int>((p.shape.work * (blockIdx.x + 1)) / gridDim.x) : 0;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -238,21 +249,27 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
         uint32_t ps = 0, use = 0;   // stage to fill next; how many times the ring has wrapped
+        bool ok = true;
         const int sra = p.batch.red_a_slot, srb = p.batch.red_b_slot;
-        for (long long w = w_begin; w < w_end;) {
-            long long unit, w_next;
+        long long ca = blockIdx.x;
+        int cw = w_begin;
+        while (ok) {
+            long long unit;
             int kb, ke;
-            if (MODE == 2) {
-                unit = w / k_tiles;
-                kb = static_cast<int>(w - unit * k_tiles);
-                ke = static_cast<int>(min(static_cast<long long>(k_tiles), kb + (w_end - w)));
-                w_next = w + (ke - kb);
-            } else {
-                unit = w / p.splits;
-                const int split = static_cast<int>(w - unit * p.splits);
+            if (ca < a_end) {
+                unit = ca / p.splits;
+                const int split = static_cast<int>(ca - unit * p.splits);
                 kb = split * p.kps;
                 ke = min(k_tiles, kb + p.kps);
-                w_next = w + gridDim.x;
+                ca += gridDim.x;
+            } else if (MODE == 2 && cw < w_end) {
+                const int tu = cw / k_tiles;
+                unit = p.sk_first + tu;
+                kb = cw - tu * k_tiles;
+                ke = min(k_tiles, kb + (w_end - cw));
+                cw += ke - kb;
+            } else {
+                break;
             }
             const int bidx = static_cast<int>(unit / tiles_per_mat);
             const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
@@ -260,7 +277,7 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
             raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
             const int m0 = tm * C::BM, n0 = tn * BN;
             const BatchCoords bc = batch_coords(p.batch, bidx);
-            for (int r = 0; r < p.batch.red_count; r++) {
+            for (int r = 0; ok && r < p.batch.red_count; r++) {
                 // the reduced batch axis has a coordinate slot of its own (or none when the
                 // operand is broadcast along it)
                 const int ca0 = bc.a[0] + (sra == 0 ? r : 0), ca1 = bc.a[1] + (sra == 1 ? r : 0),
@@ -270,8 +287,10 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 for (int kt = kb; kt < ke; kt++) {
                     if (use > 0) {
                         // the stage was used before: wait until all warps released that use
-                        if (!mbar_wait_bounded(&empty_bar[ps], (use - 1) & 1u, cta_abort, p.status, DEV_WAIT_EMPTY))
-                            return;
+                        if (!mbar_wait_bounded(&empty_bar[ps], (use - 1) & 1u, cta_abort, p.status, DEV_WAIT_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
                     }
                     uint8_t* sa = smem + ps * C::STAGE_BYTES;
                     uint8_t* sb = sa + C::RAW_A;
@@ -284,7 +303,20 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                     if (++ps == STAGES) { ps = 0; use++; }
                 }
             }
-            w = w_next;
+        }
+        if (!ok) {
+            // A wait gave up: before this thread leaves (and the CTA's shared memory can go), wait,
+            // again with a limit, for the loads it issued itself -- the last arming of every stage.
+            uint32_t s = ps, u = use;
+            for (int i = 0; i < STAGES; i++) {
+                if (s == 0) {
+                    if (u == 0) break;      // fewer than STAGES loads were ever issued
+                    s = STAGES;
+                    u--;
+                }
+                s--;
+                mbar_wait_drain(&full_bar[s], u & 1u);
+            }
         }
         return;
     }
@@ -323,27 +355,33 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const int off_am = (wm * WROWS + ty * 4) * 4;
     const int off_bm = (wn * (32 * NJ) + tx * 4) * 4;
 
-    for (long long w = w_begin; w < w_end;) {
+    long long ca = blockIdx.x;
+    int cw = w_begin;
+    for (;;) {
         long long unit;
+        long long w = 0;      // MODE_SPLITK: this item's index (its workspace slot)
         int kb, ke;
-        long long w_next;
-        if (MODE == 2) {
-            unit = w / k_tiles;
-            kb = static_cast<int>(w - unit * k_tiles);
-            ke = static_cast<int>(min(static_cast<long long>(k_tiles), kb + (w_end - w)));
-            w_next = w + (ke - kb);
-        } else {
-            unit = w / p.splits;
-            const int split = static_cast<int>(w - unit * p.splits);
+        if (ca < a_end) {
+            w = ca;
+            unit = ca / p.splits;
+            const int split = static_cast<int>(ca - unit * p.splits);
             kb = split * p.kps;
             ke = min(k_tiles, kb + p.kps);
-            w_next = w + gridDim.x;
+            ca += gridDim.x;
+        } else if (MODE == 2 && cw < w_end) {
+            const int tu = cw / k_tiles;
+            unit = p.sk_first + tu;
+            kb = cw - tu * k_tiles;
+            ke = min(k_tiles, kb + (w_end - cw));
+            cw += ke - kb;
+        } else {
+            break;
         }
         const int bidx = static_cast<int>(unit / tiles_per_mat);
         const int t = static_cast<int>(unit - static_cast<long long>(bidx) * tiles_per_mat);
         int tm, tn;
         raster_tile(t, p.shape.tiles_m, p.shape.tiles_n, RASTER_GROUP, tm, tn);
-        const bool last_tile = w_next >= w_end;
+        const bool last_tile = ca >= a_end && cw >= w_end;
 
         // Accumulators are packed float2 for the two-wide FP32 FMA.  For a row pair
         // (i, i+1) and a column pair (j, j+1):
@@ -490,71 +528,26 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
         } else {
             // One store loop for all modes.  A finished tile goes to C (bounds, bias, activation);
             // a partial one (split-K range, or a stream-K range that covers only part of the
-            // tile's k) goes densely ([BM][BN]) to its workspace slot for the reduction kernel.
-            bool partial_tile = false;
+            // tile's k) goes densely ([BM][BN]) to a workspace slot.
+            bool partial_tile = false, head_tile = false;
             long long slot = 0;
             if (MODE == 1) {
                 partial_tile = p.splits > 1;
                 slot = w;
             } else if (MODE == 2) {
-                partial_tile = kb != 0;      // the range starts inside the tile: hand the segment over
-                slot = blockIdx.x;
-                if (kb == 0 && ke != k_tiles) {
-                    // Head of a tile that the following CTAs finish: add their partial tiles
-                    // (ascending CTA = ascending k) to the accumulators, then store the tile.
-                    volatile int& s_hi = *reinterpret_cast<volatile int*>(smem + C::OFF_BAR + 256);
-                    if (tid == 0) {
-                        const long long u_hi = (unit + 1) * k_tiles;
-                        int hi = blockIdx.x;
-                        while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
-                        s_hi = hi;
-                    }
-                    consumer_sync();
-                    const int hi = s_hi;
-                    for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
-                        if (tid == 0) {
-                            const unsigned long long t0 = global_timer_ns();
-                            unsigned int spins = 0, v;
-                            for (;;) {
-                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sk_flags + cta) : "memory");
-                                if (v != 0u) break;
-                                if ((++spins & 63u) == 0 && global_timer_ns() - t0 > WAIT_LIMIT_NS) {
-                                    *cta_abort = 1u;
-                                    if (p.status) atomicCAS(p.status, 0u, static_cast<unsigned int>(DEV_WAIT_STREAMK));
-                                    break;
-                                }
-                            }
-                            p.sk_flags[cta] = 0u;   // consumed: the next launch starts from zero again
-                        }
-                        consumer_sync();
-                        if (*cta_abort) return;
-                        const float* src = p.partial + static_cast<long long>(cta) * (C::BM * BN);
-    #pragma unroll
-                        for (int h = 0; h < HALVES; h++)
-    #pragma unroll
-                            for (int ib = 0; ib < 2; ib++)
-    #pragma unroll
-                                for (int i = 0; i < 4; i++) {
-                                    const int lr = wm * WROWS + h * 32 + ib * 16 + ty * 4 + i;
-                                    const int ai = h * 8 + ib * 4 + i;
-    #pragma unroll
-                                    for (int jb = 0; jb < NJ; jb++) {
-                                        const int lc = wn * (32 * NJ) + jb * 32 + tx * 4;
-                                        const float4 q = __ldcg(reinterpret_cast<const float4*>(src + lr * BN + lc));
-                                        acc_ref(ai, jb * 4 + 0) += q.x;
-                                        acc_ref(ai, jb * 4 + 1) += q.y;
-                                        acc_ref(ai, jb * 4 + 2) += q.z;
-                                        acc_ref(ai, jb * 4 + 3) += q.w;
-                                    }
-                                }
-                    }
-                }
+                // range starts inside the tile: hand the segment over (slot = this CTA); head of a tile
+                // that the following CTAs finish: stored the same way (slot = grid + this CTA) and
+                // added up from memory below
+                partial_tile = kb != 0;
+                head_tile = kb == 0 && ke != k_tiles;
+                slot = head_tile ? gridDim.x + blockIdx.x : blockIdx.x;
             }
+            const bool raw = partial_tile || head_tile;
             float* base;
             int ld, row_lim, col_lim, vec_ok;
             const float* bias = nullptr;
             int act = 0;
-            if (partial_tile) {
+            if (raw) {
                 base = p.partial + slot * (C::BM * BN);
                 ld = BN; row_lim = C::BM; col_lim = BN; vec_ok = 1;
             } else {
@@ -599,8 +592,85 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + blockIdx.x), "r"(1u) : "memory");
                 }
             }
+            if (MODE == 2 && head_tile) {
+                // Head of a tile that the following CTAs finish.  The accumulators are in memory
+                // now; the tile is put together from memory: this CTA's segment (k from 0) plus
+                // the partial tiles of the following CTAs in ascending CTA = ascending k, then the
+                // epilogue.  (Adding the partial tiles to the accumulators instead would give the
+                // kernel a second loop over all 128 of them, which costs the main loop registers.)
+                volatile int& s_hi = *reinterpret_cast<volatile int*>(smem + C::OFF_BAR + 256);
+                if (tid == 0) {
+                    const long long u_hi = (unit - p.sk_first + 1) * k_tiles;   // end of this tile in the unit range
+                    int hi = blockIdx.x;
+                    while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
+                    s_hi = hi;
+                    for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
+                        const unsigned long long t0 = global_timer_ns();
+                        unsigned int spins = 0, v;
+                        for (;;) {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sk_flags + cta) : "memory");
+                            if (v != 0u) break;
+                            if ((++spins & 63u) == 0 && global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                                *cta_abort = 1u;
+                                if (p.status) atomicCAS(p.status, 0u, static_cast<unsigned int>(DEV_WAIT_STREAMK));
+                                break;
+                            }
+                        }
+                        p.sk_flags[cta] = 0u;   // consumed: the next launch starts from zero again
+                    }
+                }
+                consumer_sync();                // this CTA's segment is stored; the others' flags were seen
+                if (*cta_abort) return;
+                const int hi = s_hi;
+                const float* mine = p.partial + slot * (C::BM * BN);
+                float* ctile = scatter_base(p.epi, p.c, tm * C::BM) + static_cast<long long>(bidx) * p.shape.M * p.shape.N +
+                               static_cast<long long>(tm) * C::BM * p.shape.N + tn * BN;
+                const int rows_here = p.shape.M - tm * C::BM, cols_here = p.shape.N - tn * BN;
+                const float* tbias = p.epi.bias ? p.epi.bias + tn * BN : nullptr;
+                // Eight float4 per thread at a time: all loads of a group are issued before the first
+                // is used (the stores to C may alias the workspace as far as the compiler knows, so it
+                // would not move loads across them by itself).
+                constexpr int UF = 8;
+                constexpr int TOTAL4 = C::BM * BN / 4;
+                for (int e0 = tid; e0 < TOTAL4; e0 += WARPS * 32 * UF) {
+                    float4 sum[UF];
+    #pragma unroll
+                    for (int u = 0; u < UF; u++) {
+                        const int e = e0 + u * WARPS * 32;
+                        sum[u] = e < TOTAL4 ? __ldcg(reinterpret_cast<const float4*>(mine) + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
+                        const float4* part = reinterpret_cast<const float4*>(p.partial + static_cast<long long>(cta) * (C::BM * BN));
+                        float4 q[UF];
+    #pragma unroll
+                        for (int u = 0; u < UF; u++) {
+                            const int e = e0 + u * WARPS * 32;
+                            q[u] = e < TOTAL4 ? __ldcg(part + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+    #pragma unroll
+                        for (int u = 0; u < UF; u++) {
+                            sum[u].x += q[u].x; sum[u].y += q[u].y; sum[u].z += q[u].z; sum[u].w += q[u].w;
+                        }
+                    }
+    #pragma unroll
+                    for (int u = 0; u < UF; u++) {
+                        const int e = e0 + u * WARPS * 32;
+                        const int lr = e / (BN / 4), lc = (e % (BN / 4)) * 4;
+                        if (e >= TOTAL4 || lr >= rows_here || lc >= cols_here) continue;
+                        float v[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                        if (tbias != nullptr || p.epi.act != 0) bias_act4(v, tbias, lc, cols_here, p.epi.act);
+                        float* crow = ctile + static_cast<long long>(lr) * p.shape.N;
+                        if (p.c_vec_ok && lc + 3 < cols_here) {
+                            *reinterpret_cast<float4*>(crow + lc) = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+    #pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                if (lc + j < cols_here) crow[lc + j] = v[j];
+                        }
+                    }
+                }
+            }
         }
-        w = w_next;
     }
 }
 

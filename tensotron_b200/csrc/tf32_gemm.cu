@@ -229,6 +229,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* acc_empty = acc_full + ACC_BUFS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
     volatile uint32_t* cta_abort = tmem_slot + 1;
+    uint64_t* drain_bar = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // only used on the way out after a wait gave up
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -243,6 +244,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], EPI_WARPS);
         }
+        mbar_init(drain_bar, 1);
         *cta_abort = 0u;
         fence_mbar_init();
     }
@@ -264,7 +266,7 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 prefetch_tensormap(&map_alo);
                 prefetch_tensormap(&map_blo);
             }
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, armed = 0;   // armed: stages armed so far, counted up to STAGES
             bool ok = true;
             for (long long w = blockIdx.x; ok && w < p.shape.work; w += gridDim.x) {
                 const TileCoord tc = decode_tile(w, p.shape);
@@ -311,6 +313,17 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (armed < STAGES) armed++;
+                }
+            }
+            if (!ok || *cta_abort) {
+                // A wait gave up somewhere in this CTA: before the teardown, wait (again with a limit)
+                // for the loads this thread issued itself -- the last arming of every stage.
+                uint32_t st = stage, ph = phase;
+                for (uint32_t i = 0; i < armed; i++) {
+                    if (st == 0) { st = STAGES; ph ^= 1u; }
+                    st--;
+                    mbar_wait_drain(&full_bar[st], ph);
                 }
             }
         }
@@ -366,6 +379,12 @@ tf32_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) break;
                 umma_commit(&acc_full[acc]);  // accumulator complete
                 if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (*cta_abort) {
+                // leaving after a wait gave up: the MMAs issued so far must have retired before the
+                // TMEM they write is freed (commit to a barrier of its own, bounded wait)
+                umma_commit(drain_bar);
+                mbar_wait_drain(drain_bar, 0u);
             }
         }
     } else {

@@ -232,6 +232,38 @@ def test_stream_k_matches_oracle_and_is_repeatable(rt, shape, layout):
     assert np.abs(r0 - exp).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("variant,shape", [
+    (6, (512, 11392, 256)),     # 178 tiles of 256x128: less than half a wave behind the first one -> all of it dealt out as units
+    (6, (1024, 12672, 256)),    # 396 tiles: two whole waves round-robin, 100 tiles dealt out as units
+    (6, (1024, 10112, 264)),    # 316 tiles: one whole wave, 168 tiles as units (a tile and a bit per CTA); ragged K
+    (9, (1024, 1024, 1024)),    # 64 tiles of 128x128 over 148 CTAs: up to three CTAs per tile
+    (9, (900, 1156, 520)),      # ragged, 80 tiles
+    (9, (2048, 2304, 512)),     # 288 tiles of 128x128: one whole wave + 140 tiles as units
+])
+def test_stream_k_behind_whole_waves(rt, variant, shape):
+    """Multi-wave grids in stream-K mode: whole waves of tiles first (round-robin, as in the whole-tile
+    mode), then the k-tile units of the remaining tiles in equal contiguous ranges.  Compared with
+    the oracle on sampled rows and with the whole-tile kernel everywhere; bit-stable from run to run."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = layout_strides("TN", M, N, K)             # both operands MN-major: no pre-transposition involved
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, variant)
+    stats = rt.Stats()
+    assert stats["simt_tma"] == 1 and stats["splitk"] == 1 and stats["launches"] == 1, stats
+    r2 = run_matmul(rt, a, b, M, N, K, st, variant)
+    assert np.array_equal(r1, r2)
+    whole = run_matmul(rt, a, b, M, N, K, st, 2 if variant == 6 else 3)
+    assert np.abs(r1 - whole).max() <= fp32_bound(K, a, b)
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 24)]))
+    am = a.reshape(K, M)[:, rows]                   # "T": stored (K, M)
+    exp = am.T.astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    assert np.abs(r1[rows] - exp).max() <= fp32_bound(K, a, b)
+    rt.Check()
+
+
 @pytest.mark.parametrize("layout,shape", [("NN", (1028, 1540, 1032)), ("NT", (2564, 1540, 1028)), ("NT", (1028, 1540, 1032)),
                                           ("NT", (508, 1540, 1032)), ("NT", (1028, 508, 1032)), ("NN", (300, 508, 1032))])
 def test_large_k_major_operands_are_transposed_once_without_changing_a_bit(rt, layout, shape):
@@ -447,8 +479,10 @@ def test_linear_golden_cases(rt, seeded_cases):
         rt.ResetCounters()
         y = lin.Forward(xd)
         assert rt.Stats()["launches"] == 1       # Linear + bias + activation = one launch
+        rt.ResetCounters()
         dx, dw, db = lin.Backward(xd, y, dy)
         rt.Check()
+        assert rt.Stats()["launches"] == 1       # activation backward + bias gradient + dX + dW = one launch
         np.testing.assert_allclose(y.cpu().numpy(), arrays[c["output"]], atol=1e-4, rtol=1e-4)
         np.testing.assert_allclose(dx.cpu().numpy(), arrays[c["grads"][0]], atol=2e-4, rtol=2e-4)
         np.testing.assert_allclose(dw.cpu().numpy(), arrays[c["grads"][1]], atol=2e-4, rtol=2e-4)

@@ -632,6 +632,33 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Runs this rank on the CPUs of the NUMA node its GPU hangs off, before any pinned host buffer is
+    allocated: first-touch then places the buffers in that node's memory, so the host <-> device copies
+    of the end-to-end leg do not cross the socket interconnect.  Returns the node, or None when the
+    platform does not say (no sysfs entry, a single node, a container without the CPUs)."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % bdf) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -737,9 +764,12 @@ def main():
     # host buffer and one NCCL all-gather lands the whole B in every rank's local HBM (the GEMM's
     # operands and tensor maps are local memory only).
     brow = n // world
+    all_cpus = os.sched_getaffinity(0)
+    numa = bind_to_gpu_numa_node(local_rank)   # first touch of the pinned buffers below happens on the GPU's node
     ha = torch.empty((rows, n), pin_memory=True).copy_(a)
     hb = torch.empty((brow, n), pin_memory=True).copy_(b[rank * brow:(rank + 1) * brow])
-    hc = torch.empty((rows, n), pin_memory=True)
+    hc = torch.empty((rows, n), pin_memory=True).zero_()
+    os.sched_setaffinity(0, all_cpus)          # the host buffers are placed: give the CPU legs their cores back
     e2e_steps = max(1, min(args.steps, 5))
 
     # Every step copies its operands from pinned host memory and returns its C-shard to the
@@ -879,7 +909,8 @@ def main():
                     "per_rank": "H2D %d rows of A + %d rows of B, D2H %d rows of C" % (rows, brow, rows),
                     "b_placement": "local" if world == 1 else "each rank copies 1/%d of B from the host, one NCCL all-gather "
                                    "lands the whole B in every rank's HBM" % world,
-                    "pipeline": "%d row chunks per step on H2D / compute / D2H streams, two buffer sets" % n_chunks},
+                    "pipeline": "%d row chunks per step on H2D / compute / D2H streams, two buffer sets" % n_chunks,
+                    "host_numa_node": numa},
             "gpu_launches": launches,
             "check": check,
             "roofline": roof,

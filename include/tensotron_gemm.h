@@ -288,7 +288,9 @@ TT_API int tt_check(tt_handle_t h, void* stream);
  * 7 FFMA kernel with 128x192 tiles (B contiguous along N only),
  * 8 any-stride kernel with its K ranges added through the workspace (two launches) instead of
  *   through a thread-block cluster,
- * 9 FFMA kernel with 128x128 tiles and stream-K work distribution. */
+ * 9 FFMA kernel with 128x128 tiles and stream-K work distribution,
+ * 10 automatic, but tall products with N <= 16 keep the K-cut streaming kernel instead of the
+ *   TMA-fed one. */
 TT_API int tt_set_variant(tt_handle_t h, int variant);
 
 /* ---- Data-parallel gradient exchange over peer memory ---------------------------------

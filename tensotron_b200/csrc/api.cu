@@ -569,6 +569,30 @@ int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         g.aMs % 4 == 0 && (g.N == 1 || g.bNs % 4 == 0) && aligned16(g.a) && aligned16(g.b)) {
         // 8 rows per CTA while the accumulators fit comfortably; 4 rows for N > 8 (8 x 12 and
         // 8 x 16 accumulators run slower: 105 vs 88 us at 8192 x 10 x 4096)
+        // Tall products (half a wave of 56-row units or more): the TMA-fed stream, a persistent CTA
+        // per SM.  Variant 10 keeps the K-cut form below for comparison.
+        const int units = (g.M + skinny::stream::RB - 1) / skinny::stream::RB;
+        if (h->variant != 10 && units >= h->num_sms / 2) {
+            OperandView va, vb;
+            CUtensorMap ma, mb;
+            const int nt = g.N <= 4 ? 4 : g.N <= 8 ? 8 : g.N <= 12 ? 12 : 16;
+            if (operand_view(g.a, g.M, g.K, g.aMs, 1, va) == 1 && operand_view(g.b, g.N, g.K, g.bNs, 1, vb) == 1 &&
+                tma_compatible(va) && tma_compatible(vb) &&
+                encode_tensor_map(&ma, va, skinny::stream::KC, skinny::stream::RB, Swizzle::None) == 0 &&
+                encode_tensor_map(&mb, vb, skinny::stream::KC, nt, Swizzle::None) == 0) {
+                const int grid = units < h->num_sms ? units : h->num_sms;
+                const unsigned int th = skinny::stream::THREADS;
+                if (nt == 4)       skinny::skinny_n_stream_kernel<4><<<grid, th, skinny::stream::Cfg<4>::SMEM_BYTES, st>>>(ma, mb, g.c, g.M, g.N, g.K, g.epi, h->status);
+                else if (nt == 8)  skinny::skinny_n_stream_kernel<8><<<grid, th, skinny::stream::Cfg<8>::SMEM_BYTES, st>>>(ma, mb, g.c, g.M, g.N, g.K, g.epi, h->status);
+                else if (nt == 12) skinny::skinny_n_stream_kernel<12><<<grid, th, skinny::stream::Cfg<12>::SMEM_BYTES, st>>>(ma, mb, g.c, g.M, g.N, g.K, g.epi, h->status);
+                else               skinny::skinny_n_stream_kernel<16><<<grid, th, skinny::stream::Cfg<16>::SMEM_BYTES, st>>>(ma, mb, g.c, g.M, g.N, g.K, g.epi, h->status);
+                h->stats.launches++;
+                const cudaError_t e = cudaGetLastError();
+                if (e != cudaSuccess) return cuda_fail(h, e, "skinny stream launch");
+                h->stats.skinny++;
+                return TT_OK;
+            }
+        }
         const int rows = g.N <= 8 ? 8 : 4;
         const unsigned int blocks = static_cast<unsigned int>((g.M + rows - 1) / rows);   // one CTA per row group
         if (g.N <= 4)
@@ -639,7 +663,7 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         return try_launch_simt(h, st, g);
     }
     const long long vol = static_cast<long long>(g.M) * g.N * (g.K > 0 ? g.K : 1);
-    if (g.K > 0 && h->variant == 0) {
+    if (g.K > 0 && (h->variant == 0 || h->variant == 10)) {
         // one tiny dimension: stream the large operand once, in every math mode (strict FP32
         // arithmetic, so at least as accurate as the mode asks for)
         const int rc = try_launch_skinny(h, st, g);
@@ -726,6 +750,14 @@ cudaError_t init_kernels()
                                                cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     if (!g_generic_cluster16) cudaGetLastError();
     if (mlp_step::init_device() != 0) return cudaErrorUnknown;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_n_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::stream::Cfg<4>::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_n_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::stream::Cfg<8>::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_n_stream_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::stream::Cfg<12>::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_n_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::stream::Cfg<16>::SMEM_BYTES)) != cudaSuccess) return e;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
 
@@ -970,7 +1002,7 @@ TT_API int tt_get_math_mode(tt_handle_t h, int* mode)
 
 TT_API int tt_set_variant(tt_handle_t h, int variant)
 {
-    if (!h || variant < 0 || variant > 9) return TT_ERR_INVALID_ARG;
+    if (!h || variant < 0 || variant > 10) return TT_ERR_INVALID_ARG;
     h->variant = variant;
     return TT_OK;
 }

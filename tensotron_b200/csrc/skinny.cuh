@@ -11,6 +11,7 @@
 //                    (K is cut into ranges across CTAs; partials are added in range order)
 #pragma once
 #include "gemm_common.h"
+#include "ptx.cuh"
 
 namespace tt {
 namespace skinny {
@@ -123,6 +124,153 @@ skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
             for (int w = 1; w < 8; w++) s += part[w][r][n];
             if (epi.bias) s += __ldg(epi.bias + n);
             c[static_cast<long long>(m0 + r) * N + n] = act_apply(s, epi.act);
+        }
+    }
+}
+
+// ---- small N, tall M: TMA-fed stream ----------------------------------------------------------
+// The K-cut form above keeps a few kilobytes per warp in flight and sits at a quarter of the HBM
+// bandwidth when M is large.  Here the bytes in flight are explicit: a persistent CTA per SM, one
+// producer thread that keeps a ring of 4 stages filled by TMA (a stage = 56 rows x 128 k of A, 28 KB,
+// plus the matching 128 k of all rows of B), and 7 consumer warps that read both from shared memory
+// (256 threads, so the consumers may use 255 registers).  A unit of work is 56 consecutive rows over
+// the whole K; warp w owns rows 8w .. 8w+7 of the unit, lane l the four k at 4l of every 128-k chunk, so a lane holds
+// 8 x N partial sums over the chunks (visited in an order rotated by the unit index: rows are a
+// power-of-two number of bytes apart, and all CTAs walking them from the same offset would keep
+// hitting the same memory channels) and a fixed xor-shuffle tree adds the lanes at the end of the
+// unit.  One accumulator per lane and output, an order that depends on the row only: bit-stable.
+namespace stream {
+constexpr int CONSUMER_WARPS = 7, RB = 8 * CONSUMER_WARPS, KC = 128, STAGES = 4, THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int A_BYTES = RB * KC * 4;
+template <int NT> struct Cfg {
+    static constexpr int B_BYTES = NT * KC * 4;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BAR + 256 + 128;     // barriers + abort word, alignment slack
+};
+}  // namespace stream
+
+template <int NT>
+__global__ void __launch_bounds__(stream::THREADS, 1)
+skinny_n_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       float* __restrict__ c, int M, int N, int K, Epilogue epi, unsigned int* status)
+{
+    using namespace stream;
+    using C = Cfg<NT>;
+    extern __shared__ uint8_t skinny_smem_raw[];
+    uint8_t* smem = skinny_smem_raw + ((128u - (smem_u32(skinny_smem_raw) & 127u)) & 127u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* empty_bar = full_bar + STAGES;
+    volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_chunks = (K + KC - 1) / KC;
+    const int units = (M + RB - 1) / RB;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], CONSUMER_WARPS);
+        }
+        *cta_abort = 0u;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------- producer -------------------------------
+        if (lane != 0) return;
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        uint32_t ps = 0, use = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+            const int rot = unit % k_chunks;
+            for (int i = 0; i < k_chunks; i++) {
+                int kc = i + rot;
+                if (kc >= k_chunks) kc -= k_chunks;
+                if (use > 0 && !mbar_wait_bounded(&empty_bar[ps], (use - 1) & 1u, cta_abort, status, DEV_WAIT_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* sa = smem + ps * C::STAGE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[ps], C::STAGE_BYTES);
+                tma_load_5d(sa, &map_a, &full_bar[ps], kc * KC, unit * RB, 0, 0, 0);
+                tma_load_5d(sa + A_BYTES, &map_b, &full_bar[ps], kc * KC, 0, 0, 0, 0);
+                if (++ps == STAGES) { ps = 0; use++; }
+            }
+        }
+        if (!ok) {
+            // a wait gave up: wait (with a limit) for the loads this thread issued before leaving
+            uint32_t s = ps, u = use;
+            for (int i = 0; i < STAGES; i++) {
+                if (s == 0) {
+                    if (u == 0) break;
+                    s = STAGES;
+                    u--;
+                }
+                s--;
+                mbar_wait_drain(&full_bar[s], u & 1u);
+            }
+        }
+        return;
+    }
+    // -------------------------------- consumers --------------------------------
+    uint32_t stage = 0, phase = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        float acc[8][NT];
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+#pragma unroll
+            for (int n = 0; n < NT; n++) acc[r][n] = 0.f;
+        for (int i = 0; i < k_chunks; i++) {
+            if (!mbar_wait_bounded(&full_bar[stage], phase, cta_abort, status, DEV_WAIT_FULL)) return;
+            const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES) + lane * 16;
+            const uint32_t sb = sa + A_BYTES;
+            // columns in groups of at most 8, so that a group's B fragments and the 8 x 8 sums it
+            // updates stay in registers (the A fragments are read again per group: shared-memory
+            // bandwidth is not what bounds this kernel)
+#pragma unroll
+            for (int n0 = 0; n0 < NT; n0 += 8) {
+                constexpr int NG = NT < 8 ? NT : 8;
+                float4 bv[NG];
+#pragma unroll
+                for (int j = 0; j < NG; j++)
+                    if (n0 + j < NT && n0 + j < N) bv[j] = lds128(sb + (n0 + j) * (KC * 4));
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    const int row = 8 * warp + r;
+                    const float4 av = lds128(sa + row * (KC * 4));
+#pragma unroll
+                    for (int j = 0; j < NG; j++) {
+                        if (n0 + j < NT && n0 + j < N) {
+                            float t = acc[r][n0 + j];
+                            t = fmaf(av.x, bv[j].x, t);
+                            t = fmaf(av.y, bv[j].y, t);
+                            t = fmaf(av.z, bv[j].z, t);
+                            t = fmaf(av.w, bv[j].w, t);
+                            acc[r][n0 + j] = t;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int m = unit * RB + 8 * warp + r;
+#pragma unroll
+            for (int n = 0; n < NT; n++) {
+                if (n < N) {
+                    float t = acc[r][n];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+                    if (lane == 0 && m < M) {
+                        if (epi.bias) t += __ldg(epi.bias + n);
+                        c[static_cast<long long>(m) * N + n] = act_apply(t, epi.act);
+                    }
+                }
+            }
         }
     }
 }

@@ -314,6 +314,28 @@ def test_tiny_dimension_kernels(rt, case):
     assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("shape", [(8192, 10, 4096), (5000, 3, 1000), (4200, 16, 260), (9000, 12, 516), (6000, 1, 2048),
+                                   (16384, 7, 128)])
+def test_tall_tiny_n_stream_kernel(rt, shape):
+    """Tall products with N <= 16 (at least half a wave of 56-row units) run on the TMA-fed stream:
+    a persistent CTA per SM, A through a shared-memory ring.  Ragged M, K that is not a multiple of the
+    128-k chunk, N = 1; against the oracle, the K-cut form (variant 10), and itself (bit-stable)."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 5 * N + 11 * K)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    st = (K, 1, 1, K)                                   # A (M, K) row-major, B stored (N, K)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    assert stats["skinny"] == 1 and stats["launches"] == 1, stats
+    assert np.array_equal(r1, run_matmul(rt, a, b, M, N, K, st, 0))
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+    cut = run_matmul(rt, a, b, M, N, K, st, 10)
+    assert np.abs(r1 - cut).max() <= fp32_bound(K, a, b)
+
+
 def test_nan_propagates_like_reference(rt):
     a = np.zeros((128, 64), dtype=np.float32)
     b = np.ones((64, 128), dtype=np.float32)

@@ -605,6 +605,44 @@ int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     } else if (g.M <= skinny::MAXD && g.N >= 256 && g.K >= 256 && g.bNs == 1 && g.N % 4 == 0 &&
                g.bKs % 4 == 0 && aligned16(g.b) && aligned16(g.c) && bias_ok) {
         const int gx = (g.N / 4 + 63) / 64;
+        if (h->variant != 10) {
+            // TMA-fed form: one CTA per SM (its ring and operand slice fill the shared memory), so
+            // the k ranges are sized for a single wave, and capped by what the slice buffer holds
+            namespace ms = skinny::mstream;
+            OperandView vb;
+            CUtensorMap mb;
+            const long long r0 = h->num_sms / gx > 0 ? h->num_sms / gx : 1;
+            int kspan = static_cast<int>((g.K + r0 - 1) / r0);
+            kspan = (kspan + ms::KT - 1) / ms::KT * ms::KT;
+            const int mt = g.M <= 4 ? 4 : g.M <= 8 ? 8 : g.M <= 12 ? 12 : 16;
+            const int ks_max = ms::A_FLOATS / mt / ms::KT * ms::KT;
+            if (kspan > ks_max) kspan = ks_max;
+            const int n_ranges = (g.K + kspan - 1) / kspan;
+            const size_t need = n_ranges > 1 ? sizeof(float) * static_cast<size_t>(n_ranges) * g.M * g.N : 0;
+            if (need <= ws_avail && operand_view(g.b, g.K, g.N, g.bKs, 1, vb) == 1 && tma_compatible(vb) &&
+                encode_tensor_map(&mb, vb, ms::NW, ms::KT, Swizzle::None) == 0) {
+                float* partial = reinterpret_cast<float*>(h->workspace + g.ws_off);
+                float* dst = n_ranges == 1 ? g.c : partial;
+                const int direct = n_ranges == 1 ? 1 : 0;
+                const dim3 grid(gx, n_ranges);
+                if (mt == 4)       skinny::skinny_m_stream_kernel<4><<<grid, ms::THREADS, ms::SMEM_BYTES, st>>>(mb, g.a, dst, g.M, g.N, g.K, g.aMs, g.aKs, kspan, g.epi, direct, h->status);
+                else if (mt == 8)  skinny::skinny_m_stream_kernel<8><<<grid, ms::THREADS, ms::SMEM_BYTES, st>>>(mb, g.a, dst, g.M, g.N, g.K, g.aMs, g.aKs, kspan, g.epi, direct, h->status);
+                else if (mt == 12) skinny::skinny_m_stream_kernel<12><<<grid, ms::THREADS, ms::SMEM_BYTES, st>>>(mb, g.a, dst, g.M, g.N, g.K, g.aMs, g.aKs, kspan, g.epi, direct, h->status);
+                else               skinny::skinny_m_stream_kernel<16><<<grid, ms::THREADS, ms::SMEM_BYTES, st>>>(mb, g.a, dst, g.M, g.N, g.K, g.aMs, g.aKs, kspan, g.epi, direct, h->status);
+                h->stats.launches++;
+                if (n_ranges > 1) {
+                    const long long count4 = static_cast<long long>(g.M) * g.N / 4;
+                    skinny::skinny_reduce_kernel<<<static_cast<unsigned int>((count4 + 255) / 256), 256, 0, st>>>(
+                        partial, g.c, count4, g.N, n_ranges, static_cast<long long>(g.M) * g.N, g.epi);
+                    h->stats.launches++;
+                    h->stats.splitk++;
+                }
+                const cudaError_t e = cudaGetLastError();
+                if (e != cudaSuccess) return cuda_fail(h, e, "skinny stream launch");
+                h->stats.skinny++;
+                return TT_OK;
+            }
+        }
         long long ranges = (4ll * h->num_sms + gx - 1) / gx;
         if (ranges > g.K / 64) ranges = g.K / 64;
         const size_t per_range = sizeof(float) * static_cast<size_t>(g.M) * g.N;
@@ -758,6 +796,14 @@ cudaError_t init_kernels()
                                   skinny::stream::Cfg<12>::SMEM_BYTES)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(skinny::skinny_n_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   skinny::stream::Cfg<16>::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_m_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::mstream::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_m_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::mstream::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_m_stream_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::mstream::SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(skinny::skinny_m_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  skinny::mstream::SMEM_BYTES)) != cudaSuccess) return e;
     return tf32::init_device() == 0 ? cudaSuccess : cudaErrorUnknown;
 }
 

@@ -335,6 +335,154 @@ skinny_m_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
     }
 }
 
+// ---- small M, TMA-fed ---------------------------------------------------------------------------
+// The same product with the bytes in flight made explicit.  CTA (x, y) owns 256 columns and the k
+// range y.  A producer thread keeps a ring of 4 stages filled by TMA (a stage = 32 k x 256 columns of
+// B, 32 KB); the CTA's slice of the small operand (k range x M, at most 64 KB) is copied into shared
+// memory once at the start, M rounded up to 4 per k so a thread fetches it as float4 broadcasts.  The 256
+// consumer threads are the 64 column groups x 4 k lanes of skinny_m_kernel and walk k in the same
+// order, so for the same k ranges the sums are the same sums.
+namespace mstream {
+constexpr int KT = 32, NW = 256, STAGES = 4, THREADS = 288, A_FLOATS = 16384;
+constexpr int STAGE_BYTES = KT * NW * 4;
+constexpr int OFF_A = STAGES * STAGE_BYTES;
+constexpr int OFF_RED = OFF_A + A_FLOATS * 4;
+constexpr int OFF_BAR = OFF_RED + 4 * 64 * 16;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 128;
+}  // namespace mstream
+
+// M <= MT; the k range of a CTA is at most A_FLOATS / MT (a multiple of KT).
+template <int MT>
+__global__ void __launch_bounds__(mstream::THREADS, 1)
+skinny_m_stream_kernel(const __grid_constant__ CUtensorMap map_b, const float* __restrict__ a, float* __restrict__ out,
+                       int M, int N, int K, int aMs, int aKs, int kspan, Epilogue epi, int direct, unsigned int* status)
+{
+    using namespace mstream;
+    extern __shared__ uint8_t skinny_smem_raw[];
+    uint8_t* smem = skinny_smem_raw + ((128u - (smem_u32(skinny_smem_raw) & 127u)) & 127u);
+    float* as_ = reinterpret_cast<float*>(smem + OFF_A);
+    float4* red = reinterpret_cast<float4*>(smem + OFF_RED);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* empty_bar = full_bar + STAGES;
+    volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * NW;
+    const int k0 = blockIdx.y * kspan;
+    const int k1 = min(K, k0 + kspan);
+    const int tiles = (k1 - k0 + KT - 1) / KT;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 8);
+        }
+        *cta_abort = 0u;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == 8) {
+        // ------------------------------- producer -------------------------------
+        if (lane != 0) return;
+        prefetch_tensormap(&map_b);
+        uint32_t ps = 0, use = 0;
+        bool ok = true;
+        for (int t = 0; t < tiles; t++) {
+            if (use > 0 && !mbar_wait_bounded(&empty_bar[ps], (use - 1) & 1u, cta_abort, status, DEV_WAIT_EMPTY)) {
+                ok = false;
+                break;
+            }
+            mbar_arrive_expect_tx(&full_bar[ps], STAGE_BYTES);
+            tma_load_5d(smem + ps * STAGE_BYTES, &map_b, &full_bar[ps], n0, k0 + t * KT, 0, 0, 0);
+            if (++ps == STAGES) { ps = 0; use++; }
+        }
+        if (!ok) {
+            uint32_t s = ps, u = use;
+            for (int i = 0; i < STAGES; i++) {
+                if (s == 0) {
+                    if (u == 0) break;
+                    s = STAGES;
+                    u--;
+                }
+                s--;
+                mbar_wait_drain(&full_bar[s], u & 1u);
+            }
+        }
+        return;
+    }
+    // -------------------------------- consumers --------------------------------
+    const int tid = threadIdx.x;          // 0 .. 255
+    const int cl = tid & 63, kl = tid >> 6;
+    // the small operand's slice: as_[k - k0][m], zero beyond K
+    for (int i = tid; i < tiles * KT * M; i += 256) {
+        const int kk = i / M, m = i - kk * M;
+        const int k = k0 + kk;
+        as_[kk * MT + m] = k < K ? __ldg(a + static_cast<long long>(m) * aMs + static_cast<long long>(k) * aKs) : 0.f;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float4 acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) acc[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint32_t stage = 0, phase = 0;
+    const uint32_t as_u32 = smem_u32(as_);
+    for (int t = 0; t < tiles; t++) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, cta_abort, status, DEV_WAIT_FULL)) return;
+        const uint32_t sb = smem_u32(smem + stage * STAGE_BYTES) + cl * 16;
+#pragma unroll 2
+        for (int i = 0; i < KT / 4; i++) {
+            const int kk = kl + 4 * i;
+            const float4 bv = lds128(sb + kk * (NW * 4));
+            const uint32_t ap = as_u32 + ((t * KT + kk) * MT) * 4;
+#pragma unroll
+            for (int j = 0; j < MT / 4; j++) {
+                if (4 * j < M) {
+                    const float4 av = lds128(ap + j * 16);
+                    const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int m = 4 * j + q;
+                        if (m < M) {
+                            acc[m].x = fmaf(a4[q], bv.x, acc[m].x);
+                            acc[m].y = fmaf(a4[q], bv.y, acc[m].y);
+                            acc[m].z = fmaf(a4[q], bv.z, acc[m].z);
+                            acc[m].w = fmaf(a4[q], bv.w, acc[m].w);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
+    const int n = n0 + cl * 4;
+    float* dst = out + (direct ? 0ll : static_cast<long long>(blockIdx.y) * M * N);
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        if (m < M) {                       // uniform across the CTA
+            red[kl * 64 + cl] = acc[m];
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (kl == 0 && n < N) {
+                float4 s = red[cl];
+#pragma unroll
+                for (int l = 1; l < 4; l++) {
+                    const float4 q = red[l * 64 + cl];
+                    s.x += q.x; s.y += q.y; s.z += q.z; s.w += q.w;
+                }
+                if (direct) {
+                    if (epi.bias) {
+                        const float4 bb = __ldg(reinterpret_cast<const float4*>(epi.bias + n));
+                        s.x += bb.x; s.y += bb.y; s.z += bb.z; s.w += bb.w;
+                    }
+                    s.x = act_apply(s.x, epi.act); s.y = act_apply(s.y, epi.act);
+                    s.z = act_apply(s.z, epi.act); s.w = act_apply(s.w, epi.act);
+                }
+                *reinterpret_cast<float4*>(dst + static_cast<long long>(m) * N + n) = s;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+    }
+}
+
 // C[i] = act(sum over ranges (ascending) of partial[range][i] + bias[i % N]); 4 elements per thread.
 __global__ void __launch_bounds__(256)
 skinny_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, long long count4, int N,

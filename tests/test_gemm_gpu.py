@@ -336,6 +336,33 @@ def test_tall_tiny_n_stream_kernel(rt, shape):
     assert np.abs(r1 - cut).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("case", [
+    # (M, N, K, strides)
+    (10, 4096, 8192, (1, 10, 4096, 1)),        # dW of the 10-class layer: g stored (K, 10), x (K, N)
+    (16, 1024, 3000, (3000, 1, 1024, 1)),      # A stored (M, K); K not a multiple of the 32-k tile
+    (3, 260, 300, (300, 1, 260, 1)),           # N just above one 256-column block
+    (7, 772, 1000, (1, 7, 772, 1)),
+    (12, 2048, 16384, (1, 12, 2048, 1)),       # k ranges capped by the slice buffer: more CTAs than one wave
+])
+def test_tiny_m_stream_kernel(rt, case):
+    """Products with M <= 16 and a large K x N operand run on the TMA-fed stream (B through a
+    shared-memory ring, the small operand's slice resident); against the oracle, the plain-load
+    form (variant 10), and itself (bit-stable)."""
+    M, N, K, st = case
+    rng = np.random.default_rng(M * 3 + N * 5 + K * 7)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    assert stats["skinny"] == 1 and stats["launches"] <= 2, stats
+    assert np.array_equal(r1, run_matmul(rt, a, b, M, N, K, st, 0))
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+    plain = run_matmul(rt, a, b, M, N, K, st, 10)
+    assert np.abs(r1 - plain).max() <= fp32_bound(K, a, b)
+
+
 def test_nan_propagates_like_reference(rt):
     a = np.zeros((128, 64), dtype=np.float32)
     b = np.ones((64, 128), dtype=np.float32)

@@ -141,6 +141,7 @@ skinny_n_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
 // unit.  One accumulator per lane and output, an order that depends on the row only: bit-stable.
 namespace stream {
 constexpr int CONSUMER_WARPS = 7, RB = 8 * CONSUMER_WARPS, KC = 128, STAGES = 4, THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int KJ = KC / 128;      // float4s per lane, row and chunk
 constexpr int A_BYTES = RB * KC * 4;
 template <int NT> struct Cfg {
     static constexpr int B_BYTES = NT * KC * 4;
@@ -214,43 +215,59 @@ skinny_n_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         return;
     }
     // -------------------------------- consumers --------------------------------
+    // Two partial sums per output (the even and the odd pairs of a lane's four k per chunk), so the
+    // four multiply-adds of a chunk are two packed two-wide FMAs: the kernel is bound by instruction
+    // issue at 10 columns, not by the memory system.  The two are added when the unit is finished.
     uint32_t stage = 0, phase = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-        float acc[8][NT];
+        // (more than 8 columns would need over 200 registers for the pairs: those groups keep one sum per output)
+        constexpr bool PACK = NT <= 8;
+        float2 acc[8][NT];
 #pragma unroll
         for (int r = 0; r < 8; r++)
 #pragma unroll
-            for (int n = 0; n < NT; n++) acc[r][n] = 0.f;
+            for (int n = 0; n < NT; n++) acc[r][n] = make_float2(0.f, 0.f);
         for (int i = 0; i < k_chunks; i++) {
             if (!mbar_wait_bounded(&full_bar[stage], phase, cta_abort, status, DEV_WAIT_FULL)) return;
-            const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES) + lane * 16;
+            const uint32_t sa0 = smem_u32(smem + stage * C::STAGE_BYTES) + lane * 16;
+            // columns in groups of at most 8, so that a group's B fragments and the sums it updates
+            // stay in registers (the A fragments are read again per group: shared-memory bandwidth
+            // is not what bounds this kernel)
+#pragma unroll
+            for (int kj = 0; kj < KJ; kj++) {
+            const uint32_t sa = sa0 + kj * 512;
             const uint32_t sb = sa + A_BYTES;
-            // columns in groups of at most 8, so that a group's B fragments and the 8 x 8 sums it
-            // updates stay in registers (the A fragments are read again per group: shared-memory
-            // bandwidth is not what bounds this kernel)
 #pragma unroll
             for (int n0 = 0; n0 < NT; n0 += 8) {
                 constexpr int NG = NT < 8 ? NT : 8;
                 float4 bv[NG];
 #pragma unroll
                 for (int j = 0; j < NG; j++)
-                    if (n0 + j < NT && n0 + j < N) bv[j] = lds128(sb + (n0 + j) * (KC * 4));
+                    if (n0 + j < NT) bv[j] = lds128(sb + (n0 + j) * (KC * 4));   // rows >= N of the stage are zero (TMA fill)
 #pragma unroll
                 for (int r = 0; r < 8; r++) {
                     const int row = 8 * warp + r;
                     const float4 av = lds128(sa + row * (KC * 4));
 #pragma unroll
                     for (int j = 0; j < NG; j++) {
-                        if (n0 + j < NT && n0 + j < N) {
-                            float t = acc[r][n0 + j];
-                            t = fmaf(av.x, bv[j].x, t);
-                            t = fmaf(av.y, bv[j].y, t);
-                            t = fmaf(av.z, bv[j].z, t);
-                            t = fmaf(av.w, bv[j].w, t);
-                            acc[r][n0 + j] = t;
+                        if (n0 + j < NT) {           // no test against N: straight-line code, zeros for the columns beyond it
+                            if constexpr (PACK) {
+                                float2 t = acc[r][n0 + j];
+                                t = __ffma2_rn(make_float2(av.x, av.y), make_float2(bv[j].x, bv[j].y), t);
+                                t = __ffma2_rn(make_float2(av.z, av.w), make_float2(bv[j].z, bv[j].w), t);
+                                acc[r][n0 + j] = t;
+                            } else {
+                                float t = acc[r][n0 + j].x;      // (.y stays zero and is never touched: no register)
+                                t = fmaf(av.x, bv[j].x, t);
+                                t = fmaf(av.y, bv[j].y, t);
+                                t = fmaf(av.z, bv[j].z, t);
+                                t = fmaf(av.w, bv[j].w, t);
+                                acc[r][n0 + j].x = t;
+                            }
                         }
                     }
                 }
+            }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);
@@ -262,7 +279,7 @@ skinny_n_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
             for (int n = 0; n < NT; n++) {
                 if (n < N) {
-                    float t = acc[r][n];
+                    float t = PACK ? acc[r][n].x + acc[r][n].y : acc[r][n].x;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
                     if (lane == 0 && m < M) {
@@ -412,11 +429,12 @@ skinny_m_stream_kernel(const __grid_constant__ CUtensorMap map_b, const float* _
     // -------------------------------- consumers --------------------------------
     const int tid = threadIdx.x;          // 0 .. 255
     const int cl = tid & 63, kl = tid >> 6;
-    // the small operand's slice: as_[k - k0][m], zero beyond K
-    for (int i = tid; i < tiles * KT * M; i += 256) {
-        const int kk = i / M, m = i - kk * M;
+    // the small operand's slice: as_[k - k0][m], zero beyond K and for the rows between M and MT (the
+    // main loop then needs no test against M: straight-line code)
+    for (int i = tid; i < tiles * KT * MT; i += 256) {
+        const int kk = i / MT, m = i - kk * MT;
         const int k = k0 + kk;
-        as_[kk * MT + m] = k < K ? __ldg(a + static_cast<long long>(m) * aMs + static_cast<long long>(k) * aKs) : 0.f;
+        as_[i] = (k < K && m < M) ? __ldg(a + static_cast<long long>(m) * aMs + static_cast<long long>(k) * aKs) : 0.f;
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
     float4 acc[MT];
@@ -434,17 +452,19 @@ skinny_m_stream_kernel(const __grid_constant__ CUtensorMap map_b, const float* _
             const uint32_t ap = as_u32 + ((t * KT + kk) * MT) * 4;
 #pragma unroll
             for (int j = 0; j < MT / 4; j++) {
-                if (4 * j < M) {
+                {
                     const float4 av = lds128(ap + j * 16);
                     const float a4[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const int m = 4 * j + q;
-                        if (m < M) {
-                            acc[m].x = fmaf(a4[q], bv.x, acc[m].x);
-                            acc[m].y = fmaf(a4[q], bv.y, acc[m].y);
-                            acc[m].z = fmaf(a4[q], bv.z, acc[m].z);
-                            acc[m].w = fmaf(a4[q], bv.w, acc[m].w);
+                        {
+                            // two packed two-wide FMAs (each lane an IEEE fused multiply-add: the bits
+                            // of four scalar fmaf)
+                            const float2 ap = make_float2(a4[q], a4[q]);
+                            const float2 lo = __ffma2_rn(ap, make_float2(bv.x, bv.y), make_float2(acc[m].x, acc[m].y));
+                            const float2 hi = __ffma2_rn(ap, make_float2(bv.z, bv.w), make_float2(acc[m].z, acc[m].w));
+                            acc[m] = make_float4(lo.x, lo.y, hi.x, hi.y);
                         }
                     }
                 }

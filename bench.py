@@ -770,7 +770,7 @@ def main():
     hb = torch.empty((brow, n), pin_memory=True).copy_(b[rank * brow:(rank + 1) * brow])
     hc = torch.empty((rows, n), pin_memory=True).zero_()
     os.sched_setaffinity(0, all_cpus)          # the host buffers are placed: give the CPU legs their cores back
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = max(1, min(args.steps, 10))
 
     # Every step copies its operands from pinned host memory and returns its C-shard to the
     # host.  A step is cut into row chunks on three streams (H2D, compute, D2H) so the copies

@@ -663,6 +663,16 @@ int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
             h->stats.launches++;
             h->stats.splitk++;
         }
+    } else if (h->variant != 10 && g.K <= skinny::MAXD && g.M >= 64 && g.N >= 256 && g.bNs == 1 && g.N % 4 == 0 &&
+               g.bKs % 4 == 0 && aligned16(g.b) && aligned16(g.c) && bias_ok) {
+        // tiny K (the dX of a narrow layer): bound by the write of C
+        const dim3 grid((g.N + skinny::SK_COLS - 1) / skinny::SK_COLS, (g.M + skinny::SK_ROWS - 1) / skinny::SK_ROWS);
+        if (grid.y > 65535u) return TT_ERR_UNSUPPORTED;
+        if (g.K <= 4)       skinny::skinny_k_kernel<1><<<grid, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.aKs, g.bKs, g.epi);
+        else if (g.K <= 8)  skinny::skinny_k_kernel<2><<<grid, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.aKs, g.bKs, g.epi);
+        else if (g.K <= 12) skinny::skinny_k_kernel<3><<<grid, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.aKs, g.bKs, g.epi);
+        else                skinny::skinny_k_kernel<4><<<grid, 256, 0, st>>>(g.a, g.b, g.c, g.M, g.N, g.K, g.aMs, g.aKs, g.bKs, g.epi);
+        h->stats.launches++;
     } else {
         return TT_ERR_UNSUPPORTED;
     }

@@ -1,6 +1,5 @@
 // FP32 kernels for products with one tiny dimension (<= 16): the 10-class output layer of
-// an MLP, value heads, matrix-vector products (a tiny K is left to the any-stride kernel,
-// which measured faster there).  A 128-wide tile would waste > 90 % of its
+// an MLP, value heads, matrix-vector products.  A 128-wide tile would waste > 90 % of its
 // FMAs on them; they are HBM-bound streams of the one large operand instead, so each kernel
 // reads that operand exactly once with 128-bit loads and keeps the small one in registers or
 // L1.  One accumulator per output, a k order that depends on the output row only, fixed
@@ -9,6 +8,7 @@
 //   skinny_n_kernel  C (M x N<=16) = A (M x K, K-major) . B (N x K, K-major)^T     reads A once
 //   skinny_m_kernel  C (M<=16 x N) = A (K x M)^T        . B (K x N, N-major)      reads B once
 //                    (K is cut into ranges across CTAs; partials are added in range order)
+//   skinny_k_kernel  C (M x N)     = A (M x K<=16)      . B (K x N, N-major)      writes C once
 #pragma once
 #include "gemm_common.h"
 #include "ptx.cuh"
@@ -289,6 +289,57 @@ skinny_n_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
             }
         }
+    }
+}
+
+// ---- small K ---------------------------------------------------------------------------------
+// C (M x N) = A (M x K<=16, any strides) . B (K x N, N-major): bound by the write of C.  A CTA owns
+// 64 rows x 1024 columns: a thread keeps the K float4 of B for its 4 columns in registers, the A tile
+// (64 x K, padded to 16 per row) sits in shared memory and is read as broadcasts, and every
+// instruction of a warp stores 512 contiguous bytes of one row.  One accumulator per output, k
+// ascending.
+constexpr int SK_ROWS = 64, SK_COLS = 1024;
+template <int KT4>   // K <= 4 * KT4
+__global__ void __launch_bounds__(256)
+skinny_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                int M, int N, int K, int aMs, int aKs, int bKs, Epilogue epi)
+{
+    __shared__ __align__(16) float as_[SK_ROWS][4 * KT4];
+    const int m0 = blockIdx.y * SK_ROWS;
+    const int n = blockIdx.x * SK_COLS + threadIdx.x * 4;
+    for (int i = threadIdx.x; i < SK_ROWS * 4 * KT4; i += 256) {
+        const int r = i / (4 * KT4), k = i - r * (4 * KT4);
+        as_[r][k] = (m0 + r < M && k < K) ? __ldg(a + static_cast<long long>(m0 + r) * aMs + static_cast<long long>(k) * aKs) : 0.f;
+    }
+    float4 bv[4 * KT4];
+#pragma unroll
+    for (int k = 0; k < 4 * KT4; k++)
+        bv[k] = (k < K && n < N) ? __ldg(reinterpret_cast<const float4*>(b + static_cast<long long>(k) * bKs + n))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (epi.bias && n < N) bias4 = __ldg(reinterpret_cast<const float4*>(epi.bias + n));
+    __syncthreads();
+    if (n >= N) return;
+    const int rows = min(SK_ROWS, M - m0);
+#pragma unroll 2
+    for (int r = 0; r < rows; r++) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k4 = 0; k4 < KT4; k4++) {
+            const float4 av = *reinterpret_cast<const float4*>(&as_[r][4 * k4]);
+            const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 bb = bv[4 * k4 + q];      // zeros beyond K: nothing to test
+                acc.x = fmaf(a4[q], bb.x, acc.x);
+                acc.y = fmaf(a4[q], bb.y, acc.y);
+                acc.z = fmaf(a4[q], bb.z, acc.z);
+                acc.w = fmaf(a4[q], bb.w, acc.w);
+            }
+        }
+        acc.x = act_apply(acc.x + bias4.x, epi.act); acc.y = act_apply(acc.y + bias4.y, epi.act);
+        acc.z = act_apply(acc.z + bias4.z, epi.act); acc.w = act_apply(acc.w + bias4.w, epi.act);
+        *reinterpret_cast<float4*>(c + static_cast<long long>(m0 + r) * N + n) = acc;
     }
 }
 

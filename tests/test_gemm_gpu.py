@@ -363,6 +363,30 @@ def test_tiny_m_stream_kernel(rt, case):
     assert np.abs(r1 - plain).max() <= fp32_bound(K, a, b)
 
 
+@pytest.mark.parametrize("case", [
+    # (M, N, K, strides)
+    (8192, 4096, 10, (10, 1, 4096, 1)),        # dX of the 10-class layer: g (M, 10) . W (10, N)
+    (1000, 260, 3, (3, 1, 260, 1)),
+    (64, 256, 16, (1, 64, 256, 1)),            # A stored (K, M)
+    (5000, 1028, 7, (7, 1, 1028, 1)),
+])
+def test_tiny_k_kernel(rt, case):
+    """Products with K <= 16 are bound by the write of C: one streaming kernel, B in registers,
+    the A tile in shared memory.  Against the oracle and the any-stride kernel (variant 1); bit-stable."""
+    M, N, K, st = case
+    rng = np.random.default_rng(M * 3 + N * 5 + K * 7)
+    a = rng.uniform(-1, 1, M * K).astype(np.float32)
+    b = rng.uniform(-1, 1, K * N).astype(np.float32)
+    rt.ResetCounters()
+    r1 = run_matmul(rt, a, b, M, N, K, st, 0)
+    stats = rt.Stats()
+    assert stats["skinny"] == 1 and stats["launches"] == 1, stats
+    assert np.array_equal(r1, run_matmul(rt, a, b, M, N, K, st, 0))
+    exp = oracle.matmul2d(a, b, M, N, K, *st)
+    assert np.abs(r1 - exp).max() <= fp32_bound(K, a, b)
+    assert np.array_equal(r1, run_matmul(rt, a, b, M, N, K, st, 1))     # same sums in the same order
+
+
 def test_nan_propagates_like_reference(rt):
     a = np.zeros((128, 64), dtype=np.float32)
     b = np.ones((64, 128), dtype=np.float32)

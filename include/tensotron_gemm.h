@@ -335,13 +335,6 @@ TT_API int tt_peer_group_create(tt_handle_t h, int world, int rank, long long n,
 TT_API int tt_peer_group_destroy(tt_peer_group_t g);
 /* Upper bound of one wait for another rank's flag (default 5000 ms). */
 TT_API int tt_peer_set_wait_limit(tt_peer_group_t g, int milliseconds);
-/* How tt_peer_adam_step brings the other ranks' parameter buffers up to date:
- * 0 (default) stores from the optimizer kernel itself; 1 the kernel writes this rank's buffer only
- * and the owned rows then travel by copy engine (cudaMemcpyAsync per rank and segment, followed by
- * the "rows updated" signal) on a stream of the group's own, ordered behind the kernel by an event
- * and joined back in tt_peer_sync: the transfer overlaps the rest of the backward pass.  Mode 1 is
- * for one process per GPU; it creates the stream and its events on first use (not during capture). */
-TT_API int tt_peer_set_broadcast(tt_peer_group_t g, int mode);
 
 /* tt_linear_bwd whose weight gradient (N x K, at float offset w_off of the flat buffer) is
  * stored row block by row block into the owners' slots for this rank, straight from the GEMM

@@ -1574,13 +1574,6 @@ struct tt_peer_group_s {
     float* params[MAX_PEERS];
     unsigned int* flags[MAX_PEERS];
     unsigned long long wait_limit_ns;
-    // copy-engine form of the parameter broadcast (tt_peer_set_broadcast): a side stream, an event
-    // per channel that orders it behind the optimizer kernel, one that joins it back
-    int broadcast_mode;
-    cudaStream_t side;
-    cudaEvent_t ev_adam[peer::CHANNELS];
-    cudaEvent_t ev_side_done;
-    bool side_busy;
 };
 
 static_assert(sizeof(cudaIpcMemHandle_t) == TT_IPC_HANDLE_BYTES, "IPC handle size");
@@ -1674,34 +1667,9 @@ TT_API int tt_peer_set_wait_limit(tt_peer_group_t g, int milliseconds)
     return TT_OK;
 }
 
-TT_API int tt_peer_set_broadcast(tt_peer_group_t g, int mode)
-{
-    if (!g || mode < 0 || mode > 1) return TT_ERR_INVALID_ARG;
-    tt_handle_t h = g->h;
-    TT_BIND(h);
-    if (mode == 1 && !g->side) {
-        if (cudaStreamCreateWithFlags(&g->side, cudaStreamNonBlocking) != cudaSuccess) { g->side = nullptr; return cuda_fail(h, cudaGetLastError(), "side stream"); }
-        bool ok = cudaEventCreateWithFlags(&g->ev_side_done, cudaEventDisableTiming) == cudaSuccess;
-        for (int c = 0; ok && c < peer::CHANNELS; c++)
-            ok = cudaEventCreateWithFlags(&g->ev_adam[c], cudaEventDisableTiming) == cudaSuccess;
-        if (!ok) return cuda_fail(h, cudaGetLastError(), "side stream events");
-    }
-    g->broadcast_mode = mode;
-    return TT_OK;
-}
-
 TT_API int tt_peer_group_destroy(tt_peer_group_t g)
 {
     if (!g) return TT_ERR_INVALID_ARG;
-    if (g->side) {
-        tt_handle_t h = g->h;
-        TT_BIND(h);
-        cudaStreamSynchronize(g->side);
-        for (int c = 0; c < peer::CHANNELS; c++)
-            if (g->ev_adam[c]) cudaEventDestroy(g->ev_adam[c]);
-        if (g->ev_side_done) cudaEventDestroy(g->ev_side_done);
-        cudaStreamDestroy(g->side);
-    }
     delete g;
     return TT_OK;
 }
@@ -1828,18 +1796,12 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
     if ((rc = fill_segments(h, g, n_owned, owned_off, owned_len, owned, owned4))) return rc;
     if ((rc = fill_segments(h, g, n_repl, repl_off, repl_len, repl, repl4))) return rc;
     unsigned int* step_counter = g->flags[g->rank] + peer::STEP_COUNTER_WORD;
-    // Copy-engine form: the kernel stores the new rows into this rank's buffer only (and tells only
-    // this rank); the other ranks' copies follow on the side stream, off the critical path.
-    const bool dma = g->broadcast_mode == 1 && g->world > 1 && g->side != nullptr;
     peer::PeerPtrs pp;
-    for (int o = 0; o < MAX_PEERS; o++) pp.p[o] = o < g->world && (!dma || o == g->rank) ? g->params[o] : nullptr;
+    for (int o = 0; o < MAX_PEERS; o++) pp.p[o] = o < g->world ? g->params[o] : nullptr;
     // tell every rank that this rank's rows are in its parameter buffer (last block of the kernel)
-    peer::FlagPtrs f, f_rest;
-    for (int o = 0; o < MAX_PEERS; o++) {
-        unsigned int* flag = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + MAX_PEERS + g->rank : nullptr;
-        f.p[o] = !dma || o == g->rank ? flag : nullptr;
-        f_rest.p[o] = dma && o != g->rank ? flag : nullptr;
-    }
+    peer::FlagPtrs f;
+    for (int o = 0; o < MAX_PEERS; o++)
+        f.p[o] = o < g->world ? g->flags[o] + channel * peer::CHANNEL_WORDS + MAX_PEERS + g->rank : nullptr;
     long long blocks = (owned4 + repl4 + 255) / 256;
     const long long cap = static_cast<long long>(h->num_sms) * 16;
     if (blocks > cap) blocks = cap;
@@ -1849,26 +1811,8 @@ TT_API int tt_peer_adam_step(tt_handle_t h, void* stream, tt_peer_group_t g, int
         beta2, lr, eps, coupled_wd, decoupled_factor, g->flags[g->rank] + channel * peer::CHANNEL_WORDS, step_counter,
         h->status, g->wait_limit_ns, f, g->flags[g->rank] + peer::DONE_COUNTER_WORD + channel);
     h->stats.launches++;
-    cudaError_t e = cudaGetLastError();
+    const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(h, e, "peer Adam launch");
-    if (dma) {
-        // side stream: behind the optimizer kernel, one copy per owned segment and rank, then the signal
-        if ((e = cudaEventRecord(g->ev_adam[channel], st)) != cudaSuccess) return cuda_fail(h, e, "peer event record");
-        if ((e = cudaStreamWaitEvent(g->side, g->ev_adam[channel], 0)) != cudaSuccess) return cuda_fail(h, e, "peer side wait");
-        for (int sgi = 0; sgi < owned.n; sgi++) {
-            const float* src = g->params[g->rank] + owned.off[sgi];
-            const size_t bytes = sizeof(float) * static_cast<size_t>(owned.len[sgi]);
-            for (int o = 0; o < g->world; o++) {
-                if (o == g->rank || bytes == 0) continue;
-                e = cudaMemcpyAsync(g->params[o] + owned.off[sgi], src, bytes, cudaMemcpyDeviceToDevice, g->side);
-                if (e != cudaSuccess) return cuda_fail(h, e, "peer parameter copy");
-            }
-        }
-        peer::rows_updated_signal_kernel<<<1, 32, 0, g->side>>>(f_rest, g->world, step_counter, h->status);
-        h->stats.launches++;
-        if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(h, e, "peer signal launch");
-        g->side_busy = true;
-    }
     return TT_OK;
 }
 
@@ -1878,13 +1822,6 @@ TT_API int tt_peer_sync(tt_handle_t h, void* stream, tt_peer_group_t g, int n_ch
     if (n_channels < 1 || n_channels > peer::CHANNELS) return fail(h, TT_ERR_INVALID_ARG, "bad channel count");
     TT_BIND(h);
     h->stats.calls++;
-    if (g->side_busy) {
-        // join the side stream: its copies read this rank's rows, which the next step rewrites
-        cudaError_t je = cudaEventRecord(g->ev_side_done, g->side);
-        if (je == cudaSuccess) je = cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), g->ev_side_done, 0);
-        if (je != cudaSuccess) return cuda_fail(h, je, "peer side join");
-        g->side_busy = false;
-    }
     peer::wait_kernel<<<1, 32 * n_channels, 0, static_cast<cudaStream_t>(stream)>>>(
         g->flags[g->rank] + MAX_PEERS, g->world, g->flags[g->rank] + peer::STEP_COUNTER_WORD, h->status,
         g->wait_limit_ns);

@@ -229,9 +229,7 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
         reinterpret_cast<float4*>(m)[at] = mm;
         reinterpret_cast<float4*>(v)[at] = vv;
         if (is_owned) {
-            // (a null entry: that rank's copy is brought up to date by a copy engine afterwards)
-            for (int o = 0; o < world; o++)
-                if (params.p[o]) reinterpret_cast<float4*>(params.p[o])[at] = pp;
+            for (int o = 0; o < world; o++) reinterpret_cast<float4*>(params.p[o])[at] = pp;
         } else {
             reinterpret_cast<float4*>(own)[at] = pp;
         }
@@ -257,21 +255,6 @@ reduce_adam_kernel(const float* __restrict__ stage, long long n, int world, int 
         const unsigned int e = *step_counter;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.p[o]), "r"(e) : "memory");
     }
-}
-
-// "Rows updated" signal of the copy-engine form: runs on the group's side stream after the copies
-// of the owned rows into the other ranks' parameter buffers; thread o tells rank o.  Nothing is
-// signalled when an error is recorded on the handle (the rows that were copied are then the
-// unchanged ones).
-__global__ void rows_updated_signal_kernel(FlagPtrs signal, int world, const unsigned int* step_counter,
-                                           const unsigned int* status)
-{
-    const int o = threadIdx.x;
-    if (o >= world || !signal.p[o]) return;
-    if (*reinterpret_cast<const volatile unsigned int*>(status) != 0u) return;
-    __threadfence_system();
-    const unsigned int e = *step_counter;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.p[o]), "r"(e) : "memory");
 }
 
 }  // namespace peer

@@ -86,9 +86,6 @@ class MlpTrainer:
         if exchange == "peer":
             from .peer import CHANNELS, PeerGroup, exchange_plan, merge_segments
             self.peer = peer_group or PeerGroup(self.rt, total, process_group)
-            if peer_group is None and self.peer.world > 1:
-                # one process per GPU: updated rows travel by copy engine, off the backward pass's stream
-                self.peer.set_broadcast(True)
             self.own_rows, owned, replicated = exchange_plan(self.dims, self.peer.world, self.offs)
             # One exchange channel per layer, so a layer's optimizer step and the transfer of its
             # updated rows overlap the backward pass of the layers below; networks with more

@@ -186,7 +186,6 @@ class PeerGroup:
         L.tt_peer_adam_step.argtypes = [vp, vp, vp, i, i, pll, pll, i, pll, pll, vp, vp, vp, f, f, f, f, f, f, i]
         L.tt_peer_sync.argtypes = [vp, vp, vp, i]
         L.tt_peer_set_wait_limit.argtypes = [vp, i]
-        L.tt_peer_set_broadcast.argtypes = [vp, i]
         L._peer_declared = True
 
     # -- the three calls of a step ------------------------------------------------------------
@@ -214,12 +213,6 @@ class PeerGroup:
 
     def set_wait_limit(self, milliseconds):
         self.rt._ck(self.rt._L.tt_peer_set_wait_limit(self._g, int(milliseconds)))
-
-    def set_broadcast(self, copy_engines):
-        """How updated rows reach the other ranks: stores from the optimizer kernel (False), or copy
-        engines on the group's side stream, overlapping the rest of the backward pass (True; one
-        process per GPU)."""
-        self.rt._ck(self.rt._L.tt_peer_set_broadcast(self._g, 1 if copy_engines else 0))
 
     def sync(self, n_channels=1, stream=None):
         rt = self.rt

@@ -24,7 +24,7 @@ EXPORTS = [
     "tt_conv2d_workspace", "tt_conv2d_fwd", "tt_conv2d_bwd", "tt_shard_range",
     "tt_peer_alloc", "tt_peer_free", "tt_peer_export", "tt_peer_open", "tt_peer_close", "tt_peer_group_create",
     "tt_peer_group_destroy", "tt_peer_linear_bwd", "tt_peer_push", "tt_peer_adam_step", "tt_peer_sync",
-    "tt_peer_set_wait_limit", "tt_peer_set_broadcast",
+    "tt_peer_set_wait_limit",
 ]
 
 

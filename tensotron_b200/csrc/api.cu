@@ -370,7 +370,14 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             const size_t need = 2 * static_cast<size_t>(h->num_sms) * bm * bn * sizeof(float);   // two partial-tile slots per CTA
             const long long waves = (tiles + h->num_sms - 1) / h->num_sms;
             const double fill = static_cast<double>(tiles) / (static_cast<double>(waves) * h->num_sms);
-            if (need <= ws_avail && fill < 0.97) {
+            // A remainder of at most half a wave behind whole waves is cut into k-aligned equal
+            // ranges (try_launch_simt_tm): whole + 1 / split waves, locality of a whole-tile wave.
+            const long long whole = tiles / h->num_sms, rest = tiles - whole * h->num_sms;
+            if (need <= ws_avail && whole >= 1 && rest > 0 && rest * 2 <= h->num_sms && k_tiles >= 2 * (h->num_sms / rest)) {
+                const double split = static_cast<double>(h->num_sms / rest);
+                const double t = (static_cast<double>(whole) + 1.0 / split) * (k_tiles + 2.0) * tile_cost + 11.0;
+                if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true, sh.nj}; }
+            } else if (need <= ws_avail && fill < 0.97) {
                 // measured: storing and re-reading the partial tiles costs about 20 us (11 units of a
                 // 128x128 k-tile) whatever the shape, and the stream-K form of the kernel runs its
                 // main loop about 4 % slower than the whole-tile form (16384^3: 145.1 ms against
@@ -428,9 +435,17 @@ int try_launch_simt_tm(tt_handle_t h, cudaStream_t st, const GemmCall& g, const 
     // less than half a wave, so the unit part holds between half a tile and a tile and a half per
     // CTA (an output tile is then shared by three CTAs at most).
     p.sk_first = 0;
+    p.sk_split = 0;
     if (plan.streamk && tiles >= h->num_sms) {
         long long whole = tiles / h->num_sms;
-        if (tiles - whole * h->num_sms < h->num_sms / 2) whole -= 1;
+        const long long rest = tiles - whole * h->num_sms;
+        if (rest > 0 && rest * 2 <= h->num_sms && k_tiles >= 2 * (h->num_sms / rest)) {
+            // at most half a wave left: every remaining tile is cut into equal k ranges, one per
+            // CTA, so the CTAs stay aligned in k (and share operand panels in L2 like a whole wave)
+            p.sk_split = static_cast<int>(h->num_sms / rest);
+        } else if (rest < h->num_sms / 2) {
+            whole -= 1;
+        }
         p.sk_first = whole * h->num_sms;
     }
     p.shape.work = plan.streamk ? (tiles - p.sk_first) * k_tiles : tiles * plan.splits;

@@ -105,6 +105,11 @@ struct Params {
     // round-robin like MODE_TILES; only the tiles behind them are dealt out as k-tile units
     // (shape.work counts those units)
     long long sk_first;
+    // stream-K, aligned form (sk_split >= 2, for a remainder of at most half a wave): every
+    // remaining tile is cut into sk_split equal k ranges, CTA j takes tile j / sk_split, range
+    // j % sk_split.  The CTAs that work on the same range index then walk k together, which keeps
+    // the L2 sharing of a whole-tile wave; contiguous unit ranges (sk_split == 0) do not.
+    int sk_split;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act)
@@ -226,8 +231,20 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
     const long long a_end = MODE == 2 ? p.sk_first : p.shape.work;
     // (the unit part is at most a tile and a half per CTA: its unit count fits 32 bits, the host
     // checks)
-    const int w_begin = MODE == 2 ? static_cast<int>((p.shape.work * blockIdx.x) / gridDim.x) : 0;
-    const int w_end = MODE == 2 ? static_cast<int>((p.shape.work * (blockIdx.x + 1)) / gridDim.x) : 0;
+    int w_begin = 0, w_end = 0;
+    if (MODE == 2) {
+        if (p.sk_split >= 2) {
+            const int kps = (k_tiles + p.sk_split - 1) / p.sk_split;
+            const int tile = blockIdx.x / p.sk_split, part = blockIdx.x - tile * p.sk_split;
+            if (static_cast<long long>(tile) * k_tiles < p.shape.work) {      // (CTAs beyond the last tile idle here)
+                w_begin = tile * k_tiles + min(k_tiles, part * kps);
+                w_end = tile * k_tiles + min(k_tiles, (part + 1) * kps);
+            }
+        } else {
+            w_begin = static_cast<int>((p.shape.work * blockIdx.x) / gridDim.x);
+            w_end = static_cast<int>((p.shape.work * (blockIdx.x + 1)) / gridDim.x);
+        }
+    }
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -600,9 +617,15 @@ sgemm_simt_kernel(const __grid_constant__ CUtensorMap map_a,
                 // kernel a second loop over all 128 of them, which costs the main loop registers.)
                 volatile int& s_hi = *reinterpret_cast<volatile int*>(smem + C::OFF_BAR + 256);
                 if (tid == 0) {
-                    const long long u_hi = (unit - p.sk_first + 1) * k_tiles;   // end of this tile in the unit range
                     int hi = blockIdx.x;
-                    while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
+                    if (p.sk_split >= 2) {
+                        // the non-empty ranges of this tile: parts 1 .. ceil(k_tiles / kps) - 1
+                        const int kps = (k_tiles + p.sk_split - 1) / p.sk_split;
+                        hi = blockIdx.x + (k_tiles + kps - 1) / kps - 1;
+                    } else {
+                        const long long u_hi = (unit - p.sk_first + 1) * k_tiles;   // end of this tile in the unit range
+                        while (hi + 1 < static_cast<int>(gridDim.x) && (p.shape.work * (hi + 1)) / gridDim.x < u_hi) hi++;
+                    }
                     s_hi = hi;
                     for (int cta = blockIdx.x + 1; cta <= hi; cta++) {
                         const unsigned long long t0 = global_timer_ns();

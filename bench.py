@@ -889,7 +889,8 @@ def main():
             "traffic_note": "ncu DRAM bytes per launch; 16384 is the 8192^3 capture scaled (reads x 8, writes x 4)",
             "peak_source": "derived: %d SMs x 128 FP32 lanes x 2 x %.0f MHz (max SM clock); the "
                            "measured-peaks file has no FP32 SIMT figure" % (sms, max_mhz),
-            "kernel": "sgemm_simt_kernel<MN-major A (transposed once into the workspace), N-major B>; "
+            "kernel": "sgemm_simt_kernel<MN-major A (transposed once into the workspace), N-major B>, whole waves of "
+                      "256x128 tiles, a remainder of at most half a wave cut into k-aligned ranges; "
                       "`achieved` is over the whole step, transposition included",
             "algorithmic_flops_per_launch": 2.0 * rows * n * n,
         }

@@ -59,6 +59,9 @@ typedef struct tt_handle_s* tt_handle_t;
 #define TT_MATH_FP32 0    /* strict IEEE float32 FFMA, the default                      */
 #define TT_MATH_TF32 3    /* AllowTf32: tcgen05 kind::tf32, fp32 accumulate             */
 #define TT_MATH_3XTF32 4  /* three tf32 products per term, recovers ~fp32 accuracy      */
+/* The tensor-core modes are permissions, as AllowTf32 is: products with a dimension of at most
+ * 16, and in mode 4 single products up to M*N*K = 2^28, run on the strict-FP32 kernels where those
+ * are faster (and at least as accurate). */
 
 /* activations fused into the Linear epilogue (src/Tensotron/Ops.Unary.cs:89-105) */
 #define TT_ACT_NONE 0

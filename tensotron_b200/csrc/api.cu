@@ -46,6 +46,7 @@ constexpr size_t DEFAULT_WORKSPACE = 256ull << 20;
 // stream-K flag per CTA (zero between launches).
 constexpr int STREAMK_FLAGS_WORD = 64, HANDLE_WORDS = 1024;
 constexpr long long TMA_MIN_FLOP_ELEMS = 1ll << 21;  // M*N*K below this -> any-stride kernel
+constexpr long long SMALL_3XTF32_MAX_ELEMS = 1ll << 28;  // M x N x K up to which 3xTF32 runs on the strict-FP32 kernels
 constexpr long long LINEAR_SMALL_MAX_ELEMS = 1ll << 21;  // M x N x K up to which a Linear backward is ONE launch (linear_small.cuh)
 constexpr long long SMALL_MAX_FLOP_ELEMS = 1ll << 27;  // ... and up to this when the output is a few tiles only
 
@@ -733,7 +734,12 @@ int run_gemm(tt_handle_t h, cudaStream_t st, const GemmCall& g)
         if (rc != TT_ERR_UNSUPPORTED) return rc;
     }
     if (g.K > 0 && h->variant != 1 && h->variant != 8) {
-        if (h->math_mode != TT_MATH_FP32 && g.batch.red_count == 1) {  // the tensor-core kernel has no reduced axis
+        // 3xTF32 on a small single product: its two operand-split launches in front of the GEMM cost
+        // more than the strict-FP32 kernels need for the whole product (512^3: 22.6 us against
+        // 18.5 us), and strict FP32 is at least as accurate as the mode asks for.
+        const bool small_3x = h->math_mode == TT_MATH_3XTF32 && h->variant == 0 && g.batch_count == 1 &&
+                              vol <= SMALL_3XTF32_MAX_ELEMS;
+        if (h->math_mode != TT_MATH_FP32 && g.batch.red_count == 1 && !small_3x) {  // the tensor-core kernel has no reduced axis
             int n_launch = 0;
             const int rc = tf32::try_launch(h->math_mode, st, g.a, g.b, g.c, g.M, g.N, g.K, g.aMs,
                                             g.aKs, g.bKs, g.bNs, g.batch_count, g.batch.rank,

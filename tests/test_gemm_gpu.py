@@ -569,7 +569,10 @@ def test_linear_golden_cases(rt, seeded_cases):
         assert np.abs(db.cpu().numpy() - dbo).max() <= fp32_bound(64, arrays[c["grad_output"]], 1.0)
 
 
-@pytest.mark.parametrize("shape", [(256, 512, 384, "relu"), (100, 36, 52, "tanh"), (33, 7, 5, "relu"), (1024, 10, 4096, "none")])
+@pytest.mark.parametrize("shape", [(256, 512, 384, "relu"), (100, 36, 52, "tanh"), (33, 7, 5, "relu"), (1024, 10, 4096, "none"),
+                                   (8192, 10, 512, "tanh"),      # tall, 10 outputs: the TMA-fed stream with bias + activation
+                                   (256, 512, 10, "relu"),       # 10 inputs: the output-streaming kernel with bias + activation
+                                   (16, 1024, 2048, "relu")])    # 16 rows: the tiny-M stream, epilogue in its range sum
 def test_linear_matches_oracle(rt, shape):
     M, N, K, act = shape
     rng = np.random.default_rng(M + N + K)

@@ -376,7 +376,9 @@ SimtPlan plan_simt(const tt_handle_t h, int M, int N, int K, int batch, size_t w
             const long long whole = tiles / h->num_sms, rest = tiles - whole * h->num_sms;
             if (need <= ws_avail && whole >= 1 && rest > 0 && rest * 2 <= h->num_sms && k_tiles >= 2 * (h->num_sms / rest)) {
                 const double split = static_cast<double>(h->num_sms / rest);
-                const double t = (static_cast<double>(whole) + 1.0 / split) * (k_tiles + 2.0) * tile_cost + 11.0;
+                // (the cost of the partial tiles scales with their size: 11 units for 256 x 128)
+                const double t = (static_cast<double>(whole) + 1.0 / split) * (k_tiles + 2.0) * tile_cost +
+                                 11.0 * (bm * bn) / (256.0 * 128.0);
                 if (t < best_t) { best_t = t; best = SimtPlan{tm, 1, k_tiles, true, sh.nj}; }
             } else if (need <= ws_avail && fill < 0.97) {
                 // measured: storing and re-reading the partial tiles costs about 20 us (11 units of a

@@ -582,8 +582,9 @@ int try_launch_skinny(tt_handle_t h, cudaStream_t st, const GemmCall& g)
     if (g.batch_count != 1 || g.batch.red_count != 1 || g.K <= 0) return TT_ERR_UNSUPPORTED;
     const bool bias_ok = !g.epi.bias || aligned16(g.epi.bias);
     const size_t ws_avail = h->workspace_bytes > g.ws_off ? h->workspace_bytes - g.ws_off : 0;
-    // (the tiny-N form only in strict FP32: in the TF32 modes the tensor-core kernel is faster)
-    if (h->math_mode == TT_MATH_FP32 && g.N <= skinny::MAXD && g.M >= 64 && g.K >= 128 && g.aKs == 1 && g.bKs == 1 && g.K % 4 == 0 &&
+    // (in every math mode: the tensor-core kernel takes 52 us for 8192 x 10 x 4096 and 40 us for
+    // 1024 x 10 x 4096, these forms 41 and 17 us, in strict FP32 arithmetic)
+    if (g.N <= skinny::MAXD && g.M >= 64 && g.K >= 128 && g.aKs == 1 && g.bKs == 1 && g.K % 4 == 0 &&
         g.aMs % 4 == 0 && (g.N == 1 || g.bNs % 4 == 0) && aligned16(g.a) && aligned16(g.b)) {
         // 8 rows per CTA while the accumulators fit comfortably; 4 rows for N > 8 (8 x 12 and
         // 8 x 16 accumulators run slower: 105 vs 88 us at 8192 x 10 x 4096)
